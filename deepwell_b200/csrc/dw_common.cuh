@@ -1,0 +1,109 @@
+// Shared device helpers for the sm_100a MXFP8 kernels: MX arithmetic on bit patterns and
+// thin inline-PTX wrappers (mbarrier, TMA, tcgen05).  No fast-math anywhere: the quantiser
+// must be bit-exact.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/dw_mxfp8.h"
+
+namespace dw {
+
+constexpr int kBlock = 32;  // elements per scaling block
+
+// ------------------------------------------------------------------------------------------
+// MX arithmetic
+// ------------------------------------------------------------------------------------------
+
+// E8M0 byte from the bf16 pattern of a block's amax (sign cleared, NaN elements excluded).
+//   rule 0: e = floor(log2 amax) - 8     rule 1: e = ceil(log2(amax/448))
+// byte = e + 127 clamped to [0, 254]; amax == 0 -> 127 (scale 1.0).
+__device__ __forceinline__ uint32_t e8m0_from_amax(uint32_t amax, int rule) {
+    const uint32_t ef = amax >> 7;
+    int b = static_cast<int>(ef) - 8;
+    if (rule == DW_RULE_REF_CEIL && (amax & 0x7Fu) > 0x60u && ef > 0u && ef < 255u) b += 1;
+    b = max(b, 0);
+    return amax == 0u ? 127u : static_cast<uint32_t>(b);
+}
+
+// 2^(127 - byte) as fp32 (exact); byte 254 gives the subnormal 2^-127.
+__device__ __forceinline__ float e8m0_inverse(uint32_t byte) {
+    return __uint_as_float(byte >= 254u ? 0x00400000u : ((254u - byte) << 23));
+}
+
+// 2^(byte - 127) as fp32; byte 0 gives the subnormal 2^-127.
+__device__ __forceinline__ float e8m0_value(uint32_t byte) {
+    return __uint_as_float(byte == 0u ? 0x00400000u : (byte << 23));
+}
+
+// max over the two unsigned 16-bit halves, lane-wise
+__device__ __forceinline__ uint32_t max_u16x2(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("max.u16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+
+// two fp32 -> packed E4M3 pair, RNE, saturating to +-448; `lo` lands in bits [0,8).
+__device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi) {
+    uint16_t d;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(d) : "f"(hi), "f"(lo));
+    return d;
+}
+
+// One bf16x2 word scaled by `inv` -> two E4M3 codes in bits [0,16).
+__device__ __forceinline__ uint32_t quant_word(uint32_t w, float inv) {
+    const float lo = __uint_as_float(w << 16) * inv;
+    const float hi = __uint_as_float(w & 0xFFFF0000u) * inv;
+    return cvt_e4m3x2(lo, hi);
+}
+
+// amax pattern (15-bit magnitude) over n bf16x2 words, NaN elements dropped as fmaxf would.
+template <int N>
+__device__ __forceinline__ uint32_t amax_words(const uint32_t (&w)[N]) {
+    uint32_t m = 0;
+#pragma unroll
+    for (int i = 0; i < N; ++i) m = max_u16x2(m, w[i] & 0x7FFF7FFFu);
+    uint32_t a = max(m & 0xFFFFu, m >> 16);
+    if (a > 0x7F80u) {  // a NaN somewhere: redo with the NaNs filtered (rare)
+        a = 0;
+#pragma unroll
+        for (int i = 0; i < N; ++i) {
+            const uint32_t lo = w[i] & 0x7FFFu, hi = (w[i] >> 16) & 0x7FFFu;
+            if (lo <= 0x7F80u) a = max(a, lo);
+            if (hi <= 0x7F80u) a = max(a, hi);
+        }
+    }
+    return a;
+}
+
+// Byte offset of (row r, k-block kb) in the tiled (tcgen05) scale layout; kt = ceil(KB/4).
+__device__ __host__ __forceinline__ int64_t sf_tiled_offset(int64_t r, int64_t kb, int64_t kt) {
+    return ((r >> 7) * kt + (kb >> 2)) * 512 + (r & 31) * 16 + ((r >> 5) & 3) * 4 + (kb & 3);
+}
+
+// ------------------------------------------------------------------------------------------
+// memory helpers
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint4 ldg_nc_v4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ void ldg_nc_v8(const void* p, uint32_t (&w)[8]) {
+    asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
+                 : "l"(p));
+}
+
+__device__ __forceinline__ void stg_v4(void* p, uint4 v) {
+    asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+}  // namespace dw

@@ -1,0 +1,477 @@
+// MX quantisation kernels for sm_100a: bf16 -> E4M3 codes + E8M0 block scales.
+//
+// Replaces quantize_to_mxfp8_kernel / dequantize_from_mxfp8_kernel and fills in the empty
+// transpose_quantize_to_mxfp8_kernel of the reference (csrc/mxfp8_quantization.cu:29-226).
+// The reference launches one 256-thread CTA per 32 elements and reads the input twice; here
+// every kernel is a single pass sized to keep HBM busy:
+//
+//   mx_quant_row_kernel   row-wise, no shared memory: 32-byte loads (16 elements per thread),
+//                         block amax by one warp shuffle, 16-byte packed E4M3 stores.
+//   mx_quant_tile_kernel  column-wise (transposed payload) and the fused "both directions from
+//                         one read" form: a 128x128 bf16 tile is staged in shared memory, the
+//                         row-wise part is computed from the registers that loaded it, the
+//                         column pass reads the tile conflict-free down the rows.
+//   mx_quant_generic_kernel  any shape / alignment / direction (ragged last block), one thread
+//                         per scaling block.
+//
+// Scales are written either flat [R, K/32] or directly in the 512-byte-tile layout the
+// tcgen05 block-scaled MMA reads (DW_SF_TILED), so the GEMM needs no re-layout pass.
+// All arithmetic is on bit patterns; no fast-math; results are bit-exact against the oracle.
+
+#include <algorithm>
+
+#include "dw_common.cuh"
+
+namespace dw {
+
+// ------------------------------------------------------------------------------------------
+// Row-wise fast path.  cols % 32 == 0.  One thread = 16 consecutive elements (half a block).
+// ------------------------------------------------------------------------------------------
+template <bool kWide>  // kWide: 32-byte aligned input -> one 256-bit load per chunk
+__global__ void __launch_bounds__(256)
+mx_quant_row_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes, uint8_t* __restrict__ scales,
+                    uint32_t total_chunks, uint32_t chunks_per_row, int rule, int layout, int packed_sf) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t T = gridDim.x * blockDim.x;
+    const uint32_t kb_per_row = chunks_per_row >> 1;
+    const int64_t kt = (kb_per_row + 3) >> 2;
+
+    for (uint32_t base = blockIdx.x * blockDim.x + (threadIdx.x & ~31u); base < total_chunks; base += 2u * T) {
+        uint32_t idx[2] = {base + lane, base + T + lane};
+        uint32_t w[2][8];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            if (idx[u] < total_chunks && idx[u] >= base) {   // second test guards uint32 wrap-around
+                const uint16_t* p = x + static_cast<int64_t>(idx[u]) * 16;
+                if (kWide) {
+                    ldg_nc_v8(p, w[u]);
+                } else {
+                    const uint4 a = ldg_nc_v4(p), b = ldg_nc_v4(p + 8);
+                    w[u][0] = a.x; w[u][1] = a.y; w[u][2] = a.z; w[u][3] = a.w;
+                    w[u][4] = b.x; w[u][5] = b.y; w[u][6] = b.z; w[u][7] = b.w;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) w[u][i] = 0;
+                idx[u] = 0xFFFFFFFFu;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            uint32_t amax = amax_words(w[u]);
+            amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+            const uint32_t sb = e8m0_from_amax(amax, rule);
+            const float inv = e8m0_inverse(sb);
+            uint4 q;
+            q.x = quant_word(w[u][0], inv) | (quant_word(w[u][1], inv) << 16);
+            q.y = quant_word(w[u][2], inv) | (quant_word(w[u][3], inv) << 16);
+            q.z = quant_word(w[u][4], inv) | (quant_word(w[u][5], inv) << 16);
+            q.w = quant_word(w[u][6], inv) | (quant_word(w[u][7], inv) << 16);
+            const bool valid = idx[u] != 0xFFFFFFFFu;
+            if (valid) stg_v4(codes + static_cast<int64_t>(idx[u]) * 16, q);
+
+            if (packed_sf) {
+                // cols % 128 == 0: lanes 0,2,4,6 of each group of 8 hold k-blocks kb..kb+3 of one row
+                uint32_t pk = sb;
+                pk |= __shfl_down_sync(0xFFFFFFFFu, sb, 2) << 8;
+                pk |= __shfl_down_sync(0xFFFFFFFFu, sb, 4) << 16;
+                pk |= __shfl_down_sync(0xFFFFFFFFu, sb, 6) << 24;
+                if (valid && (lane & 7u) == 0u) {
+                    int64_t off;
+                    if (layout == DW_SF_TILED) {
+                        const uint32_t row = idx[u] / chunks_per_row;
+                        const uint32_t kb = (idx[u] - row * chunks_per_row) >> 1;
+                        off = sf_tiled_offset(row, kb, kt);
+                    } else {
+                        off = idx[u] >> 1;
+                    }
+                    *reinterpret_cast<uint32_t*>(scales + off) = pk;
+                }
+            } else if (valid && (lane & 1u) == 0u) {
+                int64_t off;
+                if (layout == DW_SF_TILED) {
+                    const uint32_t row = idx[u] / chunks_per_row;
+                    const uint32_t kb = (idx[u] - row * chunks_per_row) >> 1;
+                    off = sf_tiled_offset(row, kb, kt);
+                } else {
+                    off = idx[u] >> 1;
+                }
+                scales[off] = static_cast<uint8_t>(sb);
+            }
+        }
+    }
+}
+
+// Writes 127 into the padding bytes of a tiled scale buffer that mx_quant_row_kernel does not
+// touch (rows beyond `rows` in the last row tile, k-blocks beyond `kb` in the last k tile).
+__global__ void mx_sf_pad_kernel(uint8_t* __restrict__ scales, int64_t rows, int64_t kb, int64_t rt, int64_t kt) {
+    const int64_t total = rt * kt * 512;
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t tile = i >> 9, in = i & 511;
+        const int64_t r = (tile / kt) * 128 + ((in >> 2) & 3) * 32 + (in >> 4);
+        const int64_t c = (tile % kt) * 4 + (in & 3);
+        if (r >= rows || c >= kb) scales[i] = 127;
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Tile kernel: column-wise transposed payload, optionally fused with the row-wise form.
+// rows % 32 == 0, cols % 32 == 0.  CTA = 256 threads, tile = 128 rows x 128 cols.
+// ------------------------------------------------------------------------------------------
+template <bool kDoRow, bool kDoCol>
+__global__ void __launch_bounds__(256)
+mx_quant_tile_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes_row, uint8_t* __restrict__ scales_row,
+                     uint8_t* __restrict__ codes_col_t, uint8_t* __restrict__ scales_col, int64_t rows, int64_t cols,
+                     uint32_t tiles_c, int rule, int layout) {
+    __shared__ __align__(16) uint4 tile[128][16];
+    __shared__ __align__(16) uint8_t sf_row[512];
+    __shared__ __align__(16) uint8_t sf_col[512];
+
+    const uint32_t t = threadIdx.x;
+    const uint32_t tr = blockIdx.x / tiles_c, tc = blockIdx.x - tr * tiles_c;
+    const int64_t r0 = static_cast<int64_t>(tr) * 128, c0 = static_cast<int64_t>(tc) * 128;
+    const int64_t kb_row = cols >> 5, kb_col = rows >> 5;           // k-blocks per operand row
+    const int64_t kt_row = (kb_row + 3) >> 2, kt_col = (kb_col + 3) >> 2;
+
+    // ---- load 8 chunks of 8 elements per thread; all loads issued before any use ----
+    const uint32_t cc = t & 15u;
+    const int64_t gc = c0 + cc * 8;
+    uint4 v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int64_t gr = r0 + (t >> 4) + 16 * j;
+        v[j] = (gr < rows && gc < cols) ? ldg_nc_v4(x + gr * cols + gc) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const uint32_t row = (t >> 4) + 16 * j;
+        if (kDoCol) tile[row][cc] = v[j];
+        if (kDoRow) {
+            const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+            uint32_t amax = amax_words(w);
+            amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+            amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
+            const uint32_t sb = e8m0_from_amax(amax, rule);
+            const float inv = e8m0_inverse(sb);
+            uint2 q;
+            q.x = quant_word(w[0], inv) | (quant_word(w[1], inv) << 16);
+            q.y = quant_word(w[2], inv) | (quant_word(w[3], inv) << 16);
+            const int64_t gr = r0 + row;
+            if (gr < rows && gc < cols) *reinterpret_cast<uint2*>(codes_row + gr * cols + gc) = q;
+            if ((cc & 3u) == 0u) sf_row[(row & 31u) * 16 + (row >> 5) * 4 + (cc >> 2)] = static_cast<uint8_t>(sb);
+        }
+    }
+    __syncthreads();
+
+    if (kDoRow) {  // scales of the row-wise operand [rows, cols/32]
+        if (layout == DW_SF_TILED) {
+            if (t < 32) {
+                uint4* dst = reinterpret_cast<uint4*>(scales_row + (static_cast<int64_t>(tr) * kt_row + tc) * 512);
+                dst[t] = reinterpret_cast<const uint4*>(sf_row)[t];
+            }
+        } else if (t < 128) {
+            const int64_t gr = r0 + t, kb0 = static_cast<int64_t>(tc) * 4;
+            if (gr < rows) {
+#pragma unroll
+                for (int b = 0; b < 4; ++b)
+                    if (kb0 + b < kb_row) scales_row[gr * kb_row + kb0 + b] = sf_row[(t & 31u) * 16 + (t >> 5) * 4 + b];
+            }
+        }
+    }
+
+    if (kDoCol) {
+        // thread = (column pair p, row block rb): 32 words down the rows, two columns at once
+        const uint32_t p = t & 63u, rb = t >> 6;
+        const uint32_t* tw = reinterpret_cast<const uint32_t*>(&tile[0][0]);
+        uint32_t w[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) w[i] = tw[(rb * 32 + i) * 64 + p];
+        uint32_t m = 0;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) m = max_u16x2(m, w[i] & 0x7FFF7FFFu);
+        uint32_t amax_a = m & 0xFFFFu, amax_b = m >> 16;
+        if (amax_a > 0x7F80u || amax_b > 0x7F80u) {  // NaN present: filtered recomputation
+            amax_a = 0; amax_b = 0;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                const uint32_t lo = w[i] & 0x7FFFu, hi = (w[i] >> 16) & 0x7FFFu;
+                if (lo <= 0x7F80u) amax_a = max(amax_a, lo);
+                if (hi <= 0x7F80u) amax_b = max(amax_b, hi);
+            }
+        }
+        const uint32_t sb_a = e8m0_from_amax(amax_a, rule), sb_b = e8m0_from_amax(amax_b, rule);
+        const float inv_a = e8m0_inverse(sb_a), inv_b = e8m0_inverse(sb_b);
+        uint32_t qa[8], qb[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            uint32_t a = 0, b = 0;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint32_t w0 = w[4 * i + 2 * h], w1 = w[4 * i + 2 * h + 1];
+                a |= cvt_e4m3x2(__uint_as_float(w0 << 16) * inv_a, __uint_as_float(w1 << 16) * inv_a) << (16 * h);
+                b |= cvt_e4m3x2(__uint_as_float(w0 & 0xFFFF0000u) * inv_b, __uint_as_float(w1 & 0xFFFF0000u) * inv_b)
+                     << (16 * h);
+            }
+            qa[i] = a; qb[i] = b;
+        }
+        const int64_t gcol = c0 + 2 * p, grow = r0 + rb * 32;
+        if (grow < rows) {
+            if (gcol < cols) {
+                uint8_t* d = codes_col_t + gcol * rows + grow;
+                stg_v4(d, make_uint4(qa[0], qa[1], qa[2], qa[3]));
+                stg_v4(d + 16, make_uint4(qa[4], qa[5], qa[6], qa[7]));
+            }
+            if (gcol + 1 < cols) {
+                uint8_t* d = codes_col_t + (gcol + 1) * rows + grow;
+                stg_v4(d, make_uint4(qb[0], qb[1], qb[2], qb[3]));
+                stg_v4(d + 16, make_uint4(qb[4], qb[5], qb[6], qb[7]));
+            }
+        }
+        const uint32_t ca = 2 * p, cb = 2 * p + 1;
+        sf_col[(ca & 31u) * 16 + (ca >> 5) * 4 + rb] = static_cast<uint8_t>(sb_a);
+        sf_col[(cb & 31u) * 16 + (cb >> 5) * 4 + rb] = static_cast<uint8_t>(sb_b);
+        __syncthreads();
+        if (layout == DW_SF_TILED) {
+            if (t < 32) {
+                uint4* dst = reinterpret_cast<uint4*>(scales_col + (static_cast<int64_t>(tc) * kt_col + tr) * 512);
+                dst[t] = reinterpret_cast<const uint4*>(sf_col)[t];
+            }
+        } else if (t < 128) {
+            const int64_t gcl = c0 + t, kb0 = static_cast<int64_t>(tr) * 4;
+            if (gcl < cols) {
+#pragma unroll
+                for (int b = 0; b < 4; ++b)
+                    if (kb0 + b < kb_col) scales_col[gcl * kb_col + kb0 + b] = sf_col[(t & 31u) * 16 + (t >> 5) * 4 + b];
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Generic kernel: one thread per scaling block, element strides, ragged last block.
+//   element (r, c) of the operand at x[r*xsr + c*xsc]; blocks of 32 along c; code written at
+//   codes[r*csr + c*csc]; scale for (r, b) flat or tiled.
+// ------------------------------------------------------------------------------------------
+__global__ void mx_quant_generic_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes,
+                                        uint8_t* __restrict__ scales, int64_t op_rows, int64_t op_cols, int64_t xsr,
+                                        int64_t xsc, int64_t csr, int64_t csc, int rule, int layout, int block_major) {
+    const int64_t nb = (op_cols + 31) >> 5, kt = (nb + 3) >> 2;
+    const int64_t total = op_rows * nb;
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        // block_major: consecutive threads take consecutive operand rows (coalesced when xsr == 1)
+        const int64_t r = block_major ? i % op_rows : i / nb;
+        const int64_t b = block_major ? i / op_rows : i % nb;
+        const int64_t c0 = b << 5, c1 = min(c0 + 32, op_cols);
+        uint32_t amax = 0;
+        for (int64_t c = c0; c < c1; ++c) {
+            const uint32_t a = x[r * xsr + c * xsc] & 0x7FFFu;
+            if (a <= 0x7F80u) amax = max(amax, a);
+        }
+        const uint32_t sb = e8m0_from_amax(amax, rule);
+        const float inv = e8m0_inverse(sb);
+        for (int64_t c = c0; c < c1; ++c) {
+            const float f = __uint_as_float(static_cast<uint32_t>(x[r * xsr + c * xsc]) << 16) * inv;
+            codes[r * csr + c * csc] = static_cast<uint8_t>(cvt_e4m3x2(f, 0.0f) & 0xFFu);
+        }
+        scales[layout == DW_SF_TILED ? sf_tiled_offset(r, b, kt) : r * nb + b] = static_cast<uint8_t>(sb);
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Dequantise: codes [rows, cols] (row-wise blocks) -> bf16.  One thread = 16 codes.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t dequant_pair(uint32_t two_codes, float s) {
+    uint32_t h2;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(static_cast<uint16_t>(two_codes)));
+    float lo, hi;
+    asm("{.reg .f16 a, b; mov.b32 {a, b}, %2; cvt.f32.f16 %0, a; cvt.f32.f16 %1, b;}" : "=f"(lo), "=f"(hi) : "r"(h2));
+    lo *= s; hi *= s;
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+
+__global__ void __launch_bounds__(256)
+mx_dequant_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ scales, uint16_t* __restrict__ out,
+                  int64_t rows, int64_t cols, int layout) {
+    const int64_t nb = (cols + 31) >> 5, kt = (nb + 3) >> 2;
+    const bool vec = (cols & 15) == 0;
+    const int64_t cpr = (cols + 15) >> 4, total = rows * cpr;
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t r = i / cpr, c = (i - r * cpr) << 4;
+        const int64_t b = c >> 5;
+        const float s = e8m0_value(scales[layout == DW_SF_TILED ? sf_tiled_offset(r, b, kt) : r * nb + b]);
+        if (vec) {
+            const uint4 q = *reinterpret_cast<const uint4*>(codes + r * cols + c);
+            const uint32_t qs[4] = {q.x, q.y, q.z, q.w};
+            uint32_t o[8];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                o[2 * k] = dequant_pair(qs[k] & 0xFFFFu, s);
+                o[2 * k + 1] = dequant_pair(qs[k] >> 16, s);
+            }
+            uint4* d = reinterpret_cast<uint4*>(out + r * cols + c);
+            d[0] = make_uint4(o[0], o[1], o[2], o[3]);
+            d[1] = make_uint4(o[4], o[5], o[6], o[7]);
+        } else {
+            for (int64_t e = c; e < min(c + 16, cols); ++e)
+                out[r * cols + e] = static_cast<uint16_t>(dequant_pair(codes[r * cols + e], s) & 0xFFFFu);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------
+static inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+static int num_sms() {
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    }
+    return sms;
+}
+
+static int launch_status() { return cudaGetLastError() == cudaSuccess ? DW_OK : DW_ERR_LAUNCH; }
+
+static int quantize_generic(const uint16_t* x, uint8_t* codes, uint8_t* scales, int64_t rows, int64_t cols, int direction,
+                            int rule, int layout, cudaStream_t st) {
+    // operand rows/cols = (rows, cols) for ROW, (cols, rows) for the column directions
+    int64_t orow, ocol, xsr, xsc, csr, csc;
+    int block_major;
+    if (direction == DW_DIR_ROW) {
+        orow = rows; ocol = cols; xsr = cols; xsc = 1; csr = cols; csc = 1; block_major = 0;
+    } else {
+        orow = cols; ocol = rows; xsr = 1; xsc = cols; block_major = 1;
+        if (direction == DW_DIR_COL_T) { csr = rows; csc = 1; } else { csr = 1; csc = cols; }
+    }
+    const int64_t nb = (ocol + 31) / 32, total = orow * nb;
+    const int grid = static_cast<int>(std::min<int64_t>((total + 255) / 256, static_cast<int64_t>(num_sms()) * 16));
+    if (layout == DW_SF_TILED) {
+        const int64_t rt = (orow + 127) / 128, kt = (nb + 3) / 4;
+        mx_sf_pad_kernel<<<static_cast<int>(std::min<int64_t>((rt * kt * 512 + 255) / 256, 4096)), 256, 0, st>>>(
+            scales, orow, nb, rt, kt);
+    }
+    mx_quant_generic_kernel<<<grid, 256, 0, st>>>(x, codes, scales, orow, ocol, xsr, xsc, csr, csc, rule, layout,
+                                                  block_major);
+    return launch_status();
+}
+
+static int quantize_row_fast(const uint16_t* x, uint8_t* codes, uint8_t* scales, int64_t rows, int64_t cols, int rule,
+                             int layout, cudaStream_t st) {
+    const int64_t total_chunks = rows * cols / 16;
+    const uint32_t cpr = static_cast<uint32_t>(cols / 16);
+    const int packed = (cols % 128 == 0) && aligned(scales, 4);
+    const int64_t want = (total_chunks + 511) / 512;
+    const int grid = static_cast<int>(std::min<int64_t>(want, static_cast<int64_t>(num_sms()) * 8));
+    if (layout == DW_SF_TILED && (rows % 128 != 0 || (cols / 32) % 4 != 0)) {
+        const int64_t nb = cols / 32, rt = (rows + 127) / 128, kt = (nb + 3) / 4;
+        mx_sf_pad_kernel<<<static_cast<int>(std::min<int64_t>((rt * kt * 512 + 255) / 256, 4096)), 256, 0, st>>>(
+            scales, rows, nb, rt, kt);
+    }
+    if (aligned(x, 32))
+        mx_quant_row_kernel<true><<<grid, 256, 0, st>>>(x, codes, scales, static_cast<uint32_t>(total_chunks), cpr, rule,
+                                                        layout, packed);
+    else
+        mx_quant_row_kernel<false><<<grid, 256, 0, st>>>(x, codes, scales, static_cast<uint32_t>(total_chunks), cpr, rule,
+                                                         layout, packed);
+    return launch_status();
+}
+
+static bool tile_path_ok(const void* x, int64_t rows, int64_t cols) {
+    const int64_t tiles = ((rows + 127) / 128) * ((cols + 127) / 128);
+    return rows % 32 == 0 && cols % 32 == 0 && aligned(x, 16) && tiles < (1ll << 31);
+}
+
+}  // namespace dw
+
+using namespace dw;
+
+extern "C" DW_API size_t dw_mxfp8_scale_bytes(int64_t rows, int64_t k, int scale_layout) {
+    if (rows <= 0 || k <= 0) return 0;
+    const int64_t nb = (k + 31) / 32;
+    if (scale_layout == DW_SF_TILED) return static_cast<size_t>(((rows + 127) / 128) * ((nb + 3) / 4) * 512);
+    return static_cast<size_t>(rows * nb);
+}
+
+extern "C" DW_API int dw_mxfp8_quantize(const void* x_bf16, void* codes, void* scales, int64_t rows, int64_t cols, int direction,
+                                 int scale_rule, int scale_layout, void* stream) {
+    if (rows < 0 || cols < 0) return DW_ERR_BAD_ARG;
+    if (direction < DW_DIR_ROW || direction > DW_DIR_COL) return DW_ERR_BAD_ARG;
+    if (scale_rule != DW_RULE_OCP_FLOOR && scale_rule != DW_RULE_REF_CEIL) return DW_ERR_BAD_ARG;
+    if (scale_layout != DW_SF_FLAT && scale_layout != DW_SF_TILED) return DW_ERR_BAD_ARG;
+    if (rows == 0 || cols == 0) return DW_OK;  // empty input: nothing to write
+    if (!x_bf16 || !codes || !scales) return DW_ERR_BAD_ARG;
+    if (!aligned(x_bf16, 2)) return DW_ERR_BAD_ARG;
+    if (rows * cols >= (1ll << 35)) return DW_ERR_TOO_LARGE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const uint16_t* x = static_cast<const uint16_t*>(x_bf16);
+    uint8_t* c = static_cast<uint8_t*>(codes);
+    uint8_t* s = static_cast<uint8_t*>(scales);
+
+    if (direction == DW_DIR_ROW && cols % 32 == 0 && aligned(x, 16) && aligned(c, 16))
+        return quantize_row_fast(x, c, s, rows, cols, scale_rule, scale_layout, st);
+    if (direction == DW_DIR_COL_T && tile_path_ok(x, rows, cols) && aligned(c, 16) &&
+        (scale_layout == DW_SF_FLAT || aligned(s, 16))) {
+        const uint32_t tiles_c = static_cast<uint32_t>((cols + 127) / 128);
+        const uint32_t tiles = static_cast<uint32_t>((rows + 127) / 128) * tiles_c;
+        mx_quant_tile_kernel<false, true><<<tiles, 256, 0, st>>>(x, nullptr, nullptr, c, s, rows, cols, tiles_c, scale_rule,
+                                                                 scale_layout);
+        return launch_status();
+    }
+    return quantize_generic(x, c, s, rows, cols, direction, scale_rule, scale_layout, st);
+}
+
+extern "C" DW_API int dw_mxfp8_quantize_both(const void* x_bf16, void* codes_row, void* scales_row, void* codes_col_t,
+                                      void* scales_col, int64_t rows, int64_t cols, int scale_rule, int scale_layout,
+                                      void* stream) {
+    const bool do_row = codes_row != nullptr, do_col = codes_col_t != nullptr;
+    if ((do_row && !scales_row) || (do_col && !scales_col)) return DW_ERR_BAD_ARG;
+    if (!do_row && !do_col) return DW_ERR_BAD_ARG;
+    if (!do_col)
+        return dw_mxfp8_quantize(x_bf16, codes_row, scales_row, rows, cols, DW_DIR_ROW, scale_rule, scale_layout, stream);
+    if (!do_row)
+        return dw_mxfp8_quantize(x_bf16, codes_col_t, scales_col, rows, cols, DW_DIR_COL_T, scale_rule, scale_layout,
+                                 stream);
+    if (rows < 0 || cols < 0) return DW_ERR_BAD_ARG;
+    if (scale_rule != DW_RULE_OCP_FLOOR && scale_rule != DW_RULE_REF_CEIL) return DW_ERR_BAD_ARG;
+    if (scale_layout != DW_SF_FLAT && scale_layout != DW_SF_TILED) return DW_ERR_BAD_ARG;
+    if (rows == 0 || cols == 0) return DW_OK;
+    if (!x_bf16) return DW_ERR_BAD_ARG;
+    if (rows * cols >= (1ll << 35)) return DW_ERR_TOO_LARGE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (tile_path_ok(x_bf16, rows, cols) && aligned(codes_row, 8) && aligned(codes_col_t, 16) &&
+        (scale_layout == DW_SF_FLAT || (aligned(scales_row, 16) && aligned(scales_col, 16)))) {
+        const uint32_t tiles_c = static_cast<uint32_t>((cols + 127) / 128);
+        const uint32_t tiles = static_cast<uint32_t>((rows + 127) / 128) * tiles_c;
+        mx_quant_tile_kernel<true, true><<<tiles, 256, 0, st>>>(
+            static_cast<const uint16_t*>(x_bf16), static_cast<uint8_t*>(codes_row), static_cast<uint8_t*>(scales_row),
+            static_cast<uint8_t*>(codes_col_t), static_cast<uint8_t*>(scales_col), rows, cols, tiles_c, scale_rule,
+            scale_layout);
+        return launch_status();
+    }
+    int rc = dw_mxfp8_quantize(x_bf16, codes_row, scales_row, rows, cols, DW_DIR_ROW, scale_rule, scale_layout, stream);
+    if (rc != DW_OK) return rc;
+    return dw_mxfp8_quantize(x_bf16, codes_col_t, scales_col, rows, cols, DW_DIR_COL_T, scale_rule, scale_layout, stream);
+}
+
+extern "C" DW_API int dw_mxfp8_dequantize(const void* codes, const void* scales, void* out_bf16, int64_t rows, int64_t cols,
+                                   int scale_layout, void* stream) {
+    if (rows < 0 || cols < 0) return DW_ERR_BAD_ARG;
+    if (scale_layout != DW_SF_FLAT && scale_layout != DW_SF_TILED) return DW_ERR_BAD_ARG;
+    if (rows == 0 || cols == 0) return DW_OK;
+    if (!codes || !scales || !out_bf16) return DW_ERR_BAD_ARG;
+    if (cols % 16 == 0 && (!aligned(codes, 16) || !aligned(out_bf16, 16))) return DW_ERR_BAD_ARG;
+    const int64_t total = rows * ((cols + 15) / 16);
+    const int grid = static_cast<int>(std::min<int64_t>((total + 255) / 256, static_cast<int64_t>(num_sms()) * 16));
+    mx_dequant_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t*>(codes), static_cast<const uint8_t*>(scales), static_cast<uint16_t*>(out_bf16), rows,
+        cols, scale_layout);
+    return launch_status();
+}

@@ -1,0 +1,108 @@
+/*
+ * dw_mxfp8.h — C ABI of the B200 (sm_100a) MXFP8 linear path.
+ *
+ * MX quantisation of bf16 matrices (E4M3 payload, one E8M0 power-of-two scale per
+ * 32 elements, row-wise or column-wise) and the block-scaled tcgen05 GEMM that
+ * consumes those operands.  Plain pointers and sizes only; every pointer is a
+ * DEVICE pointer unless stated; `stream` is a cudaStream_t passed as void*.
+ * All calls are asynchronous on `stream`, allocate nothing, and borrow the caller's
+ * buffers.  Return value: DW_OK or a negative DW_ERR_* code (the convention of the
+ * reference's only C ABI, dw_fmha_bf16_forward, csrc/fmha_bridge_min/fmha_bridge_min.cu:39-46).
+ *
+ * Each entry point names the reference interface it replaces (path:line inside the
+ * reference project).
+ */
+#ifndef DW_MXFP8_H_
+#define DW_MXFP8_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+/* symbol visibility: the library is built with -fvisibility=hidden */
+#if defined(DW_BUILDING_LIB) && defined(__GNUC__)
+#define DW_API __attribute__((visibility("default")))
+#else
+#define DW_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DW_OK                 0
+#define DW_ERR_BAD_ARG       (-1)  /* null pointer, bad shape, misaligned pointer, bad enum */
+#define DW_ERR_ARCH          (-2)  /* current device is not compute capability 10.x */
+#define DW_ERR_LAUNCH        (-3)  /* CUDA runtime / driver error at launch or descriptor encode */
+#define DW_ERR_DEVICE_STATUS (-4)  /* a kernel recorded a non-zero status word (bounded wait expired) */
+#define DW_ERR_TOO_LARGE     (-5)  /* problem exceeds a fixed capacity of the entry point */
+
+/* direction of the 32-element scaling blocks for a row-major [rows, cols] input */
+#define DW_DIR_ROW    0  /* blocks along cols; codes [rows, cols]; scales for [rows, cols/32]           */
+#define DW_DIR_COL_T  1  /* blocks along rows; codes TRANSPOSED [cols, rows]; scales for [cols, rows/32] */
+#define DW_DIR_COL    2  /* blocks along rows; codes in the input's layout [rows, cols]; scales as COL_T */
+
+#define DW_RULE_OCP_FLOOR 0  /* scale = 2^(floor(log2 amax) - 8)                                     */
+#define DW_RULE_REF_CEIL  1  /* scale = 2^ceil(log2(amax/448)), csrc/mxfp8_quantization.cu:109-114   */
+
+#define DW_SF_FLAT   0  /* scales[r * ceil(K/32) + kb], one byte each                                 */
+#define DW_SF_TILED  1  /* 512-byte tiles of 128 rows x 4 k-blocks, the tcgen05 scale-factor layout:
+                           tile (r/128, kb/4) at ((r/128)*ceil(KB/4) + kb/4)*512, inside it
+                           (r%32)*16 + ((r/32)%4)*4 + kb%4.  Padding bytes are written as 127.       */
+
+/* Library / device probes. */
+int         dw_mxfp8_abi_version(void);
+int         dw_mxfp8_device_supported(int device);      /* 1 if compute capability 10.x */
+const char *dw_mxfp8_error_string(int code);
+
+/* Bytes of the scale buffer for an operand with `rows` rows and `k` elements along its
+ * scaled dimension.  Replaces get_mxfp8_scale_layout_info, csrc/mxfp8_quantization.cu:287-298. */
+size_t dw_mxfp8_scale_bytes(int64_t rows, int64_t k, int scale_layout);
+
+/* MX quantisation of a row-major bf16 [rows, cols] matrix.
+ * Replaces quantize_to_mxfp8_bf16 (csrc/mxfp8_quantization.cu:229-246; row_major=true is
+ * DW_DIR_ROW, row_major=false is DW_DIR_COL) and gives transpose_quantize_to_mxfp8_kernel
+ * (:216-226, an empty body in the reference) its function as DW_DIR_COL_T.
+ * codes: uint8 E4M3 (fn); scales: uint8 E8M0.  x and codes 16-byte aligned. */
+int dw_mxfp8_quantize(const void *x_bf16, void *codes, void *scales, int64_t rows, int64_t cols,
+                      int direction, int scale_rule, int scale_layout, void *stream);
+
+/* One read of x, both operand forms: row-wise (codes_row [rows, cols]) and column-wise
+ * transposed (codes_col_t [cols, rows]).  Either output pair may be NULL.
+ * Counterpart of MicroscaleManager::transpose_mxfp8 (csrc/cutlass_kernels.cpp:412-424, empty). */
+int dw_mxfp8_quantize_both(const void *x_bf16, void *codes_row, void *scales_row, void *codes_col_t,
+                           void *scales_col, int64_t rows, int64_t cols, int scale_rule,
+                           int scale_layout, void *stream);
+
+/* codes [rows, cols] (row-wise blocks) + scales -> bf16 [rows, cols].
+ * Replaces dequantize_from_mxfp8_bf16, csrc/mxfp8_quantization.cu:267-284. */
+int dw_mxfp8_dequantize(const void *codes, const void *scales, void *out_bf16, int64_t rows,
+                        int64_t cols, int scale_layout, void *stream);
+
+/* D[M,N] = bf16(alpha * A[M,K] . B[N,K]^T + beta * D + bias[N]).
+ * A and B are E4M3 codes, both K-major (contraction dim contiguous), with DW_SF_TILED scales;
+ * bias (bf16 [N]) may be NULL; with beta == 0 the previous content of D is not read.
+ * Replaces launch_blackwell_mxfp8_gemm (csrc/blackwell_gemm_kernel.cu:103-156) and the MXFP8
+ * branch of BlackwellGemmKernel::gemm (csrc/cutlass_kernels.cpp:173-204), which allocated and
+ * freed two scale buffers per call and ran a bf16 cuBLAS GEMM.
+ * K % 32 == 0; a_codes, b_codes, d 16-byte aligned.  workspace: dw_mxfp8_gemm_workspace bytes
+ * (may be NULL when that is 0).  status_word: optional device int32, set non-zero by the
+ * kernel if a bounded wait expires (then read it with dw_mxfp8_check_status). */
+int dw_mxfp8_gemm(const void *a_codes, const void *a_sf, const void *b_codes, const void *b_sf,
+                  void *d_bf16, const void *bias_bf16, int64_t M, int64_t N, int64_t K, float alpha,
+                  float beta, void *workspace, size_t workspace_bytes, void *status_word, void *stream);
+
+/* Replaces BlackwellGemmKernel::get_workspace_size, csrc/cutlass_kernels.cpp:229-231. */
+size_t dw_mxfp8_gemm_workspace(int64_t M, int64_t N, int64_t K);
+
+/* Synchronises `stream`, reads the status word; DW_OK or DW_ERR_DEVICE_STATUS. */
+int dw_mxfp8_check_status(const void *status_word, void *stream);
+
+/* Selects the GEMM kernel variant for later dw_mxfp8_gemm calls in this process
+ * (0 = automatic).  Counterpart of BlackwellGemmKernel::set_cluster_shape /
+ * enable_tmem_residency, csrc/cutlass_kernels.cpp:265-272 (flags the reference stores and ignores). */
+int dw_mxfp8_gemm_set_variant(int variant);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DW_MXFP8_H_ */
