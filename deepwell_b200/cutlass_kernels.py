@@ -1,0 +1,244 @@
+"""Drop-in for the reference's extension module ``deepwell.cutlass_kernels``.
+
+Same classes, method names and argument meaning as the pybind11 module defined in
+csrc/python_bindings.cpp:258-319 of the reference (BlackwellGemmKernel,
+BlackwellGroupedGemmKernel, MicroscaleManager, PrecisionType, profile_kernel), bound to
+the sm_100a kernels of this package through the C ABI (include/dw_mxfp8.h).
+
+Differences from the reference, all deliberate:
+  * ``dtype="mxfp8"`` really quantises both operands to MXFP8 and runs the block-scaled
+    tcgen05 GEMM (the reference runs a bf16 cuBLAS GEMM there, csrc/cutlass_kernels.cpp:173-204);
+  * ``quantize_mxfp8`` returns ``torch.float8_e4m3fn`` codes and E8M0 ``uint8`` scales instead
+    of truncated ``int8`` and ``float32`` (csrc/python_bindings.cpp:211-214);
+  * ``b`` is honoured as a [K, N] tensor of any stride; the reference reads the storage of a
+    transposed view as if it were contiguous (csrc/python_bindings.cpp:50-53, :100);
+  * ``c`` takes part in ``alpha*A@B + beta*C`` as in the reference's Python module
+    (src/deepwell/cutlass_kernels.py:28-32); the compiled reference ignores it;
+  * no CPU path: CPU tensors raise, as the reference's TORCH_CHECKs do (:82-85).
+"""
+from __future__ import annotations
+
+import enum
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from . import _native as nv
+
+# The reference's pure-Python stand-in sets this flag to True; a real extension has no such flag.
+CUTLASS_PYTHON_FALLBACK = False
+
+_DTYPE_STRINGS = ("fp32", "fp16", "bf16", "mxfp8", "nvfp4", "mxfp4")   # python_bindings.cpp:56-68
+_TORCH_DTYPES = {"fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16}
+
+
+class PrecisionType(enum.IntEnum):
+    """csrc/cutlass_kernels.h:28-40, exported at csrc/python_bindings.cpp:262-272."""
+    FP32 = 0
+    FP16 = 1
+    BF16 = 2
+    FP8_E4M3 = 3
+    FP8_E5M2 = 4
+    MXFP8 = 5
+    NVFP4 = 6
+    MXFP4 = 7
+    INT8 = 8
+    INT4 = 9
+
+
+# Dense peaks used by get_expected_tflops (nominal B200 figures, TFLOP/s).
+_NOMINAL_PEAK = {"fp32": 80.0, "fp16": 2250.0, "bf16": 2250.0, "mxfp8": 4500.0, "nvfp4": 9000.0, "mxfp4": 9000.0}
+
+
+def _check_2d_cuda(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"Input {name} must be on CUDA")
+    if t.dim() != 2:
+        raise RuntimeError(f"Input {name} must be 2D")
+
+
+def mxfp8_gemm_bf16(a: torch.Tensor, b_kn: torch.Tensor, c: Optional[torch.Tensor] = None, alpha: float = 1.0,
+                    beta: float = 0.0, bias: Optional[torch.Tensor] = None, scale_rule: int = nv.RULE_OCP_FLOOR) -> torch.Tensor:
+    """alpha * A[M,K] @ B[K,N] + beta * C (+ bias) with both operands quantised to MXFP8 along K."""
+    a = a.to(torch.bfloat16)
+    b_kn = b_kn.to(torch.bfloat16)
+    a_codes, a_sf = nv.quantize(a, nv.DIR_ROW, scale_rule, nv.SF_TILED)
+    if b_kn.stride(0) == 1 and b_kn.stride(1) == b_kn.shape[0]:
+        # a transposed view of an [N, K] weight: its storage already is the K-major operand
+        b_codes, b_sf = nv.quantize(b_kn.t(), nv.DIR_ROW, scale_rule, nv.SF_TILED)
+    else:
+        b_codes, b_sf = nv.quantize(b_kn.contiguous(), nv.DIR_COL_T, scale_rule, nv.SF_TILED)
+    out = None
+    if beta != 0.0:
+        if c is None:
+            raise RuntimeError("beta != 0 needs the C operand")
+        out = c.to(torch.bfloat16).contiguous().clone()
+    return nv.gemm(a_codes, a_sf, b_codes, b_sf, out=out, bias=bias, alpha=alpha, beta=beta)
+
+
+class BlackwellGemmKernel:
+    """csrc/python_bindings.cpp:35-113 (PyBlackwellGemmKernel)."""
+
+    def __init__(self) -> None:
+        nv.load()                      # fail now, loudly, if the native library is not built
+        self.m = self.n = self.k = 0
+        self.dtype = "bf16"
+        self.use_microscaling = False
+        self.block_size = 32
+        self.tmem_residency = True
+        self.cluster_shape = (2, 1)
+        self.initialized = False
+
+    def initialize(self, m: int, n: int, k: int, dtype: str = "bf16", use_microscaling: bool = False,
+                   block_size: int = 32) -> None:
+        if dtype not in _DTYPE_STRINGS:
+            dtype = "fp16"             # the reference's default for unknown strings (:56)
+        if dtype in ("nvfp4", "mxfp4"):
+            raise RuntimeError(f"dtype {dtype!r}: only the MXFP8 block-scaled kernel is built in this package")
+        if dtype == "mxfp8" and block_size != 32:
+            raise RuntimeError("MXFP8 uses 32-element scaling blocks")
+        self.m, self.n, self.k = int(m), int(n), int(k)
+        self.dtype, self.use_microscaling, self.block_size = dtype, bool(use_microscaling), int(block_size)
+        self.initialized = True
+
+    def gemm(self, a: torch.Tensor, b: torch.Tensor, c: Optional[torch.Tensor] = None, alpha: float = 1.0,
+             beta: float = 0.0) -> torch.Tensor:
+        _check_2d_cuda(a, "A")
+        _check_2d_cuda(b, "B")
+        if not self.initialized:
+            raise RuntimeError("initialize() must be called before gemm()")
+        if a.shape[0] != self.m or a.shape[1] != self.k or b.shape[0] != self.k or b.shape[1] != self.n:
+            raise RuntimeError(f"operand shapes {tuple(a.shape)} x {tuple(b.shape)} do not match the initialised "
+                               f"problem {self.m}x{self.n}x{self.k}")
+        if self.dtype == "mxfp8":
+            out = mxfp8_gemm_bf16(a, b, c, alpha, beta)
+            return out if a.dtype == torch.bfloat16 else out.to(a.dtype)
+        # plain library GEMM for the unquantised dtypes (the reference calls cuBLAS here, :143-172)
+        td = _TORCH_DTYPES[self.dtype]
+        d = torch.matmul(a.to(td), b.to(td))
+        if alpha != 1.0:
+            d = d * alpha
+        if c is not None and beta != 0.0:
+            d = d + beta * c.to(td)
+        return d
+
+    def enable_tmem_residency(self, enable: bool = True) -> None:
+        # the accumulator always lives in TMEM in this kernel; the flag is kept for API parity
+        self.tmem_residency = bool(enable)
+
+    def set_cluster_shape(self, m: int, n: int) -> None:
+        """(2, 1) selects the CTA-pair kernel (cta_group::2), (1, 1) the single-CTA kernel."""
+        if (m, n) not in ((1, 1), (2, 1)):
+            raise RuntimeError("supported cluster shapes: (1, 1) and (2, 1)")
+        self.cluster_shape = (int(m), int(n))
+        nv.set_gemm_variant(3 if m == 2 else 2)
+
+    def get_expected_tflops(self) -> float:
+        """Nominal dense peak of the selected precision (csrc/cutlass_kernels.cpp:233-263 kept hard-coded
+        guesses; these are the published B200 dense figures) scaled by the same size heuristic."""
+        peak = _NOMINAL_PEAK.get(self.dtype, 1000.0)
+        eff = 0.8 if float(self.m) * self.n * self.k >= 1e9 else 0.5
+        return peak * eff
+
+
+class BlackwellGroupedGemmKernel:
+    """csrc/python_bindings.cpp:116-194: one GEMM per group, same kernel, launched back to back."""
+
+    def __init__(self) -> None:
+        nv.load()
+        self.problem_sizes: List[Tuple[int, int, int]] = []
+        self.dtype = "fp16"
+        self.use_microscaling = False
+        self.expert_parallel = True
+
+    def initialize(self, problem_sizes: Sequence[Tuple[int, int, int]], dtype: str = "fp16",
+                   use_microscaling: bool = False) -> None:
+        self.problem_sizes = [tuple(int(v) for v in p) for p in problem_sizes]
+        self.dtype = dtype if dtype in _DTYPE_STRINGS else "fp16"
+        self.use_microscaling = bool(use_microscaling)
+
+    def grouped_gemm(self, a_list: Sequence[torch.Tensor], b_list: Sequence[torch.Tensor], alpha: float = 1.0,
+                     beta: float = 0.0) -> List[torch.Tensor]:
+        if len(a_list) != len(b_list):
+            raise RuntimeError("a_list and b_list differ in length")
+        outs = []
+        for a, b in zip(a_list, b_list):
+            if not a.is_cuda or not b.is_cuda:
+                raise RuntimeError("All inputs must be on CUDA")
+            if self.dtype == "mxfp8":
+                o = mxfp8_gemm_bf16(a, b, None, alpha, 0.0)
+                outs.append(o if a.dtype == torch.bfloat16 else o.to(a.dtype))
+            else:
+                outs.append(alpha * torch.matmul(a, b))
+        return outs
+
+    def set_expert_parallel_strategy(self, enable: bool) -> None:
+        self.expert_parallel = bool(enable)
+
+
+class MicroscaleManager:
+    """csrc/python_bindings.cpp:197-241 (PyMicroscaleManager)."""
+
+    def __init__(self) -> None:
+        nv.load()
+
+    def quantize_mxfp8(self, input: torch.Tensor, block_size: int = 32, direction: str = "row",
+                       scale_layout: str = "flat", scale_rule: str = "ocp_floor"):
+        """-> (codes float8_e4m3fn, scales uint8 E8M0).
+
+        The two-argument call keeps the reference's meaning: blocks of 32 along the last
+        dimension, codes shaped like the input, scales flat with one entry per block
+        (csrc/python_bindings.cpp:206-214).  ``direction="col"`` scales along dim 0 and returns
+        the payload transposed; ``scale_layout="tcgen05"`` returns the scales in the 512-byte
+        tile layout the GEMM reads.
+        """
+        if not input.is_cuda:
+            raise RuntimeError("Input must be on CUDA")
+        if block_size != 32:
+            raise RuntimeError("MXFP8 uses 32-element scaling blocks")
+        x = input.to(torch.bfloat16)
+        x2 = x.reshape(-1, x.shape[-1]) if x.dim() != 2 else x
+        codes, scales = nv.quantize(x2, nv.DIRECTIONS[direction], nv.RULES[scale_rule], nv.LAYOUTS[scale_layout])
+        if nv.DIRECTIONS[direction] == nv.DIR_ROW and input.dim() != 2:
+            codes = codes.view(input.shape)
+        if nv.LAYOUTS[scale_layout] == nv.SF_FLAT and direction == "row" and input.dim() != 2:
+            scales = scales.reshape(-1)
+        return codes, scales
+
+    def dequantize_mxfp8(self, input: torch.Tensor, scales: torch.Tensor, block_size: int = 32,
+                         scale_layout: str = "flat") -> torch.Tensor:
+        """codes + scales -> bf16 (the kernel of the reference writes bf16 as well,
+        csrc/mxfp8_quantization.cu:278, into a tensor its binding declared fp16, :230-232)."""
+        if not input.is_cuda:
+            raise RuntimeError("Input must be on CUDA")
+        if not scales.is_cuda:
+            raise RuntimeError("Scales must be on CUDA")
+        if block_size != 32:
+            raise RuntimeError("MXFP8 uses 32-element scaling blocks")
+        codes2 = input.reshape(-1, input.shape[-1]) if input.dim() != 2 else input
+        out = nv.dequantize(codes2.view(torch.uint8), scales.reshape(-1).view(torch.uint8), nv.LAYOUTS[scale_layout])
+        return out.view(input.shape)
+
+
+def profile_kernel(kernel: BlackwellGemmKernel, warmup_iterations: int = 10, profile_iterations: int = 100) -> dict:
+    """Times kernel.gemm on random operands with CUDA events (the reference returns constants,
+    csrc/python_bindings.cpp:244-255)."""
+    if not kernel.initialized:
+        raise RuntimeError("initialize() must be called before profile_kernel()")
+    dev = torch.device("cuda", torch.cuda.current_device())
+    td = torch.bfloat16 if kernel.dtype == "mxfp8" else _TORCH_DTYPES[kernel.dtype]
+    a = torch.randn(kernel.m, kernel.k, device=dev, dtype=td)
+    b = torch.randn(kernel.k, kernel.n, device=dev, dtype=td)
+    for _ in range(max(1, warmup_iterations)):
+        kernel.gemm(a, b)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(max(1, profile_iterations)):
+        kernel.gemm(a, b)
+    stop.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(stop) / max(1, profile_iterations)
+    flops = 2.0 * kernel.m * kernel.n * kernel.k
+    bytes_moved = (kernel.m * kernel.k + kernel.k * kernel.n + kernel.m * kernel.n) * a.element_size()
+    return {"runtime_ms": ms, "tflops": flops / ms / 1e9, "memory_bandwidth_gb_s": bytes_moved / ms / 1e6,
+            "expected_tflops": kernel.get_expected_tflops()}

@@ -68,7 +68,9 @@ def f32_to_bf16_bits(x: np.ndarray) -> np.ndarray:
 def e4m3_encode(x: np.ndarray) -> np.ndarray:
     """float32 -> E4M3 (fn) code, RNE, saturating to +-448 (0x7E); NaN -> 0x7F.
 
-    Same result as the hardware `cvt.rn.satfinite.e4m3x2.f32`.
+    Same result as the hardware `cvt.rn.satfinite.e4m3x2.f32`, which writes the canonical
+    NaN 0x7F whatever the sign of the NaN input (measured on B200; torch's CPU cast keeps
+    the sign, the only place the two differ).
     """
     x = np.ascontiguousarray(x, dtype=np.float32)
     u = x.view(np.uint32)
@@ -89,8 +91,8 @@ def e4m3_encode(x: np.ndarray) -> np.ndarray:
     code = np.where(small, code_s, code_n)
     sat = (~small) & (ru.view(np.float32) > np.float32(E4M3_MAX))
     code = np.where(sat, 0x7E, code)
-    code = np.where(nan, 0x7F, code)
-    return (code.astype(np.uint8) | sign)
+    out = code.astype(np.uint8) | sign
+    return np.where(nan, np.uint8(0x7F), out)
 
 
 _E4M3_TABLE = None

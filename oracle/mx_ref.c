@@ -42,12 +42,12 @@ static inline uint16_t f32_bf16(float f) {
     return (uint16_t)((u + 0x7FFFu + ((u >> 16) & 1u)) >> 16);
 }
 
-/* float -> E4M3 code, RNE, saturating at +-448, NaN -> 0x7F */
+/* float -> E4M3 code, RNE, saturating at +-448, NaN (either sign) -> 0x7F as the hardware cvt does */
 static inline uint8_t e4m3_encode(float x) {
     uint32_t u = f32_bits(x);
     uint8_t sign = (uint8_t)((u >> 24) & 0x80);
     uint32_t au = u & 0x7FFFFFFFu;
-    if (au > 0x7F800000u) return (uint8_t)(sign | 0x7F);
+    if (au > 0x7F800000u) return (uint8_t)0x7F;
     if (au < 0x3C800000u) {                       /* |x| < 2^-6: multiples of 2^-9 */
         float a = bits_f32(au);
         return (uint8_t)(sign | (uint8_t)nearbyintf(a * 512.0f));

@@ -1,0 +1,38 @@
+import os
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.abspath(os.path.join(os.path.dirname(__file__), ".."))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+GOLDEN = os.path.join(ROOT, "tests", "golden")
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a B200 (sm_100a) GPU; the parity tests proper")
+
+
+@pytest.fixture(scope="session")
+def native_lib():
+    """Builds (if stale) and loads the C-ABI library."""
+    from deepwell_b200 import _build, _native
+    _build.build()
+    return _native.load()
+
+
+@pytest.fixture(scope="session")
+def golden():
+    return {name: np.load(os.path.join(GOLDEN, name + ".npz")) for name in ("kat_quant", "config1", "ref_gemm")}
+
+
+def config1_inputs():
+    """BASELINE config 1: X [2048,4096] N(0,1) with 1% entries x50, W [4096,4096] N(0,0.02), seed 1234."""
+    import torch
+    g = torch.Generator("cpu").manual_seed(1234)
+    X = torch.randn(2048, 4096, generator=g)
+    mask = torch.rand(2048, 4096, generator=g) < 0.01
+    X[mask] *= 50
+    W = torch.randn(4096, 4096, generator=g) * 0.02
+    return X.bfloat16(), W.bfloat16()

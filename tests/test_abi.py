@@ -1,0 +1,76 @@
+"""CPU tests of the drop-in boundary: the C-ABI library loads, exports every symbol the header
+declares, and rejects bad arguments before touching a GPU."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from conftest import ROOT
+
+
+def header_functions():
+    text = open(os.path.join(ROOT, "include", "dw_mxfp8.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(dw_mxfp8_\w+)\s*\(", text)))
+
+
+def test_header_and_library_agree(native_lib):
+    from deepwell_b200 import _native as nv
+    names = header_functions()
+    assert len(names) >= 11
+    for n in names:
+        assert hasattr(native_lib, n), f"{n} declared in include/dw_mxfp8.h but not exported"
+    assert sorted(nv.ABI_SYMBOLS) == names
+    assert native_lib.dw_mxfp8_abi_version() == 1
+
+
+def test_scale_bytes(native_lib):
+    from deepwell_b200 import _native as nv
+    from oracle import mx_oracle as o
+    for rows, k in [(1, 32), (128, 128), (129, 4096), (300, 1000), (16384, 14336)]:
+        assert nv.scale_bytes(rows, k, nv.SF_FLAT) == rows * ((k + 31) // 32)
+        assert nv.scale_bytes(rows, k, nv.SF_TILED) == o.sf_tiled_size(rows, (k + 31) // 32)
+    assert nv.scale_bytes(0, 128, nv.SF_TILED) == 0
+
+
+def test_bad_arguments_are_rejected_without_a_gpu(native_lib):
+    L = native_lib
+    buf = ctypes.create_string_buffer(4096)
+    p = ctypes.addressof(buf)
+    p16 = (p + 15) & ~15
+    assert L.dw_mxfp8_quantize(p16, p16, p16, -1, 32, 0, 0, 0, None) == -1          # negative shape
+    assert L.dw_mxfp8_quantize(p16, p16, p16, 4, 32, 7, 0, 0, None) == -1           # bad direction
+    assert L.dw_mxfp8_quantize(p16, p16, p16, 4, 32, 0, 5, 0, None) == -1           # bad rule
+    assert L.dw_mxfp8_quantize(p16, p16, p16, 4, 32, 0, 0, 9, None) == -1           # bad layout
+    assert L.dw_mxfp8_quantize(None, p16, p16, 4, 32, 0, 0, 0, None) == -1          # null input
+    assert L.dw_mxfp8_quantize(p16, p16, p16, 0, 32, 0, 0, 0, None) == 0            # empty: nothing to do
+    assert L.dw_mxfp8_quantize(p16, p16, p16, 1 << 20, 1 << 20, 0, 0, 0, None) == -5  # over capacity
+    assert L.dw_mxfp8_quantize_both(p16, None, None, None, None, 4, 32, 0, 0, None) == -1
+    assert L.dw_mxfp8_dequantize(p16, p16, p16, 4, 32, 3, None) == -1
+    assert L.dw_mxfp8_gemm(p16, p16, p16, p16, p16, None, 128, 128, 100, 1.0, 0.0, None, 0, None, None) == -1   # K % 32
+    assert L.dw_mxfp8_gemm(p16 + 1, p16, p16, p16, p16, None, 128, 128, 128, 1.0, 0.0, None, 0, None, None) == -1  # alignment
+    assert L.dw_mxfp8_gemm(None, p16, p16, p16, p16, None, 128, 128, 128, 1.0, 0.0, None, 0, None, None) == -1
+    assert L.dw_mxfp8_gemm(p16, p16, p16, p16, p16, None, 0, 128, 128, 1.0, 0.0, None, 0, None, None) == 0        # empty
+    assert L.dw_mxfp8_gemm_set_variant(99) == -1
+    assert L.dw_mxfp8_gemm_set_variant(0) == 0
+    assert L.dw_mxfp8_gemm_workspace(16384, 4096, 4096) == 0
+    for code in (0, -1, -2, -3, -4, -5, -77):
+        assert len(L.dw_mxfp8_error_string(code)) > 0
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    from deepwell_b200 import _native as nv
+    monkeypatch.setattr(nv, "_lib", None)
+    monkeypatch.setattr(nv, "LIB_PATH", str(tmp_path / "nope.so"))
+    with pytest.raises(nv.NativeLibraryError):
+        nv.load()
+
+
+def test_product_does_not_import_the_oracle():
+    pkg = os.path.join(ROOT, "deepwell_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert "oracle" not in text.replace("the oracle", ""), f"{f} refers to the oracle package"

@@ -1,0 +1,156 @@
+"""GPU parity tests of the block-scaled GEMM (through the C ABI) against the oracle's
+fp32-accumulated dequantised matmul.
+
+Tolerance (bf16 output, accumulation order differs from the CPU's): |got - ref| <= 1e-2 * max(|ref|, mean|ref|)."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import config1_inputs
+from oracle import mx_oracle as o
+
+pytestmark = pytest.mark.gpu
+RTOL = 1e-2
+VARIANTS = [1, 2, 3, 4]      # 1 CTA x BN128, 1 CTA x BN256, CTA pair x BN256, CTA pair x BN128
+
+
+@pytest.fixture(scope="module")
+def nv(native_lib):
+    from deepwell_b200 import _native
+    assert torch.cuda.is_available() and native_lib.dw_mxfp8_device_supported(0) == 1
+    yield _native
+    _native.set_gemm_variant(0)
+
+
+def host(t):
+    return t.view(torch.uint8).cpu().numpy()
+
+
+def assert_close(got, ref):
+    got, ref = got.double(), ref.double()
+    floor = ref.abs().mean()
+    bad = (got - ref).abs() > RTOL * torch.maximum(ref.abs(), floor)
+    assert not torch.isnan(got).any()
+    assert bad.sum().item() == 0, f"{bad.sum().item()} of {bad.numel()} outside tolerance; max err {(got-ref).abs().max().item()}"
+
+
+def oracle_gemm(nv, x, w, alpha=1.0, beta=0.0, d0=None, bias=None, rows=None, cols=None):
+    """fp32-accumulated product of the dequantised operands (optionally a row/column sample)."""
+    xc, xs = nv.quantize(x, nv.DIR_ROW, 0, nv.SF_FLAT)
+    wc, ws = nv.quantize(w, nv.DIR_ROW, 0, nv.SF_FLAT)
+    xc, xs, wc, ws = host(xc), host(xs), host(wc), host(ws)
+    if rows is not None:
+        xc, xs = xc[rows], xs[rows]
+    if cols is not None:
+        wc, ws = wc[cols], ws[cols]
+    a = torch.from_numpy(o.dequantize_rowwise(xc, xs))
+    b = torch.from_numpy(o.dequantize_rowwise(wc, ws))
+    y = alpha * (a @ b.t())
+    if beta != 0.0:
+        y = y + beta * d0.float().cpu()
+    if bias is not None:
+        y = y + bias.float().cpu()[None, :]
+    return y
+
+
+def run(nv, M, N, K, alpha=1.0, beta=0.0, use_bias=False, seed=0):
+    g = torch.Generator("cpu").manual_seed(seed + M * 31 + N * 17 + K)
+    x = torch.randn(M, K, generator=g)
+    x[torch.rand(M, K, generator=g) < 0.01] *= 50
+    x = x.bfloat16().cuda()
+    w = (torch.randn(N, K, generator=g) * 0.02).bfloat16().cuda()
+    d0 = torch.randn(M, N, generator=g).bfloat16().cuda() if beta != 0.0 else None
+    bias = torch.randn(N, generator=g).bfloat16().cuda() if use_bias else None
+    xc, xs = nv.quantize(x, nv.DIR_ROW, 0, nv.SF_TILED)
+    wc, ws = nv.quantize(w, nv.DIR_ROW, 0, nv.SF_TILED)
+    out = nv.gemm(xc, xs, wc, ws, out=None if d0 is None else d0.clone(), bias=bias, alpha=alpha, beta=beta)
+    nv.check_status()
+    assert_close(out.cpu(), oracle_gemm(nv, x, w, alpha, beta, d0, bias))
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+@pytest.mark.parametrize("shape", [(128, 128, 128), (256, 256, 256), (128, 256, 32), (512, 768, 1024), (300, 200, 160),
+                                   (1000, 520, 96), (1, 32, 32), (129, 257 * 8, 4096 + 32), (2048, 512, 2048)])
+def test_shapes(nv, variant, shape):
+    nv.set_gemm_variant(variant)
+    run(nv, *shape)
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+def test_alpha_beta_bias(nv, variant):
+    nv.set_gemm_variant(variant)
+    run(nv, 384, 640, 512, alpha=0.5, beta=2.0, use_bias=True)
+    run(nv, 200, 104, 64, alpha=-1.25, beta=0.0, use_bias=True)       # N % 8 == 0 but ragged tiles
+    run(nv, 96, 100, 64, alpha=1.0, beta=1.0, use_bias=False)          # N % 8 != 0: scalar store path
+
+
+@pytest.mark.parametrize("variant", [0, 3])
+def test_config1_full(nv, golden, variant):
+    """BASELINE config 1 in full: X [2048,4096] . W [4096,4096]^T, and the golden 64x64 corner."""
+    nv.set_gemm_variant(variant)
+    X, W = config1_inputs()
+    x, w = X.cuda(), W.cuda()
+    xc, xs = nv.quantize(x, nv.DIR_ROW, 0, nv.SF_TILED)
+    wc, ws = nv.quantize(w, nv.DIR_ROW, 0, nv.SF_TILED)
+    y = nv.gemm(xc, xs, wc, ws)
+    nv.check_status()
+    assert_close(y.cpu(), oracle_gemm(nv, x, w))
+    corner = torch.from_numpy(o.bf16_bits_to_f32(golden["config1"]["y_corner"]))
+    assert_close(y[:64, :64].cpu(), corner)
+
+
+@pytest.mark.parametrize("variant", [0, 3])
+@pytest.mark.parametrize("M,N,K", [(8192, 3072, 768), (8192, 768, 3072), (16384, 6144, 4096), (16384, 4096, 14336)])
+def test_model_shapes_sampled(nv, variant, M, N, K):
+    """GPT-2-small and Llama-3-8B linear shapes at full size: 96 sampled rows x 160 sampled
+    columns against the oracle, plus linearity in alpha (a size-independent property)."""
+    nv.set_gemm_variant(variant)
+    g = torch.Generator("cuda").manual_seed(3456)
+    x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(N, K, device="cuda", generator=g) * 0.02).bfloat16()
+    xc, xs = nv.quantize(x, nv.DIR_ROW, 0, nv.SF_TILED)
+    wc, ws = nv.quantize(w, nv.DIR_ROW, 0, nv.SF_TILED)
+    y = nv.gemm(xc, xs, wc, ws)
+    nv.check_status()
+    gi = torch.Generator().manual_seed(7)
+    rows = torch.cat([torch.tensor([0, M - 1]), torch.randint(0, M, (94,), generator=gi)])
+    cols = torch.cat([torch.tensor([0, N - 1]), torch.randint(0, N, (158,), generator=gi)])
+    ref = oracle_gemm(nv, x, w, rows=rows.numpy(), cols=cols.numpy())
+    assert_close(y[rows.cuda()][:, cols.cuda()].cpu(), ref)
+    y2 = nv.gemm(xc, xs, wc, ws, alpha=2.0)
+    assert torch.equal((y.float() * 2).bfloat16().view(torch.int16), y2.view(torch.int16))   # exact: power-of-two alpha
+
+
+def test_backward_operand_forms(nv):
+    """dgrad and wgrad through column-wise (transposed) operands: contraction over N and over M."""
+    nv.set_gemm_variant(0)
+    M, N, K = 512, 384, 256
+    g = torch.Generator("cpu").manual_seed(11)
+    x = torch.randn(M, K, generator=g).bfloat16().cuda()
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16().cuda()
+    dy = torch.randn(M, N, generator=g).bfloat16().cuda()
+    dyr, dyrs, dyc, dycs = nv.quantize_both(dy, 0, nv.SF_TILED)
+    _, _, wct, wcs = nv.quantize_both(w, 0, nv.SF_TILED)
+    _, _, xct, xcs = nv.quantize_both(x, 0, nv.SF_TILED)
+    dx = nv.gemm(dyr, dyrs, wct, wcs)            # [M, K], contraction N
+    dw = nv.gemm(dyc, dycs, xct, xcs)            # [N, K], contraction M
+    nv.check_status()
+    ref_dx = oracle_gemm(nv, dy, w.t().contiguous())
+    ref_dw = oracle_gemm(nv, dy.t().contiguous(), x.t().contiguous())
+    assert_close(dx.cpu(), ref_dx)
+    assert_close(dw.cpu(), ref_dw)
+
+
+def test_zero_and_nan_free_padding(nv):
+    """Ragged M/N/K tiles: out-of-range operand rows are zero-filled and padding scales are finite,
+    so no NaN leaks into valid outputs; an all-zero operand gives exact zeros."""
+    nv.set_gemm_variant(0)
+    x = torch.zeros(130, 96, dtype=torch.bfloat16, device="cuda")
+    w = torch.randn(70, 96, device="cuda").bfloat16()
+    xc, xs = nv.quantize(x, nv.DIR_ROW, 0, nv.SF_TILED)
+    wc, ws = nv.quantize(w, nv.DIR_ROW, 0, nv.SF_TILED)
+    # the caller's scale buffers may hold anything beyond what the quantiser wrote: poison D first
+    out = torch.full((130, 70), float("nan"), dtype=torch.bfloat16, device="cuda")
+    y = nv.gemm(xc, xs, wc, ws, out=out)
+    nv.check_status()
+    assert torch.count_nonzero(y).item() == 0

@@ -1,0 +1,126 @@
+"""GPU tests of the reference-facing layer: DWLinear / optimize() / the cutlass_kernels API."""
+import numpy as np
+import pytest
+import torch
+import torch.nn as nn
+
+from oracle import mx_oracle as o
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dw(native_lib):
+    import deepwell_b200
+    assert torch.cuda.is_available()
+    return deepwell_b200
+
+
+def bits_of(t):
+    return t.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
+def oracle_linear(x, w, b=None):
+    y = o.bf16_bits_to_f32(o.mxfp8_linear(bits_of(x), bits_of(w), bias_bits=None if b is None else bits_of(b)))
+    return torch.from_numpy(y)
+
+
+def close(got, ref, rtol=1e-2):
+    got, ref = got.double().cpu(), ref.double().cpu()
+    return bool(((got - ref).abs() <= rtol * torch.maximum(ref.abs(), ref.abs().mean())).all())
+
+
+def test_dwlinear_forward_backward_against_oracle(dw):
+    torch.manual_seed(0)
+    lin = nn.Linear(256, 384, bias=True).cuda().bfloat16()
+    m = dw.DWLinear.from_linear(lin)
+    x = torch.randn(4, 60, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)   # 240 tokens: padded to 256 for wgrad
+    y = m(x)
+    assert y.shape == (4, 60, 384)
+    assert close(y.reshape(-1, 384), oracle_linear(x.reshape(-1, 256), lin.weight, lin.bias))
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    gy2, x2 = gy.reshape(-1, 384), x.detach().reshape(-1, 256)
+    # dgrad: dY row-wise along N, W column-wise along N
+    dyc, dys = o.quantize_rowwise(bits_of(gy2))
+    wc, ws = o.quantize_rowwise(bits_of(lin.weight.detach().t().contiguous()))
+    ref_dx = o.bf16_bits_to_f32(o.gemm_dequantized(dyc, dys, wc, ws))
+    assert close(x.grad.reshape(-1, 256), torch.from_numpy(ref_dx))
+    # wgrad: both operands column-wise along M (zero rows pad M to a multiple of 32)
+    pad = lambda t: torch.nn.functional.pad(t, (0, 0, 0, (-t.shape[0]) % 32))
+    ac, asc = o.quantize_rowwise(bits_of(pad(gy2).t().contiguous()))
+    bc, bsc = o.quantize_rowwise(bits_of(pad(x2).t().contiguous()))
+    ref_dw = o.bf16_bits_to_f32(o.gemm_dequantized(ac, asc, bc, bsc))
+    assert close(lin.weight.grad, torch.from_numpy(ref_dw))
+    assert close(lin.bias.grad, gy2.float().sum(0), rtol=2e-2)
+
+
+def test_weight_cache_follows_parameter_updates(dw):
+    m = dw.DWLinear(64, 64, bias=False).cuda().bfloat16()
+    x = torch.randn(32, 64, device="cuda", dtype=torch.bfloat16)
+    y1 = m(x)
+    key = m._wq_key
+    assert m(x).equal(y1) and m._wq_key == key
+    with torch.no_grad():
+        m.weight.mul_(2.0)
+    y2 = m(x)
+    assert m._wq_key != key and torch.equal(y2.float(), 2 * y1.float())       # power-of-two scaling is exact in MX
+
+
+def test_optimize_trains_close_to_bf16(dw):
+    """An MLP trained for a few SGD steps through optimize(precision='mxfp8') tracks the bf16 model."""
+    torch.manual_seed(1)
+    ref = nn.Sequential(nn.Linear(128, 512), nn.GELU(), nn.Linear(512, 128)).cuda().bfloat16()
+    opt_model = dw.optimize(ref, precision="mxfp8", verbose=False)
+    assert sum(isinstance(mm, dw.DWLinear) for mm in opt_model.modules()) == 2
+    x = torch.randn(256, 128, device="cuda", dtype=torch.bfloat16)
+    t = torch.randn(256, 128, device="cuda", dtype=torch.bfloat16)
+    losses = []
+    for model in (ref, opt_model):
+        sgd = torch.optim.SGD(model.parameters(), lr=1e-2)
+        cur = []
+        for _ in range(5):
+            sgd.zero_grad()
+            loss = (model(x).float() - t.float()).pow(2).mean()
+            loss.backward()
+            sgd.step()
+            cur.append(loss.item())
+        losses.append(cur)
+    assert losses[1][-1] < losses[1][0]
+    assert all(abs(a - b) <= 0.05 * abs(a) for a, b in zip(*losses)), losses
+
+
+def test_extension_module_api(dw):
+    ck = dw.cutlass_kernels
+    k = ck.BlackwellGemmKernel()
+    k.initialize(256, 320, 512, "mxfp8", True, 32)
+    a = torch.randn(256, 512, device="cuda").bfloat16()
+    w = (torch.randn(320, 512, device="cuda") * 0.05).bfloat16()
+    ref = oracle_linear(a, w)
+    assert close(k.gemm(a, w.t()), ref)                        # b as the transposed view of an [N, K] weight
+    assert close(k.gemm(a, w.t().contiguous()), ref)           # b as a contiguous [K, N] matrix
+    c = torch.randn(256, 320, device="cuda").bfloat16()
+    assert close(k.gemm(a, w.t(), c, 0.5, 2.0), 0.5 * ref + 2.0 * c.float().cpu(), rtol=2e-2)
+    with pytest.raises(RuntimeError):
+        k.gemm(a[:, :64], w.t())
+    mm = ck.MicroscaleManager()
+    codes, scales = mm.quantize_mxfp8(a, 32)
+    assert codes.dtype == torch.float8_e4m3fn and codes.shape == a.shape and scales.dtype == torch.uint8
+    ec, es = o.quantize_rowwise(bits_of(a))
+    assert np.array_equal(codes.view(torch.uint8).cpu().numpy(), ec) and np.array_equal(scales.cpu().numpy(), es)
+    back = mm.dequantize_mxfp8(codes, scales)
+    assert np.array_equal(bits_of(back), o.f32_to_bf16_bits(o.dequantize_rowwise(ec, es)))
+    ct, st = mm.quantize_mxfp8(a, 32, direction="col", scale_layout="tcgen05")
+    assert ct.shape == (512, 256) and st.numel() == o.sf_tiled_size(512, 8)
+    kb = ck.BlackwellGemmKernel()
+    kb.initialize(256, 320, 512, "bf16")
+    assert close(kb.gemm(a, w.t()), a.float().cpu() @ w.float().cpu().t(), rtol=2e-2)
+    prof = ck.profile_kernel(k, 2, 3)
+    assert prof["runtime_ms"] > 0 and prof["tflops"] > 0
+    from deepwell_b200.kernels import CutlassKernel, GroupedGEMMKernel
+    kk = CutlassKernel()
+    kk.initialize(256, 320, 512, "mxfp8")
+    assert close(kk.gemm(a, w.t()), ref)
+    gk = GroupedGEMMKernel(2, 512, 320)
+    outs = gk.grouped_gemm([a, a[:128]], [w.t(), w.t()])
+    assert close(outs[0], ref) and close(outs[1], ref[:128])

@@ -1,0 +1,157 @@
+"""GPU parity tests of the MX quantiser: CUDA kernels (through the C ABI) against the oracle.
+Bar: bit-exact codes and scales."""
+import hashlib
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import config1_inputs
+from oracle import mx_oracle as o
+from oracle import mx_ref as c
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def nv(native_lib):
+    from deepwell_b200 import _native
+    assert torch.cuda.is_available(), "the parity tests need a GPU"
+    assert native_lib.dw_mxfp8_device_supported(0) == 1, "sm_100a device required"
+    return _native
+
+
+def bits_of(t):
+    return t.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
+def from_bits(bits):
+    return torch.from_numpy(bits.view(np.int16).copy()).view(torch.bfloat16).cuda()
+
+
+def host(t):
+    return t.view(torch.uint8).cpu().numpy()
+
+
+def check_all_forms(nv, x, rule):
+    """Every direction and both scale layouts of one input against the C restatement."""
+    xb = bits_of(x)
+    er, ers = c.quantize_rowwise(xb, rule)
+    et, ets = c.quantize_colwise(xb, rule, True)
+    en, _ = c.quantize_colwise(xb, rule, False)
+    for layout in (nv.SF_FLAT, nv.SF_TILED):
+        exp_rs = ers if layout == nv.SF_FLAT else o.sf_flat_to_tiled(ers)
+        exp_ts = ets if layout == nv.SF_FLAT else o.sf_flat_to_tiled(ets)
+        gc, gs = nv.quantize(x, nv.DIR_ROW, rule, layout)
+        assert np.array_equal(host(gc), er) and np.array_equal(host(gs).reshape(exp_rs.shape), exp_rs)
+        gc, gs = nv.quantize(x, nv.DIR_COL_T, rule, layout)
+        assert np.array_equal(host(gc), et) and np.array_equal(host(gs).reshape(exp_ts.shape), exp_ts)
+        gc, gs = nv.quantize(x, nv.DIR_COL, rule, layout)
+        assert np.array_equal(host(gc), en) and np.array_equal(host(gs).reshape(exp_ts.shape), exp_ts)
+        a, b, cc, d = nv.quantize_both(x, rule, layout)
+        assert np.array_equal(host(a), er) and np.array_equal(host(b).reshape(exp_rs.shape), exp_rs)
+        assert np.array_equal(host(cc), et) and np.array_equal(host(d).reshape(exp_ts.shape), exp_ts)
+
+
+@pytest.mark.parametrize("rule", [0, 1])
+def test_kat_vectors(nv, golden, rule):
+    k = golden["kat_quant"]
+    name = o.SCALE_RULES[rule]
+    x = from_bits(k["bits"])
+    gc, gs = nv.quantize(x, nv.DIR_ROW, rule, nv.SF_FLAT)
+    assert np.array_equal(host(gc), k[f"row_codes_{name}"]) and np.array_equal(host(gs), k[f"row_scales_{name}"])
+    gc, gs = nv.quantize(x, nv.DIR_COL_T, rule, nv.SF_FLAT)
+    assert np.array_equal(host(gc), k[f"col_codes_{name}"]) and np.array_equal(host(gs), k[f"col_scales_{name}"])
+    check_all_forms(nv, x, rule)
+
+
+@pytest.mark.parametrize("shape", [(128, 128), (256, 512), (96, 160), (32, 96), (33, 64), (1, 32), (7, 50), (129, 4096),
+                                   (4096, 128), (300, 1000), (1, 1), (31, 31), (64, 8), (2048, 1024)])
+@pytest.mark.parametrize("rule", [0, 1])
+def test_shapes_fast_and_ragged(nv, shape, rule):
+    g = torch.Generator("cpu").manual_seed(shape[0] * 7919 + shape[1])
+    x = torch.randn(shape, generator=g)
+    x[torch.rand(shape, generator=g) < 0.01] *= 50
+    check_all_forms(nv, x.bfloat16().cuda(), rule)
+
+
+def test_every_bf16_pattern(nv):
+    """NaN, Inf, subnormals, signed zeros: all 65536 patterns, shuffled, both directions and rules."""
+    bits = np.random.default_rng(1).permutation(65536).astype(np.uint16).reshape(512, 128)
+    for rule in (0, 1):
+        check_all_forms(nv, from_bits(bits), rule)
+
+
+def test_empty_inputs(nv):
+    for shape in [(0, 64), (64, 0)]:
+        x = torch.empty(shape, dtype=torch.bfloat16, device="cuda")
+        codes, scales = nv.quantize(x, nv.DIR_ROW, 0, nv.SF_FLAT)
+        assert codes.numel() == 0
+
+
+def test_unaligned_views_take_the_generic_path(nv):
+    base = torch.randn(257 * 96 + 1, device="cuda").bfloat16()
+    x = base[1:].view(257, 96)                      # 2-byte aligned only
+    assert x.data_ptr() % 16 != 0
+    xb = bits_of(x)
+    L = nv.load()
+    codes = torch.empty(257, 96, dtype=torch.uint8, device="cuda")
+    scales = torch.empty(257 * 3, dtype=torch.uint8, device="cuda")
+    rc = L.dw_mxfp8_quantize(x.data_ptr(), codes.data_ptr(), scales.data_ptr(), 257, 96, 0, 0, 0,
+                             torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    er, ers = c.quantize_rowwise(xb, 0)
+    assert np.array_equal(codes.cpu().numpy(), er) and np.array_equal(scales.cpu().numpy().reshape(ers.shape), ers)
+
+
+def test_config1_against_golden_digests(nv, golden):
+    g = golden["config1"]
+    X, W = config1_inputs()
+    sha = lambda a: hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
+    xc, xs = nv.quantize(X.cuda(), nv.DIR_ROW, 0, nv.SF_FLAT)
+    wc, ws = nv.quantize(W.cuda(), nv.DIR_ROW, 0, nv.SF_FLAT)
+    assert sha(host(xc)) == str(g["x_codes_sha"]) and sha(host(xs)) == str(g["x_scales_sha"])
+    assert sha(host(wc)) == str(g["w_codes_sha"]) and sha(host(ws)) == str(g["w_scales_sha"])
+    assert np.array_equal(host(xc)[:8, :64], g["x_codes_head"])
+
+
+def test_dequantize_matches_oracle(nv):
+    x = (torch.randn(256, 512) * 3).bfloat16().cuda()
+    for layout in (nv.SF_FLAT, nv.SF_TILED):
+        gc, gs = nv.quantize(x, nv.DIR_ROW, 0, layout)
+        dq = nv.dequantize(gc, gs, layout)
+        fc, fs = nv.quantize(x, nv.DIR_ROW, 0, nv.SF_FLAT)
+        exp = o.f32_to_bf16_bits(o.dequantize_rowwise(host(fc), host(fs)))
+        assert np.array_equal(bits_of(dq), exp)
+    x = torch.randn(5, 50).bfloat16().cuda()           # ragged: scalar path
+    gc, gs = nv.quantize(x, nv.DIR_ROW, 0, nv.SF_FLAT)
+    exp = o.f32_to_bf16_bits(o.dequantize_rowwise(host(gc), host(gs)))
+    assert np.array_equal(bits_of(nv.dequantize(gc, gs, nv.SF_FLAT)), exp)
+
+
+@pytest.mark.parametrize("rows,cols", [(16384, 4096), (16384, 14336), (1 << 21, 128), (4096, 16384)])
+def test_full_size_properties(nv, rows, cols):
+    """At BASELINE sizes (Student-t(3) x 0.5 inputs): sampled row blocks against the oracle, the
+    column-wise payload equals the row-wise payload of the transpose, idempotence of
+    quantise(dequantise(q)), and the fused kernel equals the two single-direction kernels."""
+    g = torch.Generator("cuda").manual_seed(4567)
+    z = torch.randn(rows, cols, device="cuda", generator=g)
+    v = torch.distributions.Chi2(torch.tensor(3.0, device="cuda")).sample((rows, 1))
+    x = (0.5 * z / torch.sqrt(v / 3)).bfloat16()
+    del z
+    rc, rs = nv.quantize(x, nv.DIR_ROW, 0, nv.SF_FLAT)
+    sel = torch.randint(0, rows, (64,), generator=torch.Generator().manual_seed(1)).tolist()
+    er, ers = c.quantize_rowwise(bits_of(x[sel]), 0)
+    assert np.array_equal(host(rc[sel]), er) and np.array_equal(host(rs[sel]), ers)
+    tc, ts = nv.quantize(x, nv.DIR_COL_T, 0, nv.SF_FLAT)
+    xt = x.t().contiguous()
+    tc2, ts2 = nv.quantize(xt, nv.DIR_ROW, 0, nv.SF_FLAT)
+    assert torch.equal(tc.view(torch.uint8), tc2.view(torch.uint8)) and torch.equal(ts, ts2)
+    del xt, tc2, ts2
+    a, b, cc, d = nv.quantize_both(x, 0, nv.SF_FLAT)
+    assert torch.equal(a.view(torch.uint8), rc.view(torch.uint8)) and torch.equal(b, rs)
+    assert torch.equal(cc.view(torch.uint8), tc.view(torch.uint8)) and torch.equal(d, ts)
+    dq = nv.dequantize(rc, rs, nv.SF_FLAT)
+    rc2, rs2 = nv.quantize(dq, nv.DIR_ROW, 0, nv.SF_FLAT)
+    dq2 = nv.dequantize(rc2, rs2, nv.SF_FLAT)
+    assert torch.equal(dq.view(torch.int16), dq2.view(torch.int16))      # idempotent after one round trip
