@@ -37,10 +37,11 @@ __device__ __forceinline__ float e8m0_value(uint32_t byte) {
     return __uint_as_float(byte == 0u ? 0x00400000u : (byte << 23));
 }
 
-// max over the two unsigned 16-bit halves, lane-wise
-__device__ __forceinline__ uint32_t max_u16x2(uint32_t a, uint32_t b) {
+// |a| max |b| on both bf16 halves at once (the sign of the result is meaningless).  A NaN operand
+// is dropped in favour of the other operand, exactly as fmaxf does.
+__device__ __forceinline__ uint32_t absmax_bf16x2(uint32_t a, uint32_t b) {
     uint32_t d;
-    asm("max.u16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    asm("max.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
     return d;
 }
 
@@ -51,29 +52,34 @@ __device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi) {
     return d;
 }
 
-// One bf16x2 word scaled by `inv` -> two E4M3 codes in bits [0,16).
-__device__ __forceinline__ uint32_t quant_word(uint32_t w, float inv) {
-    const float lo = __uint_as_float(w << 16) * inv;
-    const float hi = __uint_as_float(w & 0xFFFF0000u) * inv;
-    return cvt_e4m3x2(lo, hi);
+// 2^(127 - byte) as a bf16 pattern replicated in both halves (byte 254 -> the subnormal 2^-127).
+__device__ __forceinline__ uint32_t e8m0_inverse_bf16x2(uint32_t byte) {
+    const uint32_t h = byte >= 254u ? 0x0040u : ((254u - byte) << 7);
+    return h | (h << 16);
+}
+
+// One bf16x2 word times a power of two (`inv2` from e8m0_inverse_bf16x2) -> two E4M3 codes in
+// bits [0,16).  The bf16 product is exact wherever it matters: a result that is subnormal in bf16
+// is far below half the smallest E4M3 step and encodes as zero either way.
+__device__ __forceinline__ uint32_t quant_word(uint32_t w, uint32_t inv2) {
+    uint32_t q;
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(q) : "r"(w), "r"(inv2));
+    return cvt_e4m3x2(__uint_as_float(q << 16), __uint_as_float(q & 0xFFFF0000u));
 }
 
 // amax pattern (15-bit magnitude) over n bf16x2 words, NaN elements dropped as fmaxf would.
 template <int N>
 __device__ __forceinline__ uint32_t amax_words(const uint32_t (&w)[N]) {
-    uint32_t m = 0;
+    uint32_t m = w[0];
 #pragma unroll
-    for (int i = 0; i < N; ++i) m = max_u16x2(m, w[i] & 0x7FFF7FFFu);
-    uint32_t a = max(m & 0xFFFFu, m >> 16);
-    if (a > 0x7F80u) {  // a NaN somewhere: redo with the NaNs filtered (rare)
-        a = 0;
-#pragma unroll
-        for (int i = 0; i < N; ++i) {
-            const uint32_t lo = w[i] & 0x7FFFu, hi = (w[i] >> 16) & 0x7FFFu;
-            if (lo <= 0x7F80u) a = max(a, lo);
-            if (hi <= 0x7F80u) a = max(a, hi);
-        }
-    }
+    for (int i = 1; i < N; ++i) m = absmax_bf16x2(m, w[i]);
+    return m;   // two candidate magnitudes, one per half; fold with fold_amax()
+}
+
+// Folds the two halves of an absmax word into one 15-bit magnitude; an all-NaN block counts as 0.
+__device__ __forceinline__ uint32_t fold_amax(uint32_t m) {
+    const uint32_t lo = m & 0x7FFFu, hi = (m >> 16) & 0x7FFFu;
+    const uint32_t a = max(lo <= 0x7F80u ? lo : 0u, hi <= 0x7F80u ? hi : 0u);
     return a;
 }
 

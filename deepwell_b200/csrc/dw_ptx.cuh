@@ -156,6 +156,43 @@ __device__ __forceinline__ void tc_mma_mxf8_block_scale(uint32_t d_tmem, uint64_
             : "memory");
 }
 
+// Same two instructions with the descriptors split into a run-time low word (start address, which
+// moves with the stage and the K step) and a compile-time high word, so the issuing thread spends
+// one integer add per descriptor.
+constexpr uint32_t kDescHiSw128 = 64u | (1u << 14) | (2u << 29);   // SBO 1024 B, version 1, 128-byte swizzle
+constexpr uint32_t kDescHiSf = 8u | (1u << 14);                     // SBO 128 B, version 1, no swizzle
+__device__ __forceinline__ uint32_t desc_lo_sw128(uint32_t saddr) { return ((saddr >> 4) & 0x3FFFu) | (1u << 16); }
+__device__ __forceinline__ uint32_t desc_lo_sf(uint32_t saddr) { return (saddr >> 4) & 0x3FFFu; }
+
+template <int kCtas>
+__device__ __forceinline__ void tc_cp_sf(uint32_t taddr, uint32_t desc_lo) {
+    if (kCtas == 1)
+        asm volatile("{\n\t.reg .b64 d;\n\tmov.b64 d, {%1, %2};\n\ttcgen05.cp.cta_group::1.32x128b.warpx4 [%0], d;\n\t}"
+                     ::"r"(taddr), "r"(desc_lo), "n"(kDescHiSf) : "memory");
+    else
+        asm volatile("{\n\t.reg .b64 d;\n\tmov.b64 d, {%1, %2};\n\ttcgen05.cp.cta_group::2.32x128b.warpx4 [%0], d;\n\t}"
+                     ::"r"(taddr), "r"(desc_lo), "n"(kDescHiSf) : "memory");
+}
+
+template <int kCtas>
+__device__ __forceinline__ void tc_mma_mxf8(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                            uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+    if (kCtas == 1)
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "mov.b64 da, {%1, %7};\n\tmov.b64 db, {%2, %7};\n\t"
+            "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], da, db, %3, [%5], [%6], p;\n\t}"
+            ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem), "n"(kDescHiSw128)
+            : "memory");
+    else
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "mov.b64 da, {%1, %7};\n\tmov.b64 db, {%2, %7};\n\t"
+            "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], da, db, %3, [%5], [%6], p;\n\t}"
+            ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem), "n"(kDescHiSw128)
+            : "memory");
+}
+
 // All tcgen05 operations issued so far by this thread arrive (once) on `bar` when they complete.
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -164,6 +201,12 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
 // barrier of the peer CTA (see map_to_cta).  One arrive per call.
 __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// Pair form that arrives on the barrier at this shared-memory offset in BOTH CTAs of the pair
+// (a multicast of the barrier arrive, not of any data).
+__device__ __forceinline__ void tc_commit_both(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(static_cast<uint16_t>(3)) : "memory");
 }
 // shared::cluster address of the same shared-memory offset in CTA `cta` of this cluster
 __device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t cta) {
@@ -186,6 +229,15 @@ __device__ __forceinline__ void tc_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[3
         : "memory");
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// True in exactly one lane of a converged warp.  The pipeline roles run their loops with the whole
+// warp (so every address and descriptor is warp-uniform and can live in uniform registers) and
+// only the instructions that must be issued once sit behind this predicate.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xFFFFFFFF;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
 
 // ---------------- cluster ----------------
 __device__ __forceinline__ uint32_t cluster_ctarank() {

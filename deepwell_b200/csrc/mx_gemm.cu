@@ -34,10 +34,16 @@ struct GemmParams {
     int* status;
     int64_t M, N, K;
     float alpha, beta;
-    uint32_t tiles_m, tiles_n, num_tiles, num_kblocks;
+    uint32_t tiles_m, tiles_n, num_tiles, num_kblocks, group_m;
+    // Optional tuning counters (the caller's workspace): per CTA, SM cycles each role spent waiting
+    //   [0] producer: free stage       [1] MMA issuer: accumulator drained (two tiles back)
+    //   [2] MMA issuer: shared accumulator columns drained (previous tile)
+    //   [3] MMA issuer: operand data   [4] epilogue warp 2: accumulator finished   [7] kernel cycles
+    long long* wait_cycles;
 };
+constexpr int kWaitCounters = 8;
 
-template <int BN, int kCtas>
+template <int BN, int kCtas, int kGroup>
 struct GemmCfg {
     static constexpr int kBM = 128;                       // rows per CTA
     static constexpr int kBK = 128;                       // bytes (= elements) of K per stage
@@ -48,26 +54,38 @@ struct GemmCfg {
     static constexpr int kSfbTiles = BN / 128;
     static constexpr int kSfbBytes = kSfbTiles * 512;
     static constexpr int kStageBytes = (kABytes + kBBytes + kSfaBytes + kSfbBytes + 1023) / 1024 * 1024;
-    static constexpr int kStages = (200 * 1024 / kStageBytes) > 8 ? 8 : (200 * 1024 / kStageBytes);
-    static constexpr int kAccStages = (BN == 256) ? 1 : 2;
-    static constexpr int kSfaCol = kAccStages * BN;       // TMEM column of the A scales
-    static constexpr int kSfbCol = kSfaCol + 4;
+    static constexpr int kFit = 212 * 1024 / kStageBytes;
+    static constexpr int kStages = (kFit >= 8 ? 8 : kFit) / (kGroup % 2 ? 2 * kGroup : kGroup) * (kGroup % 2 ? 2 * kGroup : kGroup);
+    // stages are handed back to the producer `kGroup` at a time: one tcgen05.commit per group
+    static constexpr int kGroups = kStages / kGroup;
+    static_assert(kStages % 2 == 0 && kStages % kGroup == 0 && kGroups >= 2, "ring shape");
+    // Tensor memory (512 columns): two accumulators and two sets of scale columns.  With BN = 256 the
+    // two accumulators cannot both be 256 columns wide next to the scales, so they OVERLAP by 32
+    // columns: acc0 = [0,256), acc1 = [224,480).  The epilogue drains the shared 32 columns of a
+    // finished tile first and signals them free; the next tile's MMAs (which write the other
+    // accumulator) start then, while the remaining 224 columns are drained under the mainloop.
+    static constexpr int kAccStages = 2;
+    static constexpr int kAccStride = (BN == 256) ? 224 : BN;
+    static constexpr bool kOverlap = kAccStride < BN;
+    static constexpr int kSfBase = (BN == 256) ? 480 : 2 * BN;   // first scale column
+    static constexpr int kSfSetCols = 16;                  // columns per scale set (A: 4, B: up to 8)
     static constexpr int kTmemCols = 512;
     static constexpr int kBarrierBytes = 256;
     static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
     static constexpr uint32_t kTxBytes = kCtas * (kABytes + kBBytes + kSfaBytes + kSfbBytes);
-    static_assert(kSfbCol + 4 * kSfbTiles <= kTmemCols, "TMEM columns");
+    static_assert(kSfBase + 2 * kSfSetCols <= kTmemCols && 4 + 4 * kSfbTiles <= kSfSetCols, "TMEM columns");
+    static_assert(kAccStride + BN <= kSfBase, "accumulators must not reach the scale columns");
     static_assert(kStages >= 2, "pipeline depth");
 };
 
 enum : int { kErrProducer = 1, kErrMmaFull = 2, kErrMmaAcc = 3, kErrEpilogue = 4 };
 
-template <int BN, int kCtas>
+template <int BN, int kCtas, int kGroup>
 __global__ void __launch_bounds__(192, 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
                const GemmParams p) {
-    using Cfg = GemmCfg<BN, kCtas>;
+    using Cfg = GemmCfg<BN, kCtas, kGroup>;
     constexpr int kStages = Cfg::kStages, kAcc = Cfg::kAccStages;
     extern __shared__ uint8_t smem_raw[];
 
@@ -84,15 +102,18 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     auto stage_sfb = [&](int s) { return stage_sfa(s) + Cfg::kSfaBytes; };
     const uint32_t bar_base = smem_base + kStages * Cfg::kStageBytes;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
-    auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+    auto empty_bar = [&](int g) { return bar_base + 8u * (kStages + g); };   // one per group of stages
     auto accf_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
     auto acce_bar = [&](int a) { return bar_base + 8u * (2 * kStages + kAcc + a); };
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + kStages * Cfg::kStageBytes + 8 * (2 * kStages + 2 * kAcc));
+    const uint32_t ovl_bar = bar_base + 8u * (2 * kStages + 2 * kAcc);   // shared accumulator columns drained
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + kStages * Cfg::kStageBytes + 8 * (2 * kStages + 2 * kAcc + 1));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) { ptx::mbar_init(full_bar(s), 1); ptx::mbar_init(empty_bar(s), 1); }
+        for (int s = 0; s < kStages; ++s) ptx::mbar_init(full_bar(s), 1);
+        for (int g = 0; g < Cfg::kGroups; ++g) ptx::mbar_init(empty_bar(g), 1);
         for (int a = 0; a < kAcc; ++a) { ptx::mbar_init(accf_bar(a), 1); ptx::mbar_init(acce_bar(a), 4 * kCtas); }
+        ptx::mbar_init(ovl_bar, 4 * kCtas);
         *abort_flag = 0;
         ptx::fence_barrier_init();
         ptx::prefetch_tmap(&tm_a); ptx::prefetch_tmap(&tm_b); ptx::prefetch_tmap(&tm_sfa); ptx::prefetch_tmap(&tm_sfb);
@@ -109,85 +130,135 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 
     const uint32_t num_workers = gridDim.x / kCtas, worker = blockIdx.x / kCtas;
     int err = 0;
+    const bool timed = p.wait_cycles != nullptr;
+    const long long t_begin = timed ? clock64() : 0;
+    long long waited[3] = {0, 0, 0};
+    auto timed_wait = [&](uint32_t bar, uint32_t parity, int slot) {
+        if (!timed) return ptx::mbar_wait<kCtas == 2>(bar, parity, abort_flag);
+        const long long t0 = clock64();
+        const bool ok = ptx::mbar_wait<kCtas == 2>(bar, parity, abort_flag);
+        waited[slot] += clock64() - t0;
+        return ok;
+    };
+    // Tile order: bands of `group_m` row tiles, column tiles outer, row tiles inner, so the CTAs
+    // running at the same time share a small set of A and B tiles in L2.
+    auto tile_coords = [&](uint32_t tile, uint32_t& tm, uint32_t& tn) {
+        const uint32_t per_band = p.group_m * p.tiles_n;
+        const uint32_t band = tile / per_band, in_band = tile - band * per_band;
+        const uint32_t first = band * p.group_m;
+        const uint32_t rows_in_band = min(p.group_m, p.tiles_m - first);
+        tn = in_band / rows_in_band;
+        tm = first + (in_band - tn * rows_in_band);
+    };
 
+    // Both pipeline roles walk the stage ring with compile-time stage indices (the k loop is unrolled
+    // by the ring depth and every tile starts again at stage 0), so addresses and descriptors are
+    // constants plus one base register and the single issuing thread does almost no arithmetic.
+    // Each stage's barrier parity is one bit of a mask, flipped on every use of that stage.
     if (warp == 0) {
-        // ================= TMA producer =================
-        if (lane == 0) {
-            uint32_t stage = 0, phase = 0;
-            // loads of both CTAs of a pair complete on the leader's barrier
+        // ================= TMA producer (whole warp walks the ring, one elected lane issues) =================
+        {
+            uint32_t empty_parity = 0;   // bit g: parity of the next wait on empty_bar(g), inverted
+            const uint32_t full0 = (kCtas == 2) ? ptx::map_to_cta(full_bar(0), 0) : full_bar(0);   // leader's barrier
+            const int nkb = static_cast<int>(p.num_kblocks);
             for (uint32_t tile = worker; tile < p.num_tiles && !err; tile += num_workers) {
-                const uint32_t tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+                uint32_t tm, tn;
+                tile_coords(tile, tm, tn);
                 const int row_a = static_cast<int>(tm * (128 * kCtas) + rank * 128);
                 const int row_b = static_cast<int>(tn * BN + rank * Cfg::kBRows);
-                const int sfa_tile = static_cast<int>(tm * kCtas + rank);
-                const int sfb_tile = static_cast<int>(tn * Cfg::kSfbTiles);
-                for (uint32_t kb = 0; kb < p.num_kblocks; ++kb) {
-                    if (!ptx::mbar_wait<kCtas == 2>(empty_bar(stage), phase ^ 1u, abort_flag)) { err = kErrProducer; break; }
-                    const uint32_t bar = (kCtas == 2) ? ptx::map_to_cta(full_bar(stage), 0) : full_bar(stage);
-                    if (leader) ptx::mbar_arrive_expect_tx(full_bar(stage), Cfg::kTxBytes);
-                    const int k0 = static_cast<int>(kb * Cfg::kBK);
-                    if (kCtas == 2) {
-                        ptx::tma_load_2d_pair(stage_a(stage), &tm_a, bar, k0, row_a);
-                        ptx::tma_load_2d_pair(stage_b(stage), &tm_b, bar, k0, row_b);
-                        ptx::tma_load_2d_pair(stage_sfa(stage), &tm_sfa, bar, 0, sfa_tile * static_cast<int>(p.num_kblocks) + static_cast<int>(kb));
-                        for (int j = 0; j < Cfg::kSfbTiles; ++j)
-                            ptx::tma_load_2d_pair(stage_sfb(stage) + 512 * j, &tm_sfb, bar, 0,
-                                                  (sfb_tile + j) * static_cast<int>(p.num_kblocks) + static_cast<int>(kb));
-                    } else {
-                        ptx::tma_load_2d(stage_a(stage), &tm_a, bar, k0, row_a);
-                        ptx::tma_load_2d(stage_b(stage), &tm_b, bar, k0, row_b);
-                        ptx::tma_load_2d(stage_sfa(stage), &tm_sfa, bar, 0, sfa_tile * static_cast<int>(p.num_kblocks) + static_cast<int>(kb));
-                        for (int j = 0; j < Cfg::kSfbTiles; ++j)
-                            ptx::tma_load_2d(stage_sfb(stage) + 512 * j, &tm_sfb, bar, 0,
-                                             (sfb_tile + j) * static_cast<int>(p.num_kblocks) + static_cast<int>(kb));
+                const int sfa_row = static_cast<int>(tm * kCtas + rank) * nkb;
+                const int sfb_row = static_cast<int>(tn * Cfg::kSfbTiles) * nkb;
+                for (int kb0 = 0; kb0 < nkb && !err; kb0 += kStages) {
+#pragma unroll
+                    for (int s = 0; s < kStages; ++s) {
+                        const int kb = kb0 + s;
+                        if (kb < nkb && !err) {
+                            if (s % kGroup == 0) {        // first stage of a group: wait until the group is free
+                                const int g = s / kGroup;
+                                if (!timed_wait(empty_bar(g), ((empty_parity >> g) & 1u) ^ 1u, 0)) { err = kErrProducer; continue; }
+                                empty_parity ^= 1u << g;
+                            }
+                            const uint32_t bar = full0 + 8u * s;
+                            if (!ptx::elect_one()) continue;
+                            if (leader) ptx::mbar_arrive_expect_tx(full_bar(s), Cfg::kTxBytes);
+                            if (kCtas == 2) {
+                                ptx::tma_load_2d_pair(stage_a(s), &tm_a, bar, kb * Cfg::kBK, row_a);
+                                ptx::tma_load_2d_pair(stage_b(s), &tm_b, bar, kb * Cfg::kBK, row_b);
+                                ptx::tma_load_2d_pair(stage_sfa(s), &tm_sfa, bar, 0, sfa_row + kb);
+#pragma unroll
+                                for (int j = 0; j < Cfg::kSfbTiles; ++j)
+                                    ptx::tma_load_2d_pair(stage_sfb(s) + 512 * j, &tm_sfb, bar, 0, sfb_row + j * nkb + kb);
+                            } else {
+                                ptx::tma_load_2d(stage_a(s), &tm_a, bar, kb * Cfg::kBK, row_a);
+                                ptx::tma_load_2d(stage_b(s), &tm_b, bar, kb * Cfg::kBK, row_b);
+                                ptx::tma_load_2d(stage_sfa(s), &tm_sfa, bar, 0, sfa_row + kb);
+#pragma unroll
+                                for (int j = 0; j < Cfg::kSfbTiles; ++j)
+                                    ptx::tma_load_2d(stage_sfb(s) + 512 * j, &tm_sfb, bar, 0, sfb_row + j * nkb + kb);
+                            }
+                        }
                     }
-                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
             }
         }
     } else if (warp == 1) {
-        // ================= MMA issuer (leader CTA only) =================
-        if (lane == 0 && leader) {
-            uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+        // ================= MMA issuer (leader CTA only; whole warp walks, one elected lane issues) =================
+        if (leader) {
+            uint32_t full_parity = 0, acc = 0, acc_phase = 0, tiles_done = 0;
             constexpr uint32_t idesc = ptx::idesc_mxf8(128 * kCtas, BN);
+            constexpr uint32_t kStageStep = Cfg::kStageBytes >> 4;          // descriptor units of 16 bytes
+            const uint32_t a_lo0 = ptx::desc_lo_sw128(stage_a(0)), b_lo0 = ptx::desc_lo_sw128(stage_b(0));
+            const uint32_t sfa_lo0 = ptx::desc_lo_sf(stage_sfa(0)), sfb_lo0 = ptx::desc_lo_sf(stage_sfb(0));
+            const uint32_t sf_t0 = tmem_base + Cfg::kSfBase;
+            const int nkb = static_cast<int>(p.num_kblocks);
             for (uint32_t tile = worker; tile < p.num_tiles && !err; tile += num_workers) {
-                if (!ptx::mbar_wait<kCtas == 2>(acce_bar(acc), acc_phase ^ 1u, abort_flag)) { err = kErrMmaAcc; break; }
+                // this accumulator fully drained (two tiles ago) ...
+                if (!timed_wait(acce_bar(acc), acc_phase ^ 1u, 0)) { err = kErrMmaAcc; break; }
+                // ... and the columns it shares with the other accumulator drained (previous tile)
+                if (Cfg::kOverlap && tiles_done > 0 &&
+                    !timed_wait(ovl_bar, (tiles_done - 1u) & 1u, 1)) { err = kErrMmaAcc; break; }
                 ptx::tc_fence_after();
-                const uint32_t d_tmem = tmem_base + acc * BN;
-                for (uint32_t kb = 0; kb < p.num_kblocks; ++kb) {
-                    if (!ptx::mbar_wait<kCtas == 2>(full_bar(stage), phase, abort_flag)) { err = kErrMmaFull; break; }
-                    ptx::tc_fence_after();
-                    ptx::tc_cp_32x128b_warpx4<kCtas>(tmem_base + Cfg::kSfaCol, ptx::smem_desc_sf(stage_sfa(stage)));
+                const uint32_t d_tmem = tmem_base + acc * Cfg::kAccStride;
+                uint32_t accumulate = 0;
+                for (int kb0 = 0; kb0 < nkb && !err; kb0 += kStages) {
 #pragma unroll
-                    for (int j = 0; j < Cfg::kSfbTiles; ++j)
-                        ptx::tc_cp_32x128b_warpx4<kCtas>(tmem_base + Cfg::kSfbCol + 4 * j,
-                                                         ptx::smem_desc_sf(stage_sfb(stage) + 512 * j));
-                    const uint64_t a_desc = ptx::smem_desc_sw128(stage_a(stage));
-                    const uint64_t b_desc = ptx::smem_desc_sw128(stage_b(stage));
+                    for (int s = 0; s < kStages; ++s) {
+                        if (kb0 + s < nkb && !err) {
+                            if (!timed_wait(full_bar(s), (full_parity >> s) & 1u, 2)) { err = kErrMmaFull; continue; }
+                            full_parity ^= 1u << s;
+                            ptx::tc_fence_after();
+                            // scales of this k-block: shared memory -> tensor memory; two column sets
+                            // alternate so the copy never overwrites scales the previous MMAs still read
+                            const uint32_t sfa_t = sf_t0 + (s & 1) * Cfg::kSfSetCols, sfb_t = sfa_t + 4;
+                            const uint32_t acc_now = accumulate;
+                            accumulate = 1;
+                            if (!ptx::elect_one()) continue;
+                            ptx::tc_cp_sf<kCtas>(sfa_t, sfa_lo0 + s * kStageStep);
 #pragma unroll
-                    for (uint32_t k = 0; k < 4; ++k) {
-                        // advance 32 bytes along K inside the 128-byte swizzle atom: +2 in 16-byte units
-                        ptx::tc_mma_mxf8_block_scale<kCtas>(d_tmem, a_desc + 2 * k, b_desc + 2 * k,
-                                                            ptx::idesc_with_sf_ids(idesc, k, k),
-                                                            tmem_base + Cfg::kSfaCol, tmem_base + Cfg::kSfbCol,
-                                                            (kb | k) != 0u);
+                            for (int j = 0; j < Cfg::kSfbTiles; ++j)
+                                ptx::tc_cp_sf<kCtas>(sfb_t + 4 * j, sfb_lo0 + s * kStageStep + 32 * j);
+#pragma unroll
+                            for (uint32_t k = 0; k < 4; ++k) {
+                                // +2 descriptor units = 32 bytes along K inside the 128-byte swizzle atom
+                                ptx::tc_mma_mxf8<kCtas>(d_tmem, a_lo0 + s * kStageStep + 2 * k, b_lo0 + s * kStageStep + 2 * k,
+                                                        ptx::idesc_with_sf_ids(idesc, k, k), sfa_t, sfb_t, acc_now | k);
+                            }
+                            // Last stage of a group (or of the tile): the group is free again once the MMAs
+                            // issued so far have read it.  (Measured: releasing stages one at a time,
+                            // kGroup = 1, is fastest; coarser groups lengthen the refill latency.)
+                            if (s % kGroup == kGroup - 1 || kb0 + s == nkb - 1) {
+                                const int g = s / kGroup;
+                                if (kCtas == 2) ptx::tc_commit_both(empty_bar(g)); else ptx::tc_commit(empty_bar(g));
+                            }
+                        }
                     }
-                    // stage free again once these MMAs have read it (in both CTAs of a pair)
-                    if (kCtas == 2) {
-                        ptx::tc_commit_pair(empty_bar(stage));
-                        ptx::tc_commit_pair(ptx::map_to_cta(empty_bar(stage), 1));
-                    } else {
-                        ptx::tc_commit(empty_bar(stage));
-                    }
-                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
                 if (err) break;
-                if (kCtas == 2) {
-                    ptx::tc_commit_pair(accf_bar(acc));
-                    ptx::tc_commit_pair(ptx::map_to_cta(accf_bar(acc), 1));
-                } else {
-                    ptx::tc_commit(accf_bar(acc));
+                if (ptx::elect_one()) {
+                    if (kCtas == 2) ptx::tc_commit_both(accf_bar(acc)); else ptx::tc_commit(accf_bar(acc));
                 }
+                __syncwarp();
+                ++tiles_done;
                 if (++acc == kAcc) { acc = 0; acc_phase ^= 1u; }
             }
         }
@@ -196,18 +267,32 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         const uint32_t q = warp & 3u;                    // TMEM lane quadrant this warp may read
         uint32_t acc = 0, acc_phase = 0;
         const bool vec_ok = (p.N % 8) == 0;
+        constexpr int kChunks = BN / 32;
         for (uint32_t tile = worker; tile < p.num_tiles && !err; tile += num_workers) {
-            const uint32_t tm = tile % p.tiles_m, tn = tile / p.tiles_m;
+            uint32_t tm, tn;
+            tile_coords(tile, tm, tn);
             const int64_t row = static_cast<int64_t>(tm) * (128 * kCtas) + rank * 128 + q * 32 + lane;
             const int64_t col0 = static_cast<int64_t>(tn) * BN;
-            if (!ptx::mbar_wait<kCtas == 2>(accf_bar(acc), acc_phase, abort_flag)) { err = kErrEpilogue; break; }
+            if (!timed_wait(accf_bar(acc), acc_phase, 0)) { err = kErrEpilogue; break; }
             ptx::tc_fence_after();
-            const uint32_t t_row = tmem_base + acc * BN + ((q * 32u) << 16);
+            const uint32_t t_row = tmem_base + acc * Cfg::kAccStride + ((q * 32u) << 16);
+            // chunk order: the 32 columns shared with the other accumulator first (the last chunk of
+            // accumulator 0, the first chunk of accumulator 1), then the rest
+            const int first_chunk = (Cfg::kOverlap && acc == 0) ? kChunks - 1 : 0;
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
+            for (int it = 0; it < kChunks; ++it) {
+                const int ch = (it == 0) ? first_chunk : ((Cfg::kOverlap && acc == 0) ? it - 1 : it);
+                const int c = ch * 32;
                 uint32_t r[32];
                 ptx::tc_ld_32x32b_x32(t_row + c, r);
                 ptx::tc_wait_ld();
+                if (Cfg::kOverlap && it == 0) {          // shared columns are in registers: release them
+                    ptx::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (kCtas == 2) ptx::mbar_arrive_cluster(ovl_bar, 0); else ptx::mbar_arrive(ovl_bar);
+                    }
+                }
                 const int64_t col = col0 + c;
                 if (row < p.M && col < p.N) {
                     uint16_t* dst = p.d + row * p.N + col;
@@ -264,6 +349,12 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     }
 
     // ================= common exit =================
+    if (timed && lane == 0) {
+        long long* out = p.wait_cycles + static_cast<size_t>(blockIdx.x) * kWaitCounters;
+        if (warp == 0) { out[0] = waited[0]; out[7] = clock64() - t_begin; }
+        if (warp == 1) { out[1] = waited[0]; out[2] = waited[1]; out[3] = waited[2]; }
+        if (warp == 2) out[4] = waited[0];
+    }
     if (err) {
         *abort_flag = err;
         if (p.status != nullptr) atomicCAS(p.status, 0, err | (static_cast<int>(blockIdx.x) << 8));
@@ -322,7 +413,9 @@ static bool make_sf_map(CUtensorMap* m, const void* base, int64_t tiles) {
                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-static int g_variant = 0;  // 0 auto; 1: 1 CTA BN=128; 2: 1 CTA BN=256; 3: CTA pair BN=256; 4: CTA pair BN=128
+static int g_group_m = 0;  // row tiles per raster band (0 = default)
+// 0 auto; 1: 1 CTA, BN 128; 2: 1 CTA, BN 256; 3: CTA pair (256-row tile), BN 256; 4: CTA pair, BN 128
+static int g_variant = 0;
 
 static int sm_count() {
     static int sms = 0;
@@ -334,9 +427,9 @@ static int sm_count() {
     return sms;
 }
 
-template <int BN, int kCtas>
+template <int BN, int kCtas, int kGroup>
 static int launch_gemm(const void* a, const void* a_sf, const void* b, const void* b_sf, GemmParams p, cudaStream_t st) {
-    using Cfg = GemmCfg<BN, kCtas>;
+    using Cfg = GemmCfg<BN, kCtas, kGroup>;
     CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb;
     const int64_t kt = (p.K / 32 + 3) / 4;
     if (!make_operand_map(&tm_a, a, p.M, p.K, 128) || !make_operand_map(&tm_b, b, p.N, p.K, Cfg::kBRows) ||
@@ -346,11 +439,12 @@ static int launch_gemm(const void* a, const void* a_sf, const void* b, const voi
     p.tiles_n = static_cast<uint32_t>((p.N + BN - 1) / BN);
     p.num_tiles = p.tiles_m * p.tiles_n;
     p.num_kblocks = static_cast<uint32_t>((p.K + 127) / 128);
+    p.group_m = static_cast<uint32_t>(g_group_m > 0 ? g_group_m : 16 / kCtas);
 
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute(mx_gemm_kernel<BN, kCtas>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        attr_err = cudaFuncSetAttribute(mx_gemm_kernel<BN, kCtas, kGroup>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         Cfg::kSmemBytes);
     });
     if (attr_err != cudaSuccess) return DW_ERR_LAUNCH;
@@ -366,7 +460,7 @@ static int launch_gemm(const void* a, const void* a_sf, const void* b, const voi
     attr[0].val.clusterDim.x = kCtas; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (cudaLaunchKernelEx(&cfg, mx_gemm_kernel<BN, kCtas>, tm_a, tm_b, tm_sfa, tm_sfb, p) != cudaSuccess) {
+    if (cudaLaunchKernelEx(&cfg, mx_gemm_kernel<BN, kCtas, kGroup>, tm_a, tm_b, tm_sfa, tm_sfb, p) != cudaSuccess) {
         cudaGetLastError();
         return DW_ERR_LAUNCH;
     }
@@ -378,17 +472,22 @@ static int launch_gemm(const void* a, const void* a_sf, const void* b, const voi
 using namespace dw;
 
 extern "C" DW_API int dw_mxfp8_gemm_set_variant(int variant) {
-    if (variant < 0 || variant > 4) return DW_ERR_BAD_ARG;
-    g_variant = variant;
+    // bits [0,8): kernel variant; bits [8,16): row tiles per raster band (0 = default)
+    const int v = variant & 0xFF, gm = (variant >> 8) & 0xFF;
+    if (variant < 0 || v > 4) return DW_ERR_BAD_ARG;
+    g_variant = v;
+    g_group_m = gm;
     return DW_OK;
 }
 
 extern "C" DW_API size_t dw_mxfp8_gemm_workspace(int64_t, int64_t, int64_t) { return 0; }
 
+// A workspace of at least this many bytes switches the per-CTA wait counters on.
+static constexpr size_t kTimingBytes = 296 * kWaitCounters * sizeof(long long);
+
 extern "C" DW_API int dw_mxfp8_gemm(const void* a_codes, const void* a_sf, const void* b_codes, const void* b_sf, void* d_bf16,
                              const void* bias_bf16, int64_t M, int64_t N, int64_t K, float alpha, float beta, void* workspace,
                              size_t workspace_bytes, void* status_word, void* stream) {
-    (void)workspace; (void)workspace_bytes;
     if (M < 0 || N < 0 || K < 0) return DW_ERR_BAD_ARG;
     if (M == 0 || N == 0) return DW_OK;
     if (!a_codes || !a_sf || !b_codes || !b_sf || !d_bf16) return DW_ERR_BAD_ARG;
@@ -404,15 +503,17 @@ extern "C" DW_API int dw_mxfp8_gemm(const void* a_codes, const void* a_sf, const
     p.bias = static_cast<const uint16_t*>(bias_bf16);
     p.status = static_cast<int*>(status_word);
     p.M = M; p.N = N; p.K = K; p.alpha = alpha; p.beta = beta;
+    p.wait_cycles = (workspace != nullptr && workspace_bytes >= kTimingBytes &&
+                     (reinterpret_cast<uintptr_t>(workspace) & 7) == 0) ? static_cast<long long*>(workspace) : nullptr;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
 
     int v = g_variant;
-    if (v == 0) v = (N > 128) ? 2 : 1;
+    if (v == 0) v = (N <= 128) ? 1 : (M <= 128 ? 2 : 3);
     switch (v) {
-        case 1: return launch_gemm<128, 1>(a_codes, a_sf, b_codes, b_sf, p, st);
-        case 2: return launch_gemm<256, 1>(a_codes, a_sf, b_codes, b_sf, p, st);
-        case 3: return launch_gemm<256, 2>(a_codes, a_sf, b_codes, b_sf, p, st);
-        default: return launch_gemm<128, 2>(a_codes, a_sf, b_codes, b_sf, p, st);
+        case 1: return launch_gemm<128, 1, 1>(a_codes, a_sf, b_codes, b_sf, p, st);
+        case 2: return launch_gemm<256, 1, 1>(a_codes, a_sf, b_codes, b_sf, p, st);
+        case 3: return launch_gemm<256, 2, 1>(a_codes, a_sf, b_codes, b_sf, p, st);
+        default: return launch_gemm<128, 2, 1>(a_codes, a_sf, b_codes, b_sf, p, st);
     }
 }
 

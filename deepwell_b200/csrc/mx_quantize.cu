@@ -27,10 +27,30 @@ namespace dw {
 // ------------------------------------------------------------------------------------------
 // Row-wise fast path.  cols % 32 == 0.  One thread = 16 consecutive elements (half a block).
 // ------------------------------------------------------------------------------------------
+// Division of a 32-bit index by a run-time constant without a divide instruction
+// (round-up multiplier, Granlund & Montgomery): q = (t + ((n - t) >> 1)) >> shift, t = umulhi(mul, n).
+struct FastDiv {
+    uint32_t mul, shift, div;
+    __host__ static FastDiv make(uint32_t d) {      // d >= 2
+        uint32_t l = 0;
+        while ((1ull << l) < d) ++l;
+        FastDiv f;
+        f.mul = static_cast<uint32_t>(((1ull << 32) * ((1ull << l) - d)) / d + 1);
+        f.shift = l - 1;
+        f.div = d;
+        return f;
+    }
+    __device__ __forceinline__ uint32_t quot(uint32_t n) const {
+        const uint32_t t = __umulhi(mul, n);
+        return (t + ((n - t) >> 1)) >> shift;
+    }
+};
+
 template <bool kWide>  // kWide: 32-byte aligned input -> one 256-bit load per chunk
 __global__ void __launch_bounds__(256)
 mx_quant_row_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes, uint8_t* __restrict__ scales,
-                    uint32_t total_chunks, uint32_t chunks_per_row, int rule, int layout, int packed_sf) {
+                    uint32_t total_chunks, FastDiv cpr, int rule, int layout, int packed_sf) {
+    const uint32_t chunks_per_row = cpr.div;
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t T = gridDim.x * blockDim.x;
     const uint32_t kb_per_row = chunks_per_row >> 1;
@@ -58,10 +78,10 @@ mx_quant_row_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes,
         }
 #pragma unroll
         for (int u = 0; u < 2; ++u) {
-            uint32_t amax = amax_words(w[u]);
-            amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
-            const uint32_t sb = e8m0_from_amax(amax, rule);
-            const float inv = e8m0_inverse(sb);
+            uint32_t m2 = amax_words(w[u]);
+            m2 = absmax_bf16x2(m2, __shfl_xor_sync(0xFFFFFFFFu, m2, 1));
+            const uint32_t sb = e8m0_from_amax(fold_amax(m2), rule);
+            const uint32_t inv = e8m0_inverse_bf16x2(sb);
             uint4 q;
             q.x = quant_word(w[u][0], inv) | (quant_word(w[u][1], inv) << 16);
             q.y = quant_word(w[u][2], inv) | (quant_word(w[u][3], inv) << 16);
@@ -79,7 +99,7 @@ mx_quant_row_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes,
                 if (valid && (lane & 7u) == 0u) {
                     int64_t off;
                     if (layout == DW_SF_TILED) {
-                        const uint32_t row = idx[u] / chunks_per_row;
+                        const uint32_t row = cpr.quot(idx[u]);
                         const uint32_t kb = (idx[u] - row * chunks_per_row) >> 1;
                         off = sf_tiled_offset(row, kb, kt);
                     } else {
@@ -90,7 +110,7 @@ mx_quant_row_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes,
             } else if (valid && (lane & 1u) == 0u) {
                 int64_t off;
                 if (layout == DW_SF_TILED) {
-                    const uint32_t row = idx[u] / chunks_per_row;
+                    const uint32_t row = cpr.quot(idx[u]);
                     const uint32_t kb = (idx[u] - row * chunks_per_row) >> 1;
                     off = sf_tiled_offset(row, kb, kt);
                 } else {
@@ -149,11 +169,11 @@ mx_quant_tile_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes
         if (kDoCol) tile[row][cc] = v[j];
         if (kDoRow) {
             const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
-            uint32_t amax = amax_words(w);
-            amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
-            amax = max(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
-            const uint32_t sb = e8m0_from_amax(amax, rule);
-            const float inv = e8m0_inverse(sb);
+            uint32_t m2 = amax_words(w);
+            m2 = absmax_bf16x2(m2, __shfl_xor_sync(0xFFFFFFFFu, m2, 1));
+            m2 = absmax_bf16x2(m2, __shfl_xor_sync(0xFFFFFFFFu, m2, 2));
+            const uint32_t sb = e8m0_from_amax(fold_amax(m2), rule);
+            const uint32_t inv = e8m0_inverse_bf16x2(sb);
             uint2 q;
             q.x = quant_word(w[0], inv) | (quant_word(w[1], inv) << 16);
             q.y = quant_word(w[2], inv) | (quant_word(w[3], inv) << 16);
@@ -187,31 +207,25 @@ mx_quant_tile_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes
         uint32_t w[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) w[i] = tw[(rb * 32 + i) * 64 + p];
-        uint32_t m = 0;
+        uint32_t m = w[0];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) m = max_u16x2(m, w[i] & 0x7FFF7FFFu);
-        uint32_t amax_a = m & 0xFFFFu, amax_b = m >> 16;
-        if (amax_a > 0x7F80u || amax_b > 0x7F80u) {  // NaN present: filtered recomputation
-            amax_a = 0; amax_b = 0;
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                const uint32_t lo = w[i] & 0x7FFFu, hi = (w[i] >> 16) & 0x7FFFu;
-                if (lo <= 0x7F80u) amax_a = max(amax_a, lo);
-                if (hi <= 0x7F80u) amax_b = max(amax_b, hi);
-            }
-        }
+        for (int i = 1; i < 32; ++i) m = absmax_bf16x2(m, w[i]);
+        uint32_t amax_a = m & 0x7FFFu, amax_b = (m >> 16) & 0x7FFFu;   // one column per half
+        if (amax_a > 0x7F80u) amax_a = 0;                               // column of NaNs only
+        if (amax_b > 0x7F80u) amax_b = 0;
         const uint32_t sb_a = e8m0_from_amax(amax_a, rule), sb_b = e8m0_from_amax(amax_b, rule);
-        const float inv_a = e8m0_inverse(sb_a), inv_b = e8m0_inverse(sb_b);
+        const uint32_t inv2 = (e8m0_inverse_bf16x2(sb_a) & 0xFFFFu) | (e8m0_inverse_bf16x2(sb_b) & 0xFFFF0000u);
         uint32_t qa[8], qb[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             uint32_t a = 0, b = 0;
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                const uint32_t w0 = w[4 * i + 2 * h], w1 = w[4 * i + 2 * h + 1];
-                a |= cvt_e4m3x2(__uint_as_float(w0 << 16) * inv_a, __uint_as_float(w1 << 16) * inv_a) << (16 * h);
-                b |= cvt_e4m3x2(__uint_as_float(w0 & 0xFFFF0000u) * inv_b, __uint_as_float(w1 & 0xFFFF0000u) * inv_b)
-                     << (16 * h);
+                uint32_t s0, s1;   // rows 4i+2h and 4i+2h+1, both columns scaled at once
+                asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(s0) : "r"(w[4 * i + 2 * h]), "r"(inv2));
+                asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(s1) : "r"(w[4 * i + 2 * h + 1]), "r"(inv2));
+                a |= cvt_e4m3x2(__uint_as_float(s0 << 16), __uint_as_float(s1 << 16)) << (16 * h);
+                b |= cvt_e4m3x2(__uint_as_float(s0 & 0xFFFF0000u), __uint_as_float(s1 & 0xFFFF0000u)) << (16 * h);
             }
             qa[i] = a; qb[i] = b;
         }
@@ -270,7 +284,7 @@ __global__ void mx_quant_generic_kernel(const uint16_t* __restrict__ x, uint8_t*
             if (a <= 0x7F80u) amax = max(amax, a);
         }
         const uint32_t sb = e8m0_from_amax(amax, rule);
-        const float inv = e8m0_inverse(sb);
+        const float inv = e8m0_inverse(sb);          // fp32 product: exact, same codes as the bf16x2 path
         for (int64_t c = c0; c < c1; ++c) {
             const float f = __uint_as_float(static_cast<uint32_t>(x[r * xsr + c * xsc]) << 16) * inv;
             codes[r * csr + c * csc] = static_cast<uint8_t>(cvt_e4m3x2(f, 0.0f) & 0xFFu);
@@ -366,7 +380,7 @@ static int quantize_generic(const uint16_t* x, uint8_t* codes, uint8_t* scales, 
 static int quantize_row_fast(const uint16_t* x, uint8_t* codes, uint8_t* scales, int64_t rows, int64_t cols, int rule,
                              int layout, cudaStream_t st) {
     const int64_t total_chunks = rows * cols / 16;
-    const uint32_t cpr = static_cast<uint32_t>(cols / 16);
+    const FastDiv cpr = FastDiv::make(static_cast<uint32_t>(cols / 16));
     const int packed = (cols % 128 == 0) && aligned(scales, 4);
     const int64_t want = (total_chunks + 511) / 512;
     const int grid = static_cast<int>(std::min<int64_t>(want, static_cast<int64_t>(num_sms()) * 8));

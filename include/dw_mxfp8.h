@@ -84,9 +84,14 @@ int dw_mxfp8_dequantize(const void *codes, const void *scales, void *out_bf16, i
  * Replaces launch_blackwell_mxfp8_gemm (csrc/blackwell_gemm_kernel.cu:103-156) and the MXFP8
  * branch of BlackwellGemmKernel::gemm (csrc/cutlass_kernels.cpp:173-204), which allocated and
  * freed two scale buffers per call and ran a bf16 cuBLAS GEMM.
- * K % 32 == 0; a_codes, b_codes, d 16-byte aligned.  workspace: dw_mxfp8_gemm_workspace bytes
- * (may be NULL when that is 0).  status_word: optional device int32, set non-zero by the
- * kernel if a bounded wait expires (then read it with dw_mxfp8_check_status). */
+ * K % 32 == 0; a_codes, b_codes, d 16-byte aligned.  workspace: the kernel needs none
+ * (dw_mxfp8_gemm_workspace is 0, NULL is fine); a caller that passes >= DW_GEMM_TIMING_BYTES
+ * gets per-CTA tuning counters there: 8 int64 per CTA, SM cycles the producer, MMA-issuer and
+ * epilogue roles spent waiting ([0] free stage, [1] accumulator drained, [2] shared accumulator
+ * columns drained, [3] operand data, [4] accumulator finished, [7] kernel cycles).
+ * status_word: optional device int32, set non-zero by the kernel if a bounded wait expires
+ * (then read it with dw_mxfp8_check_status). */
+#define DW_GEMM_TIMING_BYTES (296 * 8 * 8)
 int dw_mxfp8_gemm(const void *a_codes, const void *a_sf, const void *b_codes, const void *b_sf,
                   void *d_bf16, const void *bias_bf16, int64_t M, int64_t N, int64_t K, float alpha,
                   float beta, void *workspace, size_t workspace_bytes, void *status_word, void *stream);
