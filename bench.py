@@ -149,9 +149,18 @@ def time_cpu(steps, warmup, rows=CPU_SAMPLE_ROWS):
                       f"{dt:.2f} s per pass: C/OpenMP quantiser + torch.matmul fp32 on dequantised operands"}, dt
 
 
+def use_all_host_threads():
+    """torchrun exports OMP_NUM_THREADS=1; the CPU arm is meant to use every core it may run on."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    os.environ["OMP_NUM_THREADS"] = str(n)          # read by the C restatement's OpenMP runtime when it loads
+    torch.set_num_threads(n)
+    return n
+
+
 def run_reference_arm(args, rank):
     if rank != 0:
         return
+    use_all_host_threads()
     cb, dt = time_cpu(args.steps, args.warmup)
     line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "TFLOP/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
@@ -397,6 +406,7 @@ def main():
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        use_all_host_threads()
         cpu_baseline, _ = time_cpu(steps=2, warmup=1)
 
     if rank == 0:

@@ -102,3 +102,18 @@ def test_shard_bounds():
     assert shard_bounds(28672, 8, 3) == (3 * 3584, 4 * 3584)
     with pytest.raises(ValueError):
         shard_bounds(100, 2, 0)
+
+
+def test_reference_import_names(native_lib):
+    """Code written against the reference package imports unchanged."""
+    import deepwell
+    from deepwell import cutlass_kernels
+    from deepwell.kernels import CutlassKernel, get_registry
+    from deepwell.kernels.cutlass_bindings import CUTLASS_AVAILABLE
+    from deepwell.kernels.registry import KernelSpec
+    from deepwell.optimizer import DeepwellOptimizer
+    import deepwell_b200
+    assert deepwell.optimize is deepwell_b200.optimize and CUTLASS_AVAILABLE
+    assert cutlass_kernels.BlackwellGemmKernel is deepwell_b200.cutlass_kernels.BlackwellGemmKernel
+    assert get_registry().find_kernel("gemm", "mxfp8", 100).name == "cutlass_sm100_mxfp8_gemm"
+    assert KernelSpec and CutlassKernel and DeepwellOptimizer
