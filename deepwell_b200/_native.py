@@ -29,6 +29,7 @@ ABI_SYMBOLS = (
     "dw_mxfp8_abi_version", "dw_mxfp8_device_supported", "dw_mxfp8_error_string", "dw_mxfp8_scale_bytes",
     "dw_mxfp8_quantize", "dw_mxfp8_quantize_both", "dw_mxfp8_dequantize", "dw_mxfp8_gemm",
     "dw_mxfp8_gemm_workspace", "dw_mxfp8_check_status", "dw_mxfp8_gemm_set_variant",
+    "dw_mxfp8_gemm_set_timing_buffer",
 )
 
 _lib = None
@@ -63,6 +64,7 @@ def load() -> ctypes.CDLL:
     L.dw_mxfp8_gemm_workspace.restype = sz
     L.dw_mxfp8_check_status.argtypes = [p, p]
     L.dw_mxfp8_gemm_set_variant.argtypes = [i32]
+    L.dw_mxfp8_gemm_set_timing_buffer.argtypes = [p, sz]
     _lib = L
     return L
 
@@ -180,10 +182,13 @@ def gemm(a_codes: torch.Tensor, a_sf: torch.Tensor, b_codes: torch.Tensor, b_sf:
     if bias is not None and (bias.dtype != torch.bfloat16 or bias.numel() != N or not bias.is_contiguous()):
         raise RuntimeError("bias must be a contiguous bfloat16 [N] tensor")
     sw = status_word(dev)
+    ws_bytes = int(load().dw_mxfp8_gemm_workspace(M, N, K))      # non-zero when the GEMM will split K
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev) if ws_bytes else None
     with torch.cuda.device(dev):
         check(load().dw_mxfp8_gemm(a_codes.data_ptr(), a_sf.data_ptr(), b_codes.data_ptr(), b_sf.data_ptr(),
                                    out.data_ptr(), None if bias is None else bias.data_ptr(), M, N, K,
-                                   float(alpha), float(beta), None, 0, sw.data_ptr(), _stream(dev)), "dw_mxfp8_gemm")
+                                   float(alpha), float(beta), None if ws is None else ws.data_ptr(), ws_bytes,
+                                   sw.data_ptr(), _stream(dev)), "dw_mxfp8_gemm")
     return out
 
 
@@ -199,5 +204,6 @@ def check_status(device=None) -> None:
         check(rc, f"GEMM kernel (status word {code & 0xFF}, CTA {code >> 8})")
 
 
-def set_gemm_variant(v: int) -> None:
-    check(load().dw_mxfp8_gemm_set_variant(int(v)), "dw_mxfp8_gemm_set_variant")
+def set_gemm_variant(v: int, group_m: int = 0, splits: int = 0) -> None:
+    """Kernel variant (0 = automatic), raster band height and split-K count for later GEMMs."""
+    check(load().dw_mxfp8_gemm_set_variant(int(v) | (int(group_m) << 8) | (int(splits) << 16)), "dw_mxfp8_gemm_set_variant")

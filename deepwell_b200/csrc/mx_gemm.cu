@@ -35,6 +35,11 @@ struct GemmParams {
     int64_t M, N, K;
     float alpha, beta;
     uint32_t tiles_m, tiles_n, num_tiles, num_kblocks, group_m;
+    // Split-K: the k-blocks of every tile are divided among `splits` work units (unit = tile +
+    // split * num_tiles); each unit leaves its raw fp32 accumulator in `partial` ([splits][M][N]) and
+    // mx_splitk_reduce_kernel sums them.  splits == 1: the epilogue writes D directly.
+    uint32_t splits, kb_per_split;
+    float* partial;
     // Optional tuning counters (the caller's workspace): per CTA, SM cycles each role spent waiting
     //   [0] producer: free stage       [1] MMA issuer: accumulator drained (two tiles back)
     //   [2] MMA issuer: shared accumulator columns drained (previous tile)
@@ -129,6 +134,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     const uint32_t tmem_base = *tmem_slot;
 
     const uint32_t num_workers = gridDim.x / kCtas, worker = blockIdx.x / kCtas;
+    const uint32_t num_units = p.num_tiles * p.splits;
     int err = 0;
     const bool timed = p.wait_cycles != nullptr;
     const long long t_begin = timed ? clock64() : 0;
@@ -161,18 +167,21 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             uint32_t empty_parity = 0;   // bit g: parity of the next wait on empty_bar(g), inverted
             const uint32_t full0 = (kCtas == 2) ? ptx::map_to_cta(full_bar(0), 0) : full_bar(0);   // leader's barrier
             const int nkb = static_cast<int>(p.num_kblocks);
-            for (uint32_t tile = worker; tile < p.num_tiles && !err; tile += num_workers) {
+            for (uint32_t unit = worker; unit < num_units && !err; unit += num_workers) {
+                const uint32_t split = unit / p.num_tiles, tile = unit - split * p.num_tiles;
                 uint32_t tm, tn;
                 tile_coords(tile, tm, tn);
                 const int row_a = static_cast<int>(tm * (128 * kCtas) + rank * 128);
                 const int row_b = static_cast<int>(tn * BN + rank * Cfg::kBRows);
                 const int sfa_row = static_cast<int>(tm * kCtas + rank) * nkb;
                 const int sfb_row = static_cast<int>(tn * Cfg::kSfbTiles) * nkb;
-                for (int kb0 = 0; kb0 < nkb && !err; kb0 += kStages) {
+                const int kb_first = static_cast<int>(split * p.kb_per_split);
+                const int kb_end = min(nkb, kb_first + static_cast<int>(p.kb_per_split));
+                for (int kb0 = kb_first; kb0 < kb_end && !err; kb0 += kStages) {
 #pragma unroll
                     for (int s = 0; s < kStages; ++s) {
                         const int kb = kb0 + s;
-                        if (kb < nkb && !err) {
+                        if (kb < kb_end && !err) {
                             if (s % kGroup == 0) {        // first stage of a group: wait until the group is free
                                 const int g = s / kGroup;
                                 if (!timed_wait(empty_bar(g), ((empty_parity >> g) & 1u) ^ 1u, 0)) { err = kErrProducer; continue; }
@@ -211,7 +220,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             const uint32_t sfa_lo0 = ptx::desc_lo_sf(stage_sfa(0)), sfb_lo0 = ptx::desc_lo_sf(stage_sfb(0));
             const uint32_t sf_t0 = tmem_base + Cfg::kSfBase;
             const int nkb = static_cast<int>(p.num_kblocks);
-            for (uint32_t tile = worker; tile < p.num_tiles && !err; tile += num_workers) {
+            for (uint32_t unit = worker; unit < num_units && !err; unit += num_workers) {
+                const uint32_t split = unit / p.num_tiles;
+                const int kb_first = static_cast<int>(split * p.kb_per_split);
+                const int kb_end = min(nkb, kb_first + static_cast<int>(p.kb_per_split));
                 // this accumulator fully drained (two tiles ago) ...
                 if (!timed_wait(acce_bar(acc), acc_phase ^ 1u, 0)) { err = kErrMmaAcc; break; }
                 // ... and the columns it shares with the other accumulator drained (previous tile)
@@ -220,10 +232,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 ptx::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * Cfg::kAccStride;
                 uint32_t accumulate = 0;
-                for (int kb0 = 0; kb0 < nkb && !err; kb0 += kStages) {
+                for (int kb0 = kb_first; kb0 < kb_end && !err; kb0 += kStages) {
 #pragma unroll
                     for (int s = 0; s < kStages; ++s) {
-                        if (kb0 + s < nkb && !err) {
+                        if (kb0 + s < kb_end && !err) {
                             if (!timed_wait(full_bar(s), (full_parity >> s) & 1u, 2)) { err = kErrMmaFull; continue; }
                             full_parity ^= 1u << s;
                             ptx::tc_fence_after();
@@ -246,7 +258,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                             // Last stage of a group (or of the tile): the group is free again once the MMAs
                             // issued so far have read it.  (Measured: releasing stages one at a time,
                             // kGroup = 1, is fastest; coarser groups lengthen the refill latency.)
-                            if (s % kGroup == kGroup - 1 || kb0 + s == nkb - 1) {
+                            if (s % kGroup == kGroup - 1 || kb0 + s == kb_end - 1) {
                                 const int g = s / kGroup;
                                 if (kCtas == 2) ptx::tc_commit_both(empty_bar(g)); else ptx::tc_commit(empty_bar(g));
                             }
@@ -268,7 +280,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         uint32_t acc = 0, acc_phase = 0;
         const bool vec_ok = (p.N % 8) == 0;
         constexpr int kChunks = BN / 32;
-        for (uint32_t tile = worker; tile < p.num_tiles && !err; tile += num_workers) {
+        for (uint32_t unit = worker; unit < num_units && !err; unit += num_workers) {
+            const uint32_t split = unit / p.num_tiles, tile = unit - split * p.num_tiles;
             uint32_t tm, tn;
             tile_coords(tile, tm, tn);
             const int64_t row = static_cast<int64_t>(tm) * (128 * kCtas) + rank * 128 + q * 32 + lane;
@@ -294,6 +307,18 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     }
                 }
                 const int64_t col = col0 + c;
+                if (p.splits > 1) {                      // split-K: raw fp32 partial sums, reduced afterwards
+                    if (row < p.M && col < p.N) {
+                        float* dst = p.partial + (static_cast<int64_t>(split) * p.M + row) * p.N + col;
+                        if ((p.N % 4) == 0 && col + 32 <= p.N) {
+#pragma unroll
+                            for (int v = 0; v < 8; ++v)
+                                *reinterpret_cast<uint4*>(dst + 4 * v) = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+                        } else {
+                            for (int i = 0; i < 32 && col + i < p.N; ++i) dst[i] = __uint_as_float(r[i]);
+                        }
+                    }
+                } else
                 if (row < p.M && col < p.N) {
                     uint16_t* dst = p.d + row * p.N + col;
                     if (vec_ok && col + 32 <= p.N) {
@@ -368,6 +393,36 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     if (warp == 1) {
         ptx::tc_fence_after();
         ptx::tmem_dealloc<kCtas>(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+// D = bf16(alpha * sum_s partial[s] + beta * D + bias): the second step of a split-K GEMM.
+__global__ void __launch_bounds__(256)
+mx_splitk_reduce_kernel(const float* __restrict__ partial, uint16_t* __restrict__ d, const uint16_t* __restrict__ bias,
+                        int64_t M, int64_t N, uint32_t splits, float alpha, float beta) {
+    const int64_t total = M * N, plane = M * N;
+    const bool vec = (N % 4) == 0;
+    const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x * 4;
+    for (int64_t i = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) * 4; i < total; i += step) {
+        float f[4] = {0.f, 0.f, 0.f, 0.f};
+        const int n = vec ? 4 : static_cast<int>(total - i < 4 ? total - i : 4);
+        for (uint32_t s = 0; s < splits; ++s) {
+            const float* src = partial + s * plane + i;
+            if (vec) {
+                const float4 v = *reinterpret_cast<const float4*>(src);
+                f[0] += v.x; f[1] += v.y; f[2] += v.z; f[3] += v.w;
+            } else {
+                for (int j = 0; j < n; ++j) f[j] += src[j];
+            }
+        }
+        for (int j = 0; j < n; ++j) {
+            float v = alpha * f[j];
+            if (beta != 0.0f) v += beta * __uint_as_float(static_cast<uint32_t>(d[i + j]) << 16);
+            if (bias != nullptr) v += __uint_as_float(static_cast<uint32_t>(bias[(i + j) % N]) << 16);
+            uint32_t o;
+            asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o) : "f"(0.0f), "f"(v));
+            d[i + j] = static_cast<uint16_t>(o & 0xFFFFu);
+        }
     }
 }
 
@@ -449,7 +504,9 @@ static int launch_gemm(const void* a, const void* a_sf, const void* b, const voi
     });
     if (attr_err != cudaSuccess) return DW_ERR_LAUNCH;
 
-    const int workers = std::min<int64_t>(p.num_tiles, sm_count() / kCtas);
+    p.kb_per_split = (p.num_kblocks + p.splits - 1) / p.splits;
+    p.splits = (p.num_kblocks + p.kb_per_split - 1) / p.kb_per_split;      // every split owns at least one k-block
+    const int workers = std::min<int64_t>(static_cast<int64_t>(p.num_tiles) * p.splits, sm_count() / kCtas);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(workers * kCtas));
     cfg.blockDim = dim3(192);
@@ -464,6 +521,65 @@ static int launch_gemm(const void* a, const void* a_sf, const void* b, const voi
         cudaGetLastError();
         return DW_ERR_LAUNCH;
     }
+    if (p.splits > 1) {
+        const int64_t quads = (p.M * p.N + 3) / 4;
+        const int grid = static_cast<int>(std::min<int64_t>((quads + 255) / 256, static_cast<int64_t>(sm_count()) * 8));
+        mx_splitk_reduce_kernel<<<grid, 256, 0, st>>>(p.partial, p.d, p.bias, p.M, p.N, p.splits, p.alpha, p.beta);
+        if (cudaGetLastError() != cudaSuccess) return DW_ERR_LAUNCH;
+    }
+    return DW_OK;
+}
+
+// Kernel variant and split count for a problem.  Split-K is chosen when the output has too few
+// tiles to occupy the GPU and K is long (weight-gradient GEMMs: small N x K output, contraction over
+// all tokens).
+struct GemmPlan { int variant; uint32_t splits; size_t ws_bytes; };
+static int g_splits = 0;   // forced split count (0 = automatic)
+
+static GemmPlan plan_gemm(int64_t M, int64_t N, int64_t K) {
+    GemmPlan pl;
+    pl.variant = g_variant != 0 ? g_variant : ((N <= 128) ? 1 : (M <= 128 ? 2 : 3));
+    const int ctas = (pl.variant >= 3) ? 2 : 1, bn = (pl.variant == 1 || pl.variant == 4) ? 128 : 256;
+    const int64_t tiles = ((M + 128 * ctas - 1) / (128 * ctas)) * ((N + bn - 1) / bn);
+    const int64_t workers = sm_count() / ctas, nkb = (K + 127) / 128;
+    int64_t splits = 1;
+    if (g_splits > 0) splits = std::min<int64_t>(g_splits, nkb);
+    // measured on B200: worth it only below a quarter of the GPU (the reduction pass costs ~10 us)
+    else if (tiles * 4 <= workers && nkb >= 32) splits = std::max<int64_t>(1, std::min<int64_t>({workers / tiles, nkb / 16, 4}));
+    pl.splits = static_cast<uint32_t>(splits);
+    pl.ws_bytes = splits > 1 ? static_cast<size_t>(splits) * M * N * sizeof(float) : 0;
+    return pl;
+}
+
+static long long* g_timing = nullptr;   // optional per-CTA wait counters (dw_mxfp8_gemm_set_timing_buffer)
+
+static int run_gemm(const void* a_codes, const void* a_sf, const void* b_codes, const void* b_sf, void* d_bf16,
+                    const void* bias_bf16, int64_t M, int64_t N, int64_t K, float alpha, float beta, int variant,
+                    uint32_t splits, float* partial, void* status_word, cudaStream_t st) {
+    GemmParams p = {};
+    p.d = static_cast<uint16_t*>(d_bf16);
+    p.bias = static_cast<const uint16_t*>(bias_bf16);
+    p.status = static_cast<int*>(status_word);
+    p.M = M; p.N = N; p.K = K; p.alpha = alpha; p.beta = beta;
+    p.splits = splits; p.partial = partial;
+    p.wait_cycles = g_timing;
+    switch (variant) {
+        case 1: return launch_gemm<128, 1, 1>(a_codes, a_sf, b_codes, b_sf, p, st);
+        case 2: return launch_gemm<256, 1, 1>(a_codes, a_sf, b_codes, b_sf, p, st);
+        case 3: return launch_gemm<256, 2, 1>(a_codes, a_sf, b_codes, b_sf, p, st);
+        default: return launch_gemm<128, 2, 1>(a_codes, a_sf, b_codes, b_sf, p, st);
+    }
+}
+
+static int check_gemm_args(const void* a_codes, const void* a_sf, const void* b_codes, const void* b_sf, const void* d_bf16,
+                           const void* bias_bf16, int64_t M, int64_t N, int64_t K) {
+    if (!a_codes || !a_sf || !b_codes || !b_sf || !d_bf16) return DW_ERR_BAD_ARG;
+    if (K == 0 || K % 32 != 0) return DW_ERR_BAD_ARG;
+    auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+    if (!al16(a_codes) || !al16(b_codes) || !al16(a_sf) || !al16(b_sf) || !al16(d_bf16)) return DW_ERR_BAD_ARG;
+    if (bias_bf16 && !al16(bias_bf16)) return DW_ERR_BAD_ARG;
+    if (M >= (1ll << 31) || N >= (1ll << 31) || K >= (1ll << 31)) return DW_ERR_TOO_LARGE;
+    if (encode_fn() == nullptr) return DW_ERR_LAUNCH;
     return DW_OK;
 }
 
@@ -472,49 +588,41 @@ static int launch_gemm(const void* a, const void* a_sf, const void* b, const voi
 using namespace dw;
 
 extern "C" DW_API int dw_mxfp8_gemm_set_variant(int variant) {
-    // bits [0,8): kernel variant; bits [8,16): row tiles per raster band (0 = default)
-    const int v = variant & 0xFF, gm = (variant >> 8) & 0xFF;
+    // bits [0,8): kernel variant; bits [8,16): row tiles per raster band; bits [16,24): split-K count (0 = automatic)
+    const int v = variant & 0xFF, gm = (variant >> 8) & 0xFF, sp = (variant >> 16) & 0xFF;
     if (variant < 0 || v > 4) return DW_ERR_BAD_ARG;
     g_variant = v;
     g_group_m = gm;
+    g_splits = sp;
     return DW_OK;
 }
 
-extern "C" DW_API size_t dw_mxfp8_gemm_workspace(int64_t, int64_t, int64_t) { return 0; }
+extern "C" DW_API int dw_mxfp8_gemm_set_timing_buffer(void* device_buffer, size_t bytes) {
+    if (device_buffer != nullptr && (bytes < DW_GEMM_TIMING_BYTES || (reinterpret_cast<uintptr_t>(device_buffer) & 7) != 0))
+        return DW_ERR_BAD_ARG;
+    g_timing = static_cast<long long*>(device_buffer);
+    return DW_OK;
+}
 
-// A workspace of at least this many bytes switches the per-CTA wait counters on.
-static constexpr size_t kTimingBytes = 296 * kWaitCounters * sizeof(long long);
+extern "C" DW_API size_t dw_mxfp8_gemm_workspace(int64_t M, int64_t N, int64_t K) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    return plan_gemm(M, N, K).ws_bytes;
+}
 
 extern "C" DW_API int dw_mxfp8_gemm(const void* a_codes, const void* a_sf, const void* b_codes, const void* b_sf, void* d_bf16,
                              const void* bias_bf16, int64_t M, int64_t N, int64_t K, float alpha, float beta, void* workspace,
                              size_t workspace_bytes, void* status_word, void* stream) {
     if (M < 0 || N < 0 || K < 0) return DW_ERR_BAD_ARG;
     if (M == 0 || N == 0) return DW_OK;
-    if (!a_codes || !a_sf || !b_codes || !b_sf || !d_bf16) return DW_ERR_BAD_ARG;
-    if (K == 0 || K % 32 != 0) return DW_ERR_BAD_ARG;
-    auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
-    if (!al16(a_codes) || !al16(b_codes) || !al16(a_sf) || !al16(b_sf) || !al16(d_bf16)) return DW_ERR_BAD_ARG;
-    if (bias_bf16 && !al16(bias_bf16)) return DW_ERR_BAD_ARG;
-    if (M >= (1ll << 31) || N >= (1ll << 31) || K >= (1ll << 31)) return DW_ERR_TOO_LARGE;
-    if (encode_fn() == nullptr) return DW_ERR_LAUNCH;
-
-    GemmParams p = {};
-    p.d = static_cast<uint16_t*>(d_bf16);
-    p.bias = static_cast<const uint16_t*>(bias_bf16);
-    p.status = static_cast<int*>(status_word);
-    p.M = M; p.N = N; p.K = K; p.alpha = alpha; p.beta = beta;
-    p.wait_cycles = (workspace != nullptr && workspace_bytes >= kTimingBytes &&
-                     (reinterpret_cast<uintptr_t>(workspace) & 7) == 0) ? static_cast<long long*>(workspace) : nullptr;
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-
-    int v = g_variant;
-    if (v == 0) v = (N <= 128) ? 1 : (M <= 128 ? 2 : 3);
-    switch (v) {
-        case 1: return launch_gemm<128, 1, 1>(a_codes, a_sf, b_codes, b_sf, p, st);
-        case 2: return launch_gemm<256, 1, 1>(a_codes, a_sf, b_codes, b_sf, p, st);
-        case 3: return launch_gemm<256, 2, 1>(a_codes, a_sf, b_codes, b_sf, p, st);
-        default: return launch_gemm<128, 2, 1>(a_codes, a_sf, b_codes, b_sf, p, st);
-    }
+    const int rc = check_gemm_args(a_codes, a_sf, b_codes, b_sf, d_bf16, bias_bf16, M, N, K);
+    if (rc != DW_OK) return rc;
+    GemmPlan pl = plan_gemm(M, N, K);
+    // without a large enough, 16-byte aligned workspace the GEMM runs unsplit
+    if (pl.splits > 1 && (workspace == nullptr || workspace_bytes < pl.ws_bytes ||
+                          (reinterpret_cast<uintptr_t>(workspace) & 15) != 0))
+        pl.splits = 1;
+    return run_gemm(a_codes, a_sf, b_codes, b_sf, d_bf16, bias_bf16, M, N, K, alpha, beta, pl.variant, pl.splits,
+                    static_cast<float*>(workspace), status_word, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" DW_API int dw_mxfp8_check_status(const void* status_word, void* stream) {

@@ -19,6 +19,7 @@
 // All arithmetic is on bit patterns; no fast-math; results are bit-exact against the oracle.
 
 #include <algorithm>
+#include <mutex>
 
 #include "dw_common.cuh"
 
@@ -139,36 +140,64 @@ __global__ void mx_sf_pad_kernel(uint8_t* __restrict__ scales, int64_t rows, int
 // Tile kernel: column-wise transposed payload, optionally fused with the row-wise form.
 // rows % 32 == 0, cols % 32 == 0.  CTA = 256 threads, tile = 128 rows x 128 cols.
 // ------------------------------------------------------------------------------------------
+constexpr int kTileSmemBytes = 2 * 128 * 16 * 16 + 1024;   // two 32 KB tiles + two 512-byte scale staging areas
+
 template <bool kDoRow, bool kDoCol>
 __global__ void __launch_bounds__(256)
 mx_quant_tile_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes_row, uint8_t* __restrict__ scales_row,
                      uint8_t* __restrict__ codes_col_t, uint8_t* __restrict__ scales_col, int64_t rows, int64_t cols,
-                     uint32_t tiles_c, int rule, int layout) {
-    __shared__ __align__(16) uint4 tile[128][16];
-    __shared__ __align__(16) uint8_t sf_row[512];
-    __shared__ __align__(16) uint8_t sf_col[512];
+                     uint32_t tiles_c, uint32_t num_tiles, int rule, int layout) {
+    // Persistent CTA, two tile buffers: the 16-byte cp.async copies of the next tile are in flight
+    // while this tile is quantised, so the SM always has loads outstanding.
+    extern __shared__ __align__(16) uint8_t tile_smem[];
+    typedef uint4 (*TilePtr)[16];
+    uint8_t* sf_row = tile_smem + 2 * 128 * 16 * 16;
+    uint8_t* sf_col = sf_row + 512;
 
     const uint32_t t = threadIdx.x;
-    const uint32_t tr = blockIdx.x / tiles_c, tc = blockIdx.x - tr * tiles_c;
-    const int64_t r0 = static_cast<int64_t>(tr) * 128, c0 = static_cast<int64_t>(tc) * 128;
+    const uint32_t cc = t & 15u;
     const int64_t kb_row = cols >> 5, kb_col = rows >> 5;           // k-blocks per operand row
     const int64_t kt_row = (kb_row + 3) >> 2, kt_col = (kb_col + 3) >> 2;
 
-    // ---- load 8 chunks of 8 elements per thread; all loads issued before any use ----
-    const uint32_t cc = t & 15u;
-    const int64_t gc = c0 + cc * 8;
-    uint4 v[8];
+    auto issue_tile = [&](uint32_t id, int buf) {
+        const uint32_t itr = id / tiles_c, itc = id - itr * tiles_c;
+        const int64_t ir0 = static_cast<int64_t>(itr) * 128, igc = static_cast<int64_t>(itc) * 128 + cc * 8;
+        TilePtr dst = reinterpret_cast<TilePtr>(tile_smem + buf * (128 * 16 * 16));
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const int64_t gr = r0 + (t >> 4) + 16 * j;
-        v[j] = (gr < rows && gc < cols) ? ldg_nc_v4(x + gr * cols + gc) : make_uint4(0, 0, 0, 0);
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t row = (t >> 4) + 16 * j;
+            const int64_t gr = ir0 + row;
+            const bool ok = gr < rows && igc < cols;
+            const uint16_t* src = ok ? x + gr * cols + igc : x;          // out of range: zero fill, nothing read
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+                         ::"r"(smem_u32(&dst[row][cc])), "l"(src), "r"(ok ? 16 : 0) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    int buf = 0;
+    if (blockIdx.x < num_tiles) issue_tile(blockIdx.x, 0);
+    for (uint32_t id = blockIdx.x; id < num_tiles; id += gridDim.x, buf ^= 1) {
+    const uint32_t next = id + gridDim.x;
+    if (next < num_tiles) {
+        issue_tile(next, buf ^ 1);
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
+    __syncthreads();
+    TilePtr tile = reinterpret_cast<TilePtr>(tile_smem + buf * (128 * 16 * 16));
+    const uint32_t tr = id / tiles_c, tc = id - tr * tiles_c;
+    const int64_t r0 = static_cast<int64_t>(tr) * 128, c0 = static_cast<int64_t>(tc) * 128;
+    const int64_t gc = c0 + cc * 8;
+
+    if (kDoRow) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
         const uint32_t row = (t >> 4) + 16 * j;
-        if (kDoCol) tile[row][cc] = v[j];
-        if (kDoRow) {
-            const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+        {
+            const uint4 v = tile[row][cc];
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
             uint32_t m2 = amax_words(w);
             m2 = absmax_bf16x2(m2, __shfl_xor_sync(0xFFFFFFFFu, m2, 1));
             m2 = absmax_bf16x2(m2, __shfl_xor_sync(0xFFFFFFFFu, m2, 2));
@@ -183,6 +212,7 @@ mx_quant_tile_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes
         }
     }
     __syncthreads();
+    }
 
     if (kDoRow) {  // scales of the row-wise operand [rows, cols/32]
         if (layout == DW_SF_TILED) {
@@ -259,6 +289,8 @@ mx_quant_tile_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes
                     if (kb0 + b < kb_col) scales_col[gcl * kb_col + kb0 + b] = sf_col[(t & 31u) * 16 + (t >> 5) * 4 + b];
             }
         }
+    }
+    __syncthreads();   // every read of this buffer and of the staging areas is done before they are reused
     }
 }
 
@@ -398,6 +430,22 @@ static int quantize_row_fast(const uint16_t* x, uint8_t* codes, uint8_t* scales,
     return launch_status();
 }
 
+template <bool kDoRow, bool kDoCol>
+static int launch_tile_kernel(const uint16_t* x, uint8_t* cr, uint8_t* sr, uint8_t* ct, uint8_t* sc, int64_t rows, int64_t cols,
+                              uint32_t tiles_c, uint32_t tiles, int rule, int layout, cudaStream_t st) {
+    static std::once_flag once;
+    static cudaError_t attr_err = cudaSuccess;
+    std::call_once(once, [] {
+        attr_err = cudaFuncSetAttribute(mx_quant_tile_kernel<kDoRow, kDoCol>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        kTileSmemBytes);
+    });
+    if (attr_err != cudaSuccess) return DW_ERR_LAUNCH;
+    const uint32_t grid = std::min<uint32_t>(tiles, static_cast<uint32_t>(num_sms()) * 3u);   // 3 CTAs of 65 KB per SM
+    mx_quant_tile_kernel<kDoRow, kDoCol><<<grid, 256, kTileSmemBytes, st>>>(x, cr, sr, ct, sc, rows, cols, tiles_c, tiles, rule,
+                                                                           layout);
+    return launch_status();
+}
+
 static bool tile_path_ok(const void* x, int64_t rows, int64_t cols) {
     const int64_t tiles = ((rows + 127) / 128) * ((cols + 127) / 128);
     return rows % 32 == 0 && cols % 32 == 0 && aligned(x, 16) && tiles < (1ll << 31);
@@ -435,9 +483,7 @@ extern "C" DW_API int dw_mxfp8_quantize(const void* x_bf16, void* codes, void* s
         (scale_layout == DW_SF_FLAT || aligned(s, 16))) {
         const uint32_t tiles_c = static_cast<uint32_t>((cols + 127) / 128);
         const uint32_t tiles = static_cast<uint32_t>((rows + 127) / 128) * tiles_c;
-        mx_quant_tile_kernel<false, true><<<tiles, 256, 0, st>>>(x, nullptr, nullptr, c, s, rows, cols, tiles_c, scale_rule,
-                                                                 scale_layout);
-        return launch_status();
+        return launch_tile_kernel<false, true>(x, nullptr, nullptr, c, s, rows, cols, tiles_c, tiles, scale_rule, scale_layout, st);
     }
     return quantize_generic(x, c, s, rows, cols, direction, scale_rule, scale_layout, st);
 }
@@ -464,11 +510,10 @@ extern "C" DW_API int dw_mxfp8_quantize_both(const void* x_bf16, void* codes_row
         (scale_layout == DW_SF_FLAT || (aligned(scales_row, 16) && aligned(scales_col, 16)))) {
         const uint32_t tiles_c = static_cast<uint32_t>((cols + 127) / 128);
         const uint32_t tiles = static_cast<uint32_t>((rows + 127) / 128) * tiles_c;
-        mx_quant_tile_kernel<true, true><<<tiles, 256, 0, st>>>(
-            static_cast<const uint16_t*>(x_bf16), static_cast<uint8_t*>(codes_row), static_cast<uint8_t*>(scales_row),
-            static_cast<uint8_t*>(codes_col_t), static_cast<uint8_t*>(scales_col), rows, cols, tiles_c, scale_rule,
-            scale_layout);
-        return launch_status();
+        return launch_tile_kernel<true, true>(static_cast<const uint16_t*>(x_bf16), static_cast<uint8_t*>(codes_row),
+                                              static_cast<uint8_t*>(scales_row), static_cast<uint8_t*>(codes_col_t),
+                                              static_cast<uint8_t*>(scales_col), rows, cols, tiles_c, tiles, scale_rule,
+                                              scale_layout, st);
     }
     int rc = dw_mxfp8_quantize(x_bf16, codes_row, scales_row, rows, cols, DW_DIR_ROW, scale_rule, scale_layout, stream);
     if (rc != DW_OK) return rc;

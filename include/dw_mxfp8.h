@@ -84,14 +84,13 @@ int dw_mxfp8_dequantize(const void *codes, const void *scales, void *out_bf16, i
  * Replaces launch_blackwell_mxfp8_gemm (csrc/blackwell_gemm_kernel.cu:103-156) and the MXFP8
  * branch of BlackwellGemmKernel::gemm (csrc/cutlass_kernels.cpp:173-204), which allocated and
  * freed two scale buffers per call and ran a bf16 cuBLAS GEMM.
- * K % 32 == 0; a_codes, b_codes, d 16-byte aligned.  workspace: the kernel needs none
- * (dw_mxfp8_gemm_workspace is 0, NULL is fine); a caller that passes >= DW_GEMM_TIMING_BYTES
- * gets per-CTA tuning counters there: 8 int64 per CTA, SM cycles the producer, MMA-issuer and
- * epilogue roles spent waiting ([0] free stage, [1] accumulator drained, [2] shared accumulator
- * columns drained, [3] operand data, [4] accumulator finished, [7] kernel cycles).
+ * K % 32 == 0; a_codes, b_codes, d 16-byte aligned.
+ * workspace: dw_mxfp8_gemm_workspace(M, N, K) bytes, 16-byte aligned.  It is non-zero when the
+ * output has too few tiles to fill the GPU and K is long (weight-gradient shapes): the GEMM then
+ * splits K, leaves fp32 partial sums in the workspace and reduces them in a second kernel.  With
+ * NULL or too small a workspace the GEMM runs unsplit (same result within rounding).
  * status_word: optional device int32, set non-zero by the kernel if a bounded wait expires
  * (then read it with dw_mxfp8_check_status). */
-#define DW_GEMM_TIMING_BYTES (296 * 8 * 8)
 int dw_mxfp8_gemm(const void *a_codes, const void *a_sf, const void *b_codes, const void *b_sf,
                   void *d_bf16, const void *bias_bf16, int64_t M, int64_t N, int64_t K, float alpha,
                   float beta, void *workspace, size_t workspace_bytes, void *status_word, void *stream);
@@ -102,8 +101,17 @@ size_t dw_mxfp8_gemm_workspace(int64_t M, int64_t N, int64_t K);
 /* Synchronises `stream`, reads the status word; DW_OK or DW_ERR_DEVICE_STATUS. */
 int dw_mxfp8_check_status(const void *status_word, void *stream);
 
-/* Selects the GEMM kernel variant for later dw_mxfp8_gemm calls in this process
- * (0 = automatic).  Counterpart of BlackwellGemmKernel::set_cluster_shape /
+/* Tuning aid: per-CTA counters of the SM cycles the GEMM's producer, MMA-issuer and epilogue
+ * roles spent waiting, written by every later dw_mxfp8_gemm launch of this process into
+ * `device_buffer` (8 int64 per CTA: [0] free stage, [1] accumulator drained, [2] shared accumulator
+ * columns drained, [3] operand data, [4] accumulator finished, [7] kernel cycles).  NULL switches
+ * them off.  No counterpart in the reference (its profile_kernel returns constants,
+ * csrc/python_bindings.cpp:244-255). */
+#define DW_GEMM_TIMING_BYTES (296 * 8 * 8)
+int dw_mxfp8_gemm_set_timing_buffer(void *device_buffer, size_t bytes);
+
+/* Selects the GEMM kernel variant (bits 0-7), raster band height (bits 8-15) and split-K count
+ * (bits 16-23) for later dw_mxfp8_gemm calls in this process (0 = automatic).  Counterpart of BlackwellGemmKernel::set_cluster_shape /
  * enable_tmem_residency, csrc/cutlass_kernels.cpp:265-272 (flags the reference stores and ignores). */
 int dw_mxfp8_gemm_set_variant(int variant);
 

@@ -121,6 +121,43 @@ def test_model_shapes_sampled(nv, variant, M, N, K):
     assert torch.equal((y.float() * 2).bfloat16().view(torch.int16), y2.view(torch.int16))   # exact: power-of-two alpha
 
 
+@pytest.mark.parametrize("variant", VARIANTS)
+@pytest.mark.parametrize("splits", [2, 3, 8])
+def test_split_k_forced(nv, variant, splits):
+    """K divided among work units, fp32 partial sums in the workspace, second-pass reduction."""
+    nv.set_gemm_variant(variant, splits=splits)
+    try:
+        run(nv, 384, 512, 2048, alpha=0.5, beta=2.0, use_bias=True)
+        run(nv, 300, 200, 1152)                 # ragged tiles; 9 k-blocks do not divide by 2 or 8
+        run(nv, 130, 100, 640)                  # N % 4 != 0: scalar partial stores and reduction
+    finally:
+        nv.set_gemm_variant(0)
+
+
+def test_split_k_automatic_for_weight_gradient_shapes(nv, native_lib):
+    """Small outputs with a long contraction (weight gradients of narrow layers over many tokens): the
+    planner splits K when the tiles would occupy less than a quarter of the GPU."""
+    nv.set_gemm_variant(0)
+    assert native_lib.dw_mxfp8_gemm_workspace(1024, 1024, 16384) == 4 * 1024 * 1024 * 4
+    assert native_lib.dw_mxfp8_gemm_workspace(3072, 768, 8192) == 0        # GPT-2-small wgrad: half the GPU, unsplit
+    assert native_lib.dw_mxfp8_gemm_workspace(16384, 4096, 4096) == 0
+    run(nv, 1024, 1024, 16384)
+    run(nv, 3072, 768, 8192)
+    run(nv, 768, 3072, 8192)
+    # same operands, split and unsplit, agree to bf16 rounding of the same fp32 sums
+    g = torch.Generator("cpu").manual_seed(5)
+    a = torch.randn(768, 16384, generator=g).bfloat16().cuda()
+    b = torch.randn(1024, 16384, generator=g).bfloat16().cuda()
+    ac, asf = nv.quantize(a, nv.DIR_ROW, 0, nv.SF_TILED)
+    bc, bsf = nv.quantize(b, nv.DIR_ROW, 0, nv.SF_TILED)
+    y_split = nv.gemm(ac, asf, bc, bsf)
+    nv.set_gemm_variant(0, splits=1)
+    y_one = nv.gemm(ac, asf, bc, bsf)
+    nv.set_gemm_variant(0)
+    nv.check_status()
+    assert_close(y_split.cpu(), y_one.float().cpu())
+
+
 def test_backward_operand_forms(nv):
     """dgrad and wgrad through column-wise (transposed) operands: contraction over N and over M."""
     nv.set_gemm_variant(0)
