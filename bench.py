@@ -176,8 +176,7 @@ def run_reference_arm(args, rank):
 # small single-kernel cases for profiler captures (inputs larger than L2, well under 1 GB)
 # ----------------------------------------------------------------------------------------------
 def run_profile_case(args):
-    from deepwell_b200 import _build, _native as nv
-    _build.build()
+    from deepwell_b200 import _native as nv
     L = nv.load()
     nv.set_gemm_variant(args.variant)
     dev = torch.device("cuda", 0)
@@ -252,7 +251,7 @@ def main():
         return
 
     import torch.distributed as dist
-    from deepwell_b200 import _build, _native as nv
+    from deepwell_b200 import _native as nv
     from deepwell_b200 import cutlass_kernels as ck
     from deepwell_b200.sharded import shard_bounds
 
@@ -263,7 +262,6 @@ def main():
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
-    _build.build()
     L = nv.load()
     if L.dw_mxfp8_device_supported(local_rank) != 1:
         raise SystemExit("device is not sm_100 (B200)")

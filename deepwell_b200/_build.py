@@ -1,6 +1,9 @@
 """Builds the C-ABI shared library (CUDA kernels for sm_100a) in-tree with nvcc.
 
-    python -m deepwell_b200._build [--force] [--verbose]
+    python deepwell_b200/_build.py [--force] [--verbose]      (or: python -m deepwell_b200._build)
+
+The file imports nothing from the package, so it can be run (or loaded by path) while the library
+is missing or stale.
 
 Output: deepwell_b200/lib/libdw_mxfp8.so.  nvcc cross-compiles without a GPU.
 """

@@ -29,7 +29,7 @@ ABI_SYMBOLS = (
     "dw_mxfp8_abi_version", "dw_mxfp8_device_supported", "dw_mxfp8_error_string", "dw_mxfp8_scale_bytes",
     "dw_mxfp8_quantize", "dw_mxfp8_quantize_both", "dw_mxfp8_dequantize", "dw_mxfp8_gemm",
     "dw_mxfp8_gemm_workspace", "dw_mxfp8_check_status", "dw_mxfp8_gemm_set_variant",
-    "dw_mxfp8_gemm_set_timing_buffer",
+    "dw_mxfp8_gemm_set_timing_buffer", "dw_mxfp8_gemm_splitk_static",
 )
 
 _lib = None
@@ -49,6 +49,10 @@ def load() -> ctypes.CDLL:
             f"{LIB_PATH} is missing: build it with `python -m deepwell_b200._build` "
             "(nvcc, sm_100a).  There is no fallback path.")
     L = ctypes.CDLL(LIB_PATH)
+    missing = [name for name in ABI_SYMBOLS if not hasattr(L, name)]
+    if missing:
+        raise NativeLibraryError(f"{LIB_PATH} is older than the sources (no {missing[0]}): rebuild it with "
+                                 "`python deepwell_b200/_build.py`")
     p, i64, i32, f32, sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_float, ctypes.c_size_t
     L.dw_mxfp8_abi_version.restype = i32
     L.dw_mxfp8_device_supported.argtypes = [i32]
@@ -65,6 +69,7 @@ def load() -> ctypes.CDLL:
     L.dw_mxfp8_check_status.argtypes = [p, p]
     L.dw_mxfp8_gemm_set_variant.argtypes = [i32]
     L.dw_mxfp8_gemm_set_timing_buffer.argtypes = [p, sz]
+    L.dw_mxfp8_gemm_splitk_static.argtypes = [p, p, p, p, p, p, i64, i64, i64, f32, f32, i32, p, p]
     _lib = L
     return L
 

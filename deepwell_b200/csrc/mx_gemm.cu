@@ -625,6 +625,55 @@ extern "C" DW_API int dw_mxfp8_gemm(const void* a_codes, const void* a_sf, const
                     static_cast<float*>(workspace), status_word, static_cast<cudaStream_t>(stream));
 }
 
+// ------------------------------------------------------------------------------------------
+// Split-K GEMM for callers that cannot allocate: the fp32 partial sums live in a fixed array that
+// is part of the library image on every device that loads it (DW_GEMM_STATIC_SCRATCH_BYTES each).
+// ------------------------------------------------------------------------------------------
+namespace dw {
+constexpr size_t kStaticScratchFloats = DW_GEMM_STATIC_SCRATCH_BYTES / sizeof(float);
+static __device__ __align__(256) float g_splitk_scratch[kStaticScratchFloats];
+
+// In host code `g_splitk_scratch` is only a handle for the runtime, not an address a kernel can use.
+// The device address is looked up once per device, with that device current.
+static int static_scratch_address(float** out) {
+    constexpr int kMaxDevices = 64;
+    static std::mutex mu;
+    static float* cached[kMaxDevices] = {};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return DW_ERR_LAUNCH;
+    std::lock_guard<std::mutex> lock(mu);
+    if (cached[dev] == nullptr) {
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_splitk_scratch) != cudaSuccess || ptr == nullptr) {
+            cudaGetLastError();
+            return DW_ERR_LAUNCH;
+        }
+        cached[dev] = static_cast<float*>(ptr);
+    }
+    *out = cached[dev];
+    return DW_OK;
+}
+}  // namespace dw
+
+extern "C" DW_API int dw_mxfp8_gemm_splitk_static(const void* a_codes, const void* a_sf, const void* b_codes, const void* b_sf,
+                                                  void* d_bf16, const void* bias_bf16, int64_t M, int64_t N, int64_t K,
+                                                  float alpha, float beta, int splits, void* status_word, void* stream) {
+    if (M < 0 || N < 0 || K < 0 || splits < 2 || splits > 255) return DW_ERR_BAD_ARG;
+    if (M == 0 || N == 0) return DW_OK;
+    const int rc = check_gemm_args(a_codes, a_sf, b_codes, b_sf, d_bf16, bias_bf16, M, N, K);
+    if (rc != DW_OK) return rc;
+    const int64_t nkb = (K + 127) / 128;
+    const int64_t eff = std::min<int64_t>(splits, nkb);                        // the kernel never uses more
+    if (static_cast<uint64_t>(eff) * static_cast<uint64_t>(M) * static_cast<uint64_t>(N) > kStaticScratchFloats)
+        return DW_ERR_TOO_LARGE;
+    float* scratch = nullptr;
+    const int arc = static_scratch_address(&scratch);
+    if (arc != DW_OK) return arc;
+    const int variant = plan_gemm(M, N, K).variant;
+    return run_gemm(a_codes, a_sf, b_codes, b_sf, d_bf16, bias_bf16, M, N, K, alpha, beta, variant,
+                    static_cast<uint32_t>(eff), scratch, status_word, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" DW_API int dw_mxfp8_check_status(const void* status_word, void* stream) {
     if (!status_word) return DW_ERR_BAD_ARG;
     int host = 0;

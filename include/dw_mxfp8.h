@@ -98,6 +98,34 @@ int dw_mxfp8_gemm(const void *a_codes, const void *a_sf, const void *b_codes, co
 /* Replaces BlackwellGemmKernel::get_workspace_size, csrc/cutlass_kernels.cpp:229-231. */
 size_t dw_mxfp8_gemm_workspace(int64_t M, int64_t N, int64_t K);
 
+/* Split-K GEMM that allocates nothing and needs no workspace from the caller.  No counterpart in
+ * the reference.
+ *
+ * Some callers of this library may not (or cannot) obtain device memory at the moment they need a
+ * GEMM: an operator running inside a serving engine that has already handed all free HBM to its
+ * own pool and forbids cudaMalloc after warm-up, a plugin called under a lock the allocator also
+ * takes, a host language binding with no access to the framework's caching allocator.  dw_mxfp8_gemm
+ * asks such a caller for a workspace when it splits K; this entry point instead keeps the fp32
+ * partial sums in an array that is part of the library itself: DW_GEMM_STATIC_SCRATCH_BYTES of
+ * device memory on every GPU that loads the library, held until the process exits.
+ *
+ * Same arithmetic and operands as dw_mxfp8_gemm, with K divided among `splits` (2..255; never more
+ * than ceil(K/128)) groups of thread blocks and a second kernel summing the partial results.
+ * Limits and rules:
+ *   - min(splits, ceil(K/128)) * M * N * 4 bytes must fit in the array, else DW_ERR_TOO_LARGE and
+ *     nothing is launched;
+ *   - the first call on each device looks up the array's device address (with that device current)
+ *     and caches it, so make that first call outside any stream capture;
+ *   - all calls on a device share the one array and it keeps whatever the last call left there.
+ *     Nothing in it has to start at zero (every element the reduction reads is written by the
+ *     same call first), but two calls that overlap on the GPU (different streams, or different
+ *     host threads without ordering) race on it: serialise them;
+ *   - it calls no cudaMalloc / cudaFree and no allocating library routine. */
+#define DW_GEMM_STATIC_SCRATCH_BYTES (32u * 1024u * 1024u)
+int dw_mxfp8_gemm_splitk_static(const void *a_codes, const void *a_sf, const void *b_codes, const void *b_sf,
+                                void *d_bf16, const void *bias_bf16, int64_t M, int64_t N, int64_t K, float alpha,
+                                float beta, int splits, void *status_word, void *stream);
+
 /* Synchronises `stream`, reads the status word; DW_OK or DW_ERR_DEVICE_STATUS. */
 int dw_mxfp8_check_status(const void *status_word, void *stream);
 

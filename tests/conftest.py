@@ -14,11 +14,20 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a B200 (sm_100a) GPU; the parity tests proper")
 
 
+def load_build_module():
+    """deepwell_b200/_build.py loaded by path (importing the package needs an up-to-date library)."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("_dw_build", os.path.join(ROOT, "deepwell_b200", "_build.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
 @pytest.fixture(scope="session")
 def native_lib():
     """Builds (if stale) and loads the C-ABI library."""
-    from deepwell_b200 import _build, _native
-    _build.build()
+    load_build_module().build()            # before the package is imported: its import loads the library
+    from deepwell_b200 import _native
     return _native.load()
 
 
