@@ -29,7 +29,7 @@ ABI_SYMBOLS = (
     "dw_mxfp8_abi_version", "dw_mxfp8_device_supported", "dw_mxfp8_error_string", "dw_mxfp8_scale_bytes",
     "dw_mxfp8_quantize", "dw_mxfp8_quantize_both", "dw_mxfp8_dequantize", "dw_mxfp8_gemm",
     "dw_mxfp8_gemm_workspace", "dw_mxfp8_check_status", "dw_mxfp8_gemm_set_variant",
-    "dw_mxfp8_gemm_set_timing_buffer", "dw_mxfp8_gemm_splitk_static",
+    "dw_mxfp8_gemm_set_timing_buffer", "dw_mxfp8_gemm_splitk_static", "dw_mxfp8_gemm_fused",
 )
 
 _lib = None
@@ -69,6 +69,7 @@ def load() -> ctypes.CDLL:
     L.dw_mxfp8_check_status.argtypes = [p, p]
     L.dw_mxfp8_gemm_set_variant.argtypes = [i32]
     L.dw_mxfp8_gemm_set_timing_buffer.argtypes = [p, sz]
+    L.dw_mxfp8_gemm_fused.argtypes = [p, p, p, p, p, p, i64, i64, i64, f32, f32, i32, p, p, i32, p, p]
     L.dw_mxfp8_gemm_splitk_static.argtypes = [p, p, p, p, p, p, i64, i64, i64, f32, f32, i32, p, p]
     _lib = L
     return L
@@ -195,6 +196,34 @@ def gemm(a_codes: torch.Tensor, a_sf: torch.Tensor, b_codes: torch.Tensor, b_sf:
                                    float(alpha), float(beta), None if ws is None else ws.data_ptr(), ws_bytes,
                                    sw.data_ptr(), _stream(dev)), "dw_mxfp8_gemm")
     return out
+
+
+ACTIVATIONS = {"none": 0, "relu": 1, "gelu": 2, "silu": 3}
+
+
+def gemm_fused(a_codes: torch.Tensor, a_sf: torch.Tensor, b_codes: torch.Tensor, b_sf: torch.Tensor,
+               bias: Optional[torch.Tensor] = None, activation: str = "none", quantize_out: bool = True,
+               write_d: bool = True, alpha: float = 1.0, rule: int = RULE_OCP_FLOOR):
+    """act(alpha * A . B^T + bias) -> (D bf16 or None, codes or None, tiled scales or None).  See dw_mxfp8_gemm_fused."""
+    for t, n in ((a_codes, "A"), (b_codes, "B"), (a_sf, "A scales"), (b_sf, "B scales")):
+        _require_cuda(t, n)
+    M, K = a_codes.shape
+    N, Kb = b_codes.shape
+    if K != Kb:
+        raise RuntimeError(f"contraction mismatch: A is [{M},{K}], B is [{N},{Kb}]")
+    dev = a_codes.device
+    d = torch.empty((M, N), dtype=torch.bfloat16, device=dev) if write_d else None
+    codes = torch.empty((M, N), dtype=torch.uint8, device=dev) if quantize_out else None
+    scales = torch.empty(scale_bytes(M, N, SF_TILED), dtype=torch.uint8, device=dev) if quantize_out else None
+    if bias is not None and (bias.dtype != torch.bfloat16 or bias.numel() != N or not bias.is_contiguous()):
+        raise RuntimeError("bias must be a contiguous bfloat16 [N] tensor")
+    sw = status_word(dev)
+    ptr = lambda t: None if t is None else t.data_ptr()
+    with torch.cuda.device(dev):
+        check(load().dw_mxfp8_gemm_fused(a_codes.data_ptr(), a_sf.data_ptr(), b_codes.data_ptr(), b_sf.data_ptr(), ptr(d),
+                                         ptr(bias), M, N, K, float(alpha), 0.0, ACTIVATIONS[activation], ptr(codes),
+                                         ptr(scales), rule, sw.data_ptr(), _stream(dev)), "dw_mxfp8_gemm_fused")
+    return d, (None if codes is None else codes.view(torch.float8_e4m3fn)), scales
 
 
 def check_status(device=None) -> None:

@@ -40,6 +40,12 @@ struct GemmParams {
     // mx_splitk_reduce_kernel sums them.  splits == 1: the epilogue writes D directly.
     uint32_t splits, kb_per_split;
     float* partial;
+    // Fused epilogue: activation after alpha/beta/bias, and optionally the output quantised row-wise
+    // (blocks of 32 along N) as the next GEMM's A operand: codes [M, N] + tiled scales.  d may be null then.
+    int act, q_rule;
+    uint8_t* q_codes;
+    uint8_t* q_scales;
+    int64_t q_kt;
     // Optional tuning counters (the caller's workspace): per CTA, SM cycles each role spent waiting
     //   [0] producer: free stage       [1] MMA issuer: accumulator drained (two tiles back)
     //   [2] MMA issuer: shared accumulator columns drained (previous tile)
@@ -82,6 +88,15 @@ struct GemmCfg {
     static_assert(kAccStride + BN <= kSfBase, "accumulators must not reach the scale columns");
     static_assert(kStages >= 2, "pipeline depth");
 };
+
+// ReLU / exact GELU / SiLU on the fp32 value before it is rounded to bf16
+// (EpilogueConfig::Op::{BiasReLU, BiasGELU, BiasSwish} of the reference, csrc/cutlass_kernels.h:65-77, never applied there).
+__device__ __forceinline__ float apply_activation(float x, int act) {
+    if (act == DW_ACT_RELU) return fmaxf(x, 0.0f);
+    if (act == DW_ACT_GELU) return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
+    if (act == DW_ACT_SILU) return x / (1.0f + expf(-x));
+    return x;
+}
 
 enum : int { kErrProducer = 1, kErrMmaFull = 2, kErrMmaAcc = 3, kErrEpilogue = 4 };
 
@@ -315,52 +330,90 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                             for (int v = 0; v < 8; ++v)
                                 *reinterpret_cast<uint4*>(dst + 4 * v) = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
                         } else {
-                            for (int i = 0; i < 32 && col + i < p.N; ++i) dst[i] = __uint_as_float(r[i]);
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                if (col + i < p.N) dst[i] = __uint_as_float(r[i]);
                         }
                     }
-                } else
-                if (row < p.M && col < p.N) {
+                } else if (vec_ok && col + 32 <= p.N) {
+                    // full chunk: 32 consecutive columns of one row = exactly one MX block of the output
+                    const bool in_rows = row < p.M;
+                    uint32_t o[16];                      // the 32 outputs as bf16x2 words
+                    if (in_rows) {
+                        float f[32];
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) f[i] = p.alpha * __uint_as_float(r[i]);
+                        if (p.beta != 0.0f) {
+                            const uint16_t* old = p.d + row * p.N + col;
+#pragma unroll
+                            for (int v = 0; v < 4; ++v) {
+                                const uint4 t4 = *reinterpret_cast<const uint4*>(old + 8 * v);
+                                const uint32_t ow[4] = {t4.x, t4.y, t4.z, t4.w};
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    f[8 * v + 2 * i] += p.beta * __uint_as_float(ow[i] << 16);
+                                    f[8 * v + 2 * i + 1] += p.beta * __uint_as_float(ow[i] & 0xFFFF0000u);
+                                }
+                            }
+                        }
+                        if (p.bias != nullptr) {
+#pragma unroll
+                            for (int v = 0; v < 4; ++v) {
+                                const uint4 t4 = *reinterpret_cast<const uint4*>(p.bias + col + 8 * v);
+                                const uint32_t ow[4] = {t4.x, t4.y, t4.z, t4.w};
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    f[8 * v + 2 * i] += __uint_as_float(ow[i] << 16);
+                                    f[8 * v + 2 * i + 1] += __uint_as_float(ow[i] & 0xFFFF0000u);
+                                }
+                            }
+                        }
+                        if (p.act != DW_ACT_NONE) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) f[i] = apply_activation(f[i], p.act);
+                        }
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o[i]) : "f"(f[2 * i + 1]), "f"(f[2 * i]));
+                        if (p.d != nullptr) {
+                            uint16_t* dst = p.d + row * p.N + col;
+#pragma unroll
+                            for (int v = 0; v < 4; ++v)
+                                *reinterpret_cast<uint4*>(dst + 8 * v) = make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
+                        }
+                    }
+                    if (p.q_codes != nullptr) {
+                        // the bf16 outputs quantised in place as the next GEMM's row-wise operand
+                        if (in_rows) {
+                            const uint32_t sb = e8m0_from_amax(fold_amax(amax_words(o)), p.q_rule);
+                            const uint32_t inv = e8m0_inverse_bf16x2(sb);
+                            uint32_t q[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) q[i] = quant_word(o[2 * i], inv) | (quant_word(o[2 * i + 1], inv) << 16);
+                            uint8_t* qd = p.q_codes + row * p.N + col;
+                            stg_v4(qd, make_uint4(q[0], q[1], q[2], q[3]));
+                            stg_v4(qd + 16, make_uint4(q[4], q[5], q[6], q[7]));
+                            p.q_scales[sf_tiled_offset(row, col >> 5, p.q_kt)] = static_cast<uint8_t>(sb);
+                        } else if (row < ((p.M + 127) & ~int64_t(127))) {
+                            p.q_scales[sf_tiled_offset(row, col >> 5, p.q_kt)] = 127;     // padding rows of the last tile
+                        }
+                    }
+                } else if (row < p.M && col < p.N) {     // ragged N: scalar stores, no fused quantisation
                     uint16_t* dst = p.d + row * p.N + col;
-                    if (vec_ok && col + 32 <= p.N) {
 #pragma unroll
-                        for (int v = 0; v < 4; ++v) {
-                            float f[8];
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) f[i] = p.alpha * __uint_as_float(r[8 * v + i]);
-                            if (p.beta != 0.0f) {
-                                const uint4 o = *reinterpret_cast<const uint4*>(dst + 8 * v);
-                                const uint32_t ow[4] = {o.x, o.y, o.z, o.w};
-#pragma unroll
-                                for (int i = 0; i < 4; ++i) {
-                                    f[2 * i] += p.beta * __uint_as_float(ow[i] << 16);
-                                    f[2 * i + 1] += p.beta * __uint_as_float(ow[i] & 0xFFFF0000u);
-                                }
-                            }
-                            if (p.bias != nullptr) {
-                                const uint4 o = *reinterpret_cast<const uint4*>(p.bias + col + 8 * v);
-                                const uint32_t ow[4] = {o.x, o.y, o.z, o.w};
-#pragma unroll
-                                for (int i = 0; i < 4; ++i) {
-                                    f[2 * i] += __uint_as_float(ow[i] << 16);
-                                    f[2 * i + 1] += __uint_as_float(ow[i] & 0xFFFF0000u);
-                                }
-                            }
-                            uint32_t o[4];
-#pragma unroll
-                            for (int i = 0; i < 4; ++i)
-                                asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o[i]) : "f"(f[2 * i + 1]), "f"(f[2 * i]));
-                            *reinterpret_cast<uint4*>(dst + 8 * v) = make_uint4(o[0], o[1], o[2], o[3]);
-                        }
-                    } else {
-                        for (int i = 0; i < 32 && col + i < p.N; ++i) {
-                            float f = p.alpha * __uint_as_float(r[i]);
-                            if (p.beta != 0.0f) f += p.beta * __uint_as_float(static_cast<uint32_t>(dst[i]) << 16);
-                            if (p.bias != nullptr) f += __uint_as_float(static_cast<uint32_t>(p.bias[col + i]) << 16);
-                            uint32_t o;
-                            asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o) : "f"(0.0f), "f"(f));
-                            dst[i] = static_cast<uint16_t>(o & 0xFFFFu);
-                        }
+                    for (int i = 0; i < 32; ++i) {
+                        if (col + i >= p.N) break;
+                        float f = p.alpha * __uint_as_float(r[i]);
+                        if (p.beta != 0.0f) f += p.beta * __uint_as_float(static_cast<uint32_t>(dst[i]) << 16);
+                        if (p.bias != nullptr) f += __uint_as_float(static_cast<uint32_t>(p.bias[col + i]) << 16);
+                        f = apply_activation(f, p.act);
+                        uint32_t ob;
+                        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(ob) : "f"(0.0f), "f"(f));
+                        dst[i] = static_cast<uint16_t>(ob & 0xFFFFu);
                     }
+                } else if (p.q_codes != nullptr && col >= p.N && col < ((p.N + 127) & ~int64_t(127)) &&
+                           row < ((p.M + 127) & ~int64_t(127))) {
+                    p.q_scales[sf_tiled_offset(row, col >> 5, p.q_kt)] = 127;             // padding k-blocks of the scale tile
                 }
             }
             // accumulator drained: hand it back to the MMA issuer (on the leader CTA)
@@ -494,7 +547,8 @@ static int launch_gemm(const void* a, const void* a_sf, const void* b, const voi
     p.tiles_n = static_cast<uint32_t>((p.N + BN - 1) / BN);
     p.num_tiles = p.tiles_m * p.tiles_n;
     p.num_kblocks = static_cast<uint32_t>((p.K + 127) / 128);
-    p.group_m = static_cast<uint32_t>(g_group_m > 0 ? g_group_m : 16 / kCtas);
+    // band height: 2048 rows of tiles, 4096 for very wide outputs (measured best on the Llama-3-8B shapes)
+    p.group_m = static_cast<uint32_t>(g_group_m > 0 ? g_group_m : (p.N >= 16384 ? 32 : 16) / kCtas);
 
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
@@ -553,10 +607,15 @@ static GemmPlan plan_gemm(int64_t M, int64_t N, int64_t K) {
 
 static long long* g_timing = nullptr;   // optional per-CTA wait counters (dw_mxfp8_gemm_set_timing_buffer)
 
+struct FusedOut { int act = DW_ACT_NONE; int rule = DW_RULE_OCP_FLOOR; void* codes = nullptr; void* scales = nullptr; };
+
 static int run_gemm(const void* a_codes, const void* a_sf, const void* b_codes, const void* b_sf, void* d_bf16,
                     const void* bias_bf16, int64_t M, int64_t N, int64_t K, float alpha, float beta, int variant,
-                    uint32_t splits, float* partial, void* status_word, cudaStream_t st) {
+                    uint32_t splits, float* partial, void* status_word, cudaStream_t st, const FusedOut& fo = FusedOut()) {
     GemmParams p = {};
+    p.act = fo.act; p.q_rule = fo.rule;
+    p.q_codes = static_cast<uint8_t*>(fo.codes); p.q_scales = static_cast<uint8_t*>(fo.scales);
+    p.q_kt = (N / 32 + 3) / 4;
     p.d = static_cast<uint16_t*>(d_bf16);
     p.bias = static_cast<const uint16_t*>(bias_bf16);
     p.status = static_cast<int*>(status_word);
@@ -572,8 +631,8 @@ static int run_gemm(const void* a_codes, const void* a_sf, const void* b_codes, 
 }
 
 static int check_gemm_args(const void* a_codes, const void* a_sf, const void* b_codes, const void* b_sf, const void* d_bf16,
-                           const void* bias_bf16, int64_t M, int64_t N, int64_t K) {
-    if (!a_codes || !a_sf || !b_codes || !b_sf || !d_bf16) return DW_ERR_BAD_ARG;
+                           const void* bias_bf16, int64_t M, int64_t N, int64_t K, bool d_optional = false) {
+    if (!a_codes || !a_sf || !b_codes || !b_sf || (!d_bf16 && !d_optional)) return DW_ERR_BAD_ARG;
     if (K == 0 || K % 32 != 0) return DW_ERR_BAD_ARG;
     auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
     if (!al16(a_codes) || !al16(b_codes) || !al16(a_sf) || !al16(b_sf) || !al16(d_bf16)) return DW_ERR_BAD_ARG;
@@ -623,6 +682,28 @@ extern "C" DW_API int dw_mxfp8_gemm(const void* a_codes, const void* a_sf, const
         pl.splits = 1;
     return run_gemm(a_codes, a_sf, b_codes, b_sf, d_bf16, bias_bf16, M, N, K, alpha, beta, pl.variant, pl.splits,
                     static_cast<float*>(workspace), status_word, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" DW_API int dw_mxfp8_gemm_fused(const void* a_codes, const void* a_sf, const void* b_codes, const void* b_sf,
+                                          void* d_bf16, const void* bias_bf16, int64_t M, int64_t N, int64_t K, float alpha,
+                                          float beta, int activation, void* out_codes, void* out_scales, int scale_rule,
+                                          void* status_word, void* stream) {
+    if (M < 0 || N < 0 || K < 0) return DW_ERR_BAD_ARG;
+    if (activation < DW_ACT_NONE || activation > DW_ACT_SILU) return DW_ERR_BAD_ARG;
+    if (scale_rule != DW_RULE_OCP_FLOOR && scale_rule != DW_RULE_REF_CEIL) return DW_ERR_BAD_ARG;
+    if ((out_codes == nullptr) != (out_scales == nullptr)) return DW_ERR_BAD_ARG;
+    if (d_bf16 == nullptr && out_codes == nullptr) return DW_ERR_BAD_ARG;          // nothing to write
+    if (d_bf16 == nullptr && beta != 0.0f) return DW_ERR_BAD_ARG;                  // beta reads D
+    if (M == 0 || N == 0) return DW_OK;
+    const int rc = check_gemm_args(a_codes, a_sf, b_codes, b_sf, d_bf16, bias_bf16, M, N, K, true);
+    if (rc != DW_OK) return rc;
+    if (out_codes != nullptr && (N % 32 != 0 || (reinterpret_cast<uintptr_t>(out_codes) & 15) != 0)) return DW_ERR_BAD_ARG;
+    if (out_codes == nullptr && N % 8 != 0 && activation != DW_ACT_NONE && d_bf16 == nullptr) return DW_ERR_BAD_ARG;
+    FusedOut fo;
+    fo.act = activation; fo.rule = scale_rule; fo.codes = out_codes; fo.scales = out_scales;
+    const GemmPlan pl = plan_gemm(M, N, K);
+    return run_gemm(a_codes, a_sf, b_codes, b_sf, d_bf16, bias_bf16, M, N, K, alpha, beta, pl.variant, 1, nullptr, status_word,
+                    static_cast<cudaStream_t>(stream), fo);
 }
 
 // ------------------------------------------------------------------------------------------

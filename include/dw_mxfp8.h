@@ -95,6 +95,24 @@ int dw_mxfp8_gemm(const void *a_codes, const void *a_sf, const void *b_codes, co
                   void *d_bf16, const void *bias_bf16, int64_t M, int64_t N, int64_t K, float alpha,
                   float beta, void *workspace, size_t workspace_bytes, void *status_word, void *stream);
 
+/* GEMM with a fused epilogue: D = act(alpha * A.B^T + beta * D + bias), act applied in fp32 before the
+ * bf16 rounding, and - when out_codes / out_scales are given - the bf16 result quantised row-wise
+ * (32-element blocks along N, DW_SF_TILED scales for an [M, N/32] operand) in the same pass, so the
+ * next layer's GEMM can consume it without the activation travelling through HBM in bf16 and back.
+ * The codes are exactly what dw_mxfp8_quantize(DW_DIR_ROW) gives on the bf16 D of the same call.
+ * d_bf16 may be NULL when only the quantised form is wanted (beta must be 0 then).  N % 32 == 0 for
+ * the quantised output.  Gives a body to EpilogueConfig::Op::{BiasReLU, BiasGELU, BiasSwish}
+ * (csrc/cutlass_kernels.h:65-77; accepted and ignored at csrc/cutlass_kernels.cpp:223-226) and to
+ * FusedLinearGELU (src/deepwell/kernels/blackwell_production.py:487-527). */
+#define DW_ACT_NONE 0
+#define DW_ACT_RELU 1
+#define DW_ACT_GELU 2   /* exact: 0.5 x (1 + erf(x / sqrt 2)) */
+#define DW_ACT_SILU 3
+int dw_mxfp8_gemm_fused(const void *a_codes, const void *a_sf, const void *b_codes, const void *b_sf,
+                        void *d_bf16, const void *bias_bf16, int64_t M, int64_t N, int64_t K, float alpha,
+                        float beta, int activation, void *out_codes, void *out_scales, int scale_rule,
+                        void *status_word, void *stream);
+
 /* Replaces BlackwellGemmKernel::get_workspace_size, csrc/cutlass_kernels.cpp:229-231. */
 size_t dw_mxfp8_gemm_workspace(int64_t M, int64_t N, int64_t K);
 

@@ -191,3 +191,54 @@ def test_zero_and_nan_free_padding(nv):
     y = nv.gemm(xc, xs, wc, ws, out=out)
     nv.check_status()
     assert torch.count_nonzero(y).item() == 0
+
+
+@pytest.mark.parametrize("act", ["none", "relu", "gelu", "silu"])
+@pytest.mark.parametrize("shape", [(384, 512, 256), (300, 160, 96)])
+def test_fused_epilogue_activation_and_quantised_output(nv, act, shape):
+    """dw_mxfp8_gemm_fused: D = act(A.B^T + bias) within tolerance of the fp32 reference, and the quantised
+    output is bit-for-bit what the row-wise quantiser gives on that D (codes, scales, padding bytes)."""
+    nv.set_gemm_variant(0)
+    M, N, K = shape
+    g = torch.Generator("cpu").manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=g).bfloat16().cuda()
+    w = (torch.randn(N, K, generator=g) * 0.1).bfloat16().cuda()
+    bias = torch.randn(N, generator=g).bfloat16().cuda()
+    xc, xs = nv.quantize(x, nv.DIR_ROW, 0, nv.SF_TILED)
+    wc, ws = nv.quantize(w, nv.DIR_ROW, 0, nv.SF_TILED)
+    d, codes, scales = nv.gemm_fused(xc, xs, wc, ws, bias=bias, activation=act)
+    nv.check_status()
+    pre = oracle_gemm(nv, x, w, bias=bias)
+    fn = {"none": lambda t: t, "relu": torch.relu, "gelu": torch.nn.functional.gelu, "silu": torch.nn.functional.silu}[act]
+    assert_close(d.cpu(), fn(pre))
+    bits = d.cpu().view(torch.int16).numpy().view(np.uint16)
+    ec, es = o.quantize_rowwise(bits)
+    assert np.array_equal(host(codes), ec)
+    assert np.array_equal(host(scales), o.sf_flat_to_tiled(es))
+    # quantised form only (no bf16 D written): same bytes
+    d2, codes2, scales2 = nv.gemm_fused(xc, xs, wc, ws, bias=bias, activation=act, write_d=False)
+    nv.check_status()
+    assert d2 is None and torch.equal(codes2.view(torch.uint8), codes.view(torch.uint8)) and torch.equal(scales2, scales)
+
+
+def test_fused_mlp_chain_never_stores_the_activation(nv):
+    """up-projection with bias + GELU + quantise fused, then the down-projection consumes the codes directly:
+    identical bits to GEMM -> bf16 -> quantise -> GEMM."""
+    nv.set_gemm_variant(0)
+    g = torch.Generator("cpu").manual_seed(9)
+    x = torch.randn(512, 256, generator=g).bfloat16().cuda()
+    w1 = (torch.randn(1024, 256, generator=g) * 0.06).bfloat16().cuda()
+    b1 = torch.randn(1024, generator=g).bfloat16().cuda()
+    w2 = (torch.randn(256, 1024, generator=g) * 0.03).bfloat16().cuda()
+    xc, xs = nv.quantize(x, nv.DIR_ROW, 0, nv.SF_TILED)
+    w1c, w1s = nv.quantize(w1, nv.DIR_ROW, 0, nv.SF_TILED)
+    w2c, w2s = nv.quantize(w2, nv.DIR_ROW, 0, nv.SF_TILED)
+    _, hc, hs = nv.gemm_fused(xc, xs, w1c, w1s, bias=b1, activation="gelu", write_d=False)
+    y_fused = nv.gemm(hc, hs, w2c, w2s)
+    h, _, _ = nv.gemm_fused(xc, xs, w1c, w1s, bias=b1, activation="gelu", quantize_out=False)
+    hc2, hs2 = nv.quantize(h, nv.DIR_ROW, 0, nv.SF_TILED)
+    y_two = nv.gemm(hc2, hs2, w2c, w2s)
+    nv.check_status()
+    assert torch.equal(y_fused.view(torch.int16), y_two.view(torch.int16))
+    ref = torch.nn.functional.gelu(x.float() @ w1.float().t() + b1.float()) @ w2.float().t()
+    assert ((y_fused.float() - ref).norm() / ref.norm()).item() < 0.05                  # MXFP8 end to end vs fp32 (Frobenius)

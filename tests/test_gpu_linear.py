@@ -124,3 +124,62 @@ def test_extension_module_api(dw):
     gk = GroupedGEMMKernel(2, 512, 320)
     outs = gk.grouped_gemm([a, a[:128]], [w.t(), w.t()])
     assert close(outs[0], ref) and close(outs[1], ref[:128])
+
+
+class _Block(nn.Module):
+    """Pre-LN decoder block built from plain nn.Linear projections + scaled_dot_product_attention
+    (the shape of BASELINE config 5, scaled down)."""
+
+    def __init__(self, hidden, heads, ffn):
+        super().__init__()
+        self.heads = heads
+        self.ln1, self.ln2 = nn.LayerNorm(hidden), nn.LayerNorm(hidden)
+        self.qkv, self.proj = nn.Linear(hidden, 3 * hidden), nn.Linear(hidden, hidden)
+        self.up, self.down = nn.Linear(hidden, ffn), nn.Linear(ffn, hidden)
+
+    def forward(self, x):
+        b, s, h = x.shape
+        q, k, v = self.qkv(self.ln1(x)).view(b, s, 3, self.heads, h // self.heads).permute(2, 0, 3, 1, 4)
+        a = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True)
+        x = x + self.proj(a.transpose(1, 2).reshape(b, s, h))
+        return x + self.down(torch.nn.functional.gelu(self.up(self.ln2(x))))
+
+
+class _Decoder(nn.Module):
+    def __init__(self, vocab=1024, hidden=256, heads=4, ffn=1024, layers=2):
+        super().__init__()
+        self.embed = nn.Embedding(vocab, hidden)
+        self.blocks = nn.ModuleList([_Block(hidden, heads, ffn) for _ in range(layers)])
+        self.ln_f = nn.LayerNorm(hidden)
+        self.head = nn.Linear(hidden, vocab, bias=False)
+
+    def forward(self, ids):
+        x = self.embed(ids)
+        for blk in self.blocks:
+            x = blk(x)
+        return self.head(self.ln_f(x))
+
+
+def test_optimize_decoder_training_step_tracks_bf16(dw):
+    """deepwell.optimize(model, precision='mxfp8') on a small pre-LN decoder: every nn.Linear becomes a
+    DWLinear, a few training steps run, and the loss curve stays within 3 % of the bf16 model's."""
+    torch.manual_seed(5678)
+    ref = _Decoder().cuda().bfloat16()
+    model = dw.optimize(ref, precision="mxfp8", verbose=False)
+    n_lin = sum(isinstance(m, nn.Linear) for m in ref.modules())
+    assert sum(isinstance(m, dw.DWLinear) for m in model.modules()) == n_lin == 9
+    ids = torch.randint(0, 1024, (4, 128), device="cuda")
+    curves = []
+    for net in (ref, model):
+        opt = torch.optim.AdamW(net.parameters(), lr=1e-3)
+        cur = []
+        for _ in range(6):
+            opt.zero_grad()
+            logits = net(ids)
+            loss = torch.nn.functional.cross_entropy(logits[:, :-1].reshape(-1, 1024).float(), ids[:, 1:].reshape(-1))
+            loss.backward()
+            opt.step()
+            cur.append(loss.item())
+        curves.append(cur)
+    assert curves[1][-1] < curves[1][0] - 0.3, curves
+    assert all(abs(a - b) <= 0.03 * abs(a) for a, b in zip(*curves)), curves

@@ -155,3 +155,27 @@ def test_full_size_properties(nv, rows, cols):
     rc2, rs2 = nv.quantize(dq, nv.DIR_ROW, 0, nv.SF_FLAT)
     dq2 = nv.dequantize(rc2, rs2, nv.SF_FLAT)
     assert torch.equal(dq.view(torch.int16), dq2.view(torch.int16))      # idempotent after one round trip
+
+
+def test_largest_sweep_point_2_pow_32_elements(nv):
+    """The top of the quantise sweep (2^32 elements, K = 16384): 64-bit addressing everywhere.  Row blocks
+    sampled from the start, the middle and the very end against the oracle; column-wise payload of
+    sampled columns against the oracle on the gathered columns."""
+    rows, cols = 1 << 18, 1 << 14
+    x = torch.empty(rows, cols, dtype=torch.bfloat16, device="cuda")
+    g = torch.Generator("cuda").manual_seed(4567)
+    for r0 in range(0, rows, 1 << 14):                      # filled in slices: no 16 GiB fp32 temporary
+        z = torch.randn(1 << 14, cols, device="cuda", generator=g)
+        v = torch.distributions.Chi2(torch.tensor(3.0, device="cuda")).sample((1 << 14, 1))
+        x[r0:r0 + (1 << 14)] = (0.5 * z / torch.sqrt(v / 3)).bfloat16()
+    del z, v
+    rc, rs = nv.quantize(x, nv.DIR_ROW, 0, nv.SF_FLAT)
+    sel = [0, 1, 131071, 131072, rows - 2, rows - 1]
+    er, ers = c.quantize_rowwise(bits_of(x[sel]), 0)
+    assert np.array_equal(host(rc[sel]), er) and np.array_equal(host(rs[sel]), ers)
+    del rc, rs
+    tc, ts = nv.quantize(x, nv.DIR_COL_T, 0, nv.SF_FLAT)
+    csel = [0, 77, cols - 1]
+    xs = x[:, csel].t().contiguous()                        # [3, rows]: the sampled columns as rows
+    ec, ecs = c.quantize_rowwise(bits_of(xs), 0)
+    assert np.array_equal(host(tc[csel]), ec) and np.array_equal(host(ts[csel]), ecs)
