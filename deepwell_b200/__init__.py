@@ -12,5 +12,6 @@ __version__ = "0.1.0"
 from .optimizer import DeepwellOptimizer, optimize          # noqa: E402
 from .linear import DWLinear                                # noqa: E402
 from . import cutlass_kernels, kernels                      # noqa: E402
+from .kernels.production_kernels import optimize_for_blackwell   # noqa: E402
 
-__all__ = ["optimize", "DeepwellOptimizer", "DWLinear", "cutlass_kernels", "kernels", "__version__"]
+__all__ = ["optimize", "optimize_for_blackwell", "DeepwellOptimizer", "DWLinear", "cutlass_kernels", "kernels", "__version__"]

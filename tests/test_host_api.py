@@ -117,3 +117,19 @@ def test_reference_import_names(native_lib):
     assert cutlass_kernels.BlackwellGemmKernel is deepwell_b200.cutlass_kernels.BlackwellGemmKernel
     assert get_registry().find_kernel("gemm", "mxfp8", 100).name == "cutlass_sm100_mxfp8_gemm"
     assert KernelSpec and CutlassKernel and DeepwellOptimizer
+
+
+def test_legacy_linear_replacement_names(native_lib):
+    """optimize_for_blackwell / optimize_model_inplace / OptimizedLinear of the reference lead to DWLinear."""
+    import deepwell
+    from deepwell.kernels.production_kernels import KernelConfig, OptimizedLinear, ProductionKernelManager, optimize_model_inplace
+    import deepwell_b200 as dw
+    model = nn.Sequential(nn.Embedding(100, 64), nn.LayerNorm(64), nn.Linear(64, 96))
+    new = deepwell.optimize_for_blackwell(model, precision="mxfp8", seq_len=8, batch_size=2)
+    assert isinstance(new[2], dw.DWLinear) and type(model[2]) is nn.Linear
+    same = optimize_model_inplace(model, KernelConfig(precision="mxfp8"))
+    assert same is model and isinstance(model[2], dw.DWLinear)
+    lin = OptimizedLinear(64, 32, bias=False)
+    assert isinstance(lin, dw.DWLinear) and lin.bias is None and isinstance(lin.kernel_manager, ProductionKernelManager)
+    with pytest.raises(RuntimeError):
+        ProductionKernelManager().gemm(torch.randn(4, 32), torch.randn(32, 32))
