@@ -39,9 +39,10 @@ METRIC = "mxfp8_quant_gemm_tflops"
 WORKLOAD = "llama3_8b_linears_M16384"
 CPU_SAMPLE_ROWS = 4096
 NOMINAL_MXFP8_TFLOPS = 4500.0
-# DRAM bytes (read + write) of one GEMM launch of the gate+up shape, from the ncu capture summarised
-# in profiles/ (null until a capture exists)
-GEMM_DRAM_TRAFFIC_BYTES = None
+# dram__bytes_read.sum + dram__bytes_write.sum of the four GEMM launches of one step at N = 1 (ncu capture of
+# this file's own launches, summarised in profiles/mx_gemm_kernel_bench_shapes_dram_traffic.md), bytes
+GEMM_DRAM_TRAFFIC = {"qkv": 278289152, "o": 178107648, "gate_up": 1457078272, "down": 1161285120}
+GEMM_DRAM_TRAFFIC_BYTES = sum(GEMM_DRAM_TRAFFIC.values()) / len(GEMM_DRAM_TRAFFIC)      # mean per launch
 
 
 def measured_peaks():
@@ -235,6 +236,8 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--variant", type=int, default=0, help="GEMM kernel variant (0 = automatic)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--emulate-world", type=int, default=0,
+                    help="tuning aid: on one GPU, run the shard sizes rank 0 would get in a job of this many GPUs")
     ap.add_argument("--serial", action="store_true", help="quantise and GEMM on one stream (no overlap between layers)")
     ap.add_argument("--profile-case", default=None, choices=["gemm", "quant_row", "quant_both", "quant_col"],
                     help="run a few launches of one kernel on a small case (for an ncu capture) and exit")
@@ -273,7 +276,7 @@ def main():
     g = torch.Generator(device=dev).manual_seed(3456)
     layers = []
     for name, k, n in LAYERS:
-        n0, n1 = shard_bounds(n, world, rank)
+        n0, n1 = shard_bounds(n, max(world, args.emulate_world), rank)
         x = torch.randn(M_TOKENS, k, device=dev, generator=g).bfloat16()
         w_full = (torch.randn(n, k, device=dev, generator=g) * 0.02).bfloat16()
         w = w_full[n0:n1].contiguous()
@@ -359,7 +362,8 @@ def main():
     peaks = measured_peaks()
     peak = 2.0 * peaks["bf16_tflops_sustained"]
     roofline = {"bound": "tensor", "kernel": "mx_gemm_kernel", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                "frac": achieved / peak, "traffic": GEMM_DRAM_TRAFFIC_BYTES,
+                "frac": achieved / peak, "traffic": GEMM_DRAM_TRAFFIC_BYTES if world == 1 else None,
+                "traffic_note": "mean DRAM bytes per GEMM launch (ncu, N = 1); algorithmic mean A + B + D = 5.16e8",
                 "peak_basis": f"2 x bf16_tflops_sustained of {peaks['source']} MEASURED_PEAKS (MXFP8 issues at twice the "
                               "bf16 tensor rate); nominal dense MXFP8 is 4500",
                 "frac_of_nominal_4500": achieved / NOMINAL_MXFP8_TFLOPS,
@@ -475,7 +479,10 @@ def main():
                            "step": "per layer: quantise X, quantise W shard, block-scaled GEMM"
                                    + ("" if args.serial else "; quantisation of the next layer on a second stream"),
                            "l2": f"inputs larger than L2: {bytes_step / 1e9:.2f} GB touched per step per GPU",
-                           "gemm_variant": args.variant},
+                           "gemm_variant": args.variant,
+                           **({"emulated_world": args.emulate_world,
+                               "note": "TUNING RUN: one rank's shard on one GPU; value is not a job throughput"}
+                              if args.emulate_world else {})},
                 "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roofline,
                 "roofline_quantize": roofline_q, "cpu_baseline": cpu_baseline}
         print(json.dumps(line), flush=True)
