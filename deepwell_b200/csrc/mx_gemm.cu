@@ -547,8 +547,16 @@ static int launch_gemm(const void* a, const void* a_sf, const void* b, const voi
     p.tiles_n = static_cast<uint32_t>((p.N + BN - 1) / BN);
     p.num_tiles = p.tiles_m * p.tiles_n;
     p.num_kblocks = static_cast<uint32_t>((p.K + 127) / 128);
-    // band height: 2048 rows of tiles, 4096 for very wide outputs (measured best on the Llama-3-8B shapes)
-    p.group_m = static_cast<uint32_t>(g_group_m > 0 ? g_group_m : (p.N >= 16384 ? 32 : 16) / kCtas);
+    // Band height (row tiles per raster band).  Inside a band the A tiles are reused by every wave of
+    // CTAs while B streams through once, so DRAM reads are about A + (bands x B): when B is small it
+    // stays in L2 anyway and a low band is fine; otherwise the band is made as tall as an A band of
+    // ~32 MB allows (measured: L2 keeps roughly that much beside the streaming operand and D).
+    {
+        const int64_t tile_bytes = static_cast<int64_t>(128 * kCtas) * p.K, b_bytes = p.N * p.K;
+        int64_t g = 16 / kCtas;
+        if (b_bytes > (32ll << 20)) g = std::max<int64_t>(16 / kCtas, std::min<int64_t>((32ll << 20) / tile_bytes, 64 / kCtas));
+        p.group_m = static_cast<uint32_t>(g_group_m > 0 ? g_group_m : g);
+    }
 
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;

@@ -140,6 +140,11 @@ __global__ void mx_sf_pad_kernel(uint8_t* __restrict__ scales, int64_t rows, int
 // Tile kernel: column-wise transposed payload, optionally fused with the row-wise form.
 // rows % 32 == 0, cols % 32 == 0.  CTA = 256 threads, tile = 128 rows x 128 cols.
 // ------------------------------------------------------------------------------------------
+// Position of 16-byte chunk c (0..15) of tile row r in shared memory.  The XOR with the row makes the
+// column pass and the row pass conflict-free: 8 lanes that read the same chunk of 8 consecutive rows,
+// or the four blocks of two consecutive rows, land in 8 different 16-byte bank groups.
+__device__ __forceinline__ uint32_t tile_chunk(uint32_t c, uint32_t r) { return c ^ (r & 7u) ^ ((c >> 3) << 1); }
+
 constexpr int kTileSmemBytes = 2 * 128 * 16 * 16 + 1024;   // two 32 KB tiles + two 512-byte scale staging areas
 
 template <bool kDoRow, bool kDoCol>
@@ -158,6 +163,7 @@ mx_quant_tile_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes
     const uint32_t cc = t & 15u;
     const int64_t kb_row = cols >> 5, kb_col = rows >> 5;           // k-blocks per operand row
     const int64_t kt_row = (kb_row + 3) >> 2, kt_col = (kb_col + 3) >> 2;
+    const bool wide_rows = (reinterpret_cast<uintptr_t>(codes_row) & 31) == 0;   // 32-byte stores of the row payload
 
     auto issue_tile = [&](uint32_t id, int buf) {
         const uint32_t itr = id / tiles_c, itc = id - itr * tiles_c;
@@ -170,7 +176,7 @@ mx_quant_tile_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes
             const bool ok = gr < rows && igc < cols;
             const uint16_t* src = ok ? x + gr * cols + igc : x;          // out of range: zero fill, nothing read
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
-                         ::"r"(smem_u32(&dst[row][cc])), "l"(src), "r"(ok ? 16 : 0) : "memory");
+                         ::"r"(smem_u32(&dst[row][tile_chunk(cc, row)])), "l"(src), "r"(ok ? 16 : 0) : "memory");
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
@@ -189,29 +195,39 @@ mx_quant_tile_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes
     TilePtr tile = reinterpret_cast<TilePtr>(tile_smem + buf * (128 * 16 * 16));
     const uint32_t tr = id / tiles_c, tc = id - tr * tiles_c;
     const int64_t r0 = static_cast<int64_t>(tr) * 128, c0 = static_cast<int64_t>(tc) * 128;
-    const int64_t gc = c0 + cc * 8;
 
     if (kDoRow) {
+        // one thread = one whole 32-element block (row r, block b): four 16-byte chunks, no shuffles;
+        // four consecutive lanes cover the 128 bytes of codes of one row, so stores stay coalesced.
+        const uint32_t b = t & 3u;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const uint32_t row = (t >> 4) + 16 * j;
-        {
-            const uint4 v = tile[row][cc];
-            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-            uint32_t m2 = amax_words(w);
-            m2 = absmax_bf16x2(m2, __shfl_xor_sync(0xFFFFFFFFu, m2, 1));
-            m2 = absmax_bf16x2(m2, __shfl_xor_sync(0xFFFFFFFFu, m2, 2));
-            const uint32_t sb = e8m0_from_amax(fold_amax(m2), rule);
+        for (int i = 0; i < 2; ++i) {
+            const uint32_t r = (t >> 2) + 64 * i;
+            uint32_t w[16];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint4 v = tile[r][tile_chunk(4 * b + j, r)];
+                w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+            }
+            const uint32_t sb = e8m0_from_amax(fold_amax(amax_words(w)), rule);
             const uint32_t inv = e8m0_inverse_bf16x2(sb);
-            uint2 q;
-            q.x = quant_word(w[0], inv) | (quant_word(w[1], inv) << 16);
-            q.y = quant_word(w[2], inv) | (quant_word(w[3], inv) << 16);
-            const int64_t gr = r0 + row;
-            if (gr < rows && gc < cols) *reinterpret_cast<uint2*>(codes_row + gr * cols + gc) = q;
-            if ((cc & 3u) == 0u) sf_row[(row & 31u) * 16 + (row >> 5) * 4 + (cc >> 2)] = static_cast<uint8_t>(sb);
+            uint32_t q[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) q[j] = __byte_perm(quant_word(w[2 * j], inv), quant_word(w[2 * j + 1], inv), 0x5410);
+            const int64_t gr = r0 + r, gcb = c0 + 32 * b;
+            if (gr < rows && gcb < cols) {
+                uint8_t* d = codes_row + gr * cols + gcb;
+                if (wide_rows) {
+                    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(d), "r"(q[0]), "r"(q[1]), "r"(q[2]),
+                                 "r"(q[3]), "r"(q[4]), "r"(q[5]), "r"(q[6]), "r"(q[7]) : "memory");
+                } else {
+                    stg_v4(d, make_uint4(q[0], q[1], q[2], q[3]));
+                    stg_v4(d + 16, make_uint4(q[4], q[5], q[6], q[7]));
+                }
+            }
+            sf_row[(r & 31u) * 16 + (r >> 5) * 4 + b] = static_cast<uint8_t>(sb);
         }
-    }
-    __syncthreads();
+        __syncthreads();
     }
 
     if (kDoRow) {  // scales of the row-wise operand [rows, cols/32]
@@ -236,7 +252,8 @@ mx_quant_tile_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes
         const uint32_t* tw = reinterpret_cast<const uint32_t*>(&tile[0][0]);
         uint32_t w[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) w[i] = tw[(rb * 32 + i) * 64 + p];
+        for (int i = 0; i < 32; ++i)      // chunk index XORed with the row, as written by issue_tile
+            w[i] = tw[(rb * 32 + i) * 64 + ((tile_chunk(p >> 2, i) << 2) | (p & 3u))];
         uint32_t m = w[0];
 #pragma unroll
         for (int i = 1; i < 32; ++i) m = absmax_bf16x2(m, w[i]);
@@ -248,16 +265,17 @@ mx_quant_tile_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes
         uint32_t qa[8], qb[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            uint32_t a = 0, b = 0;
+            uint32_t ca[2], cb[2];
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
                 uint32_t s0, s1;   // rows 4i+2h and 4i+2h+1, both columns scaled at once
                 asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(s0) : "r"(w[4 * i + 2 * h]), "r"(inv2));
                 asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(s1) : "r"(w[4 * i + 2 * h + 1]), "r"(inv2));
-                a |= cvt_e4m3x2(__uint_as_float(s0 << 16), __uint_as_float(s1 << 16)) << (16 * h);
-                b |= cvt_e4m3x2(__uint_as_float(s0 & 0xFFFF0000u), __uint_as_float(s1 & 0xFFFF0000u)) << (16 * h);
+                ca[h] = cvt_e4m3x2(__uint_as_float(s0 << 16), __uint_as_float(s1 << 16));
+                cb[h] = cvt_e4m3x2(__uint_as_float(s0 & 0xFFFF0000u), __uint_as_float(s1 & 0xFFFF0000u));
             }
-            qa[i] = a; qb[i] = b;
+            qa[i] = __byte_perm(ca[0], ca[1], 0x5410);
+            qb[i] = __byte_perm(cb[0], cb[1], 0x5410);
         }
         const int64_t gcol = c0 + 2 * p, grow = r0 + rb * 32;
         if (grow < rows) {
