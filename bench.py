@@ -225,6 +225,62 @@ def run_profile_case(args):
 
 
 # ----------------------------------------------------------------------------------------------
+# quantise-only sweep: Student-t(3) x 0.5 inputs, K in {128, 1024, 4096, 16384}, 2^20 .. 2^32 elements
+# ----------------------------------------------------------------------------------------------
+def run_quantize_sweep(args):
+    from deepwell_b200 import _native as nv
+    L = nv.load()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    st = torch.cuda.current_stream(dev).cuda_stream
+    peak = measured_peaks()["hbm_gbs"]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)           # larger than L2
+    g = torch.Generator(device=dev).manual_seed(4567)
+    rows_out = []
+    for log2n in range(20, 33, 2):
+        n = 1 << log2n
+        # one buffer per size, re-viewed for every K (values are i.i.d., the shape does not matter to them)
+        x_flat = torch.empty(n, dtype=torch.bfloat16, device=dev)
+        step_elems = min(n, 1 << 26)
+        for off in range(0, n, step_elems):
+            z = torch.randn(step_elems, device=dev, generator=g)
+            v = torch.distributions.Chi2(torch.tensor(3.0, device=dev)).sample((step_elems,))
+            x_flat[off:off + step_elems] = (0.5 * z / torch.sqrt(v / 3)).bfloat16()
+            del z, v
+        codes = torch.empty(n, dtype=torch.uint8, device=dev)
+        for k in (128, 1024, 4096, 16384):
+            r = n // k
+            if r < 32:
+                continue
+            for name, direction in (("row", nv.DIR_ROW), ("col", nv.DIR_COL_T)):
+                scales = torch.empty(nv.scale_bytes(r if direction == nv.DIR_ROW else k, k if direction == nv.DIR_ROW else r,
+                                                    nv.SF_TILED), dtype=torch.uint8, device=dev)
+                run = lambda: nv.check(L.dw_mxfp8_quantize(x_flat.data_ptr(), codes.data_ptr(), scales.data_ptr(), r, k,
+                                                           direction, 0, nv.SF_TILED, st), "quantize")
+                small = n * 3 < (256 << 20)                  # working set could sit in L2: flush between launches
+                reps = 5 if log2n >= 28 else 20
+                for _ in range(3):
+                    run()
+                times = []
+                for _ in range(reps):
+                    if small:
+                        flush.zero_()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    run()
+                    e1.record()
+                    torch.cuda.synchronize(dev)
+                    times.append(e0.elapsed_time(e1))
+                ms = float(np.median(times))
+                gbs = n * 3.03125 / (ms * 1e-3) / 1e9
+                rows_out.append({"log2_elements": log2n, "K": k, "direction": name, "us": ms * 1e3, "GBps": gbs,
+                                 "frac_of_measured_copy": gbs / peak, "l2_flushed": small})
+                print(json.dumps(rows_out[-1]), flush=True)
+        del x_flat, codes
+    print(json.dumps({"sweep": "quantize", "peak_hbm_gbs": peak, "points": len(rows_out)}))
+
+
+# ----------------------------------------------------------------------------------------------
 # GPU arm
 # ----------------------------------------------------------------------------------------------
 def main():
@@ -236,6 +292,8 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--variant", type=int, default=0, help="GEMM kernel variant (0 = automatic)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sweep-quantize", action="store_true",
+                    help="quantise-only bandwidth sweep (K in {128,1024,4096,16384}, 2^20..2^32 elements, both directions)")
     ap.add_argument("--emulate-world", type=int, default=0,
                     help="tuning aid: on one GPU, run the shard sizes rank 0 would get in a job of this many GPUs")
     ap.add_argument("--serial", action="store_true", help="quantise and GEMM on one stream (no overlap between layers)")
@@ -252,6 +310,9 @@ def main():
         return
     if args.profile_case:
         run_profile_case(args)
+        return
+    if args.sweep_quantize:
+        run_quantize_sweep(args)
         return
 
     import torch.distributed as dist
