@@ -1,8 +1,15 @@
-"""ctypes binding of the C ABI declared in include/dw_mxfp8.h.
+"""Binding of the C ABI declared in include/dw_mxfp8.h.
+
+Two routes reach the same shared library.  ctypes (load()) exposes every entry point with raw
+pointers: the tests and the rarely-called functions use it.  deepwell_b200._C (ext(), built from
+csrc/python_bindings.cpp) wraps the per-layer calls (quantize, quantize_both, gemm, the linear
+layer's forward and backward) so that one Python call allocates the outputs and launches; the
+hot path of DWLinear goes through it because the ctypes route costs more host time than a small
+layer's kernels take.
 
 The shared library is the product: there is no Python, PyTorch or CPU stand-in for any of
-these calls.  If the library is missing or a call fails this module raises; it never
-falls back (contrast src/deepwell/kernels/cutlass_bindings.py:181-192 of the reference,
+these calls.  If the library or the extension is missing or a call fails this module raises; it
+never falls back (contrast src/deepwell/kernels/cutlass_bindings.py:181-192 of the reference,
 which silently drops to torch.matmul).
 """
 from __future__ import annotations
@@ -30,6 +37,7 @@ ABI_SYMBOLS = (
     "dw_mxfp8_quantize", "dw_mxfp8_quantize_both", "dw_mxfp8_dequantize", "dw_mxfp8_gemm",
     "dw_mxfp8_gemm_workspace", "dw_mxfp8_check_status", "dw_mxfp8_gemm_set_variant",
     "dw_mxfp8_gemm_set_timing_buffer", "dw_mxfp8_gemm_splitk_static", "dw_mxfp8_gemm_fused",
+    "dw_mxfp8_colsum_workspace", "dw_mxfp8_quantize_both_colsum",
 )
 
 _lib = None
@@ -63,6 +71,9 @@ def load() -> ctypes.CDLL:
     L.dw_mxfp8_quantize.argtypes = [p, p, p, i64, i64, i32, i32, i32, p]
     L.dw_mxfp8_quantize_both.argtypes = [p, p, p, p, p, i64, i64, i32, i32, p]
     L.dw_mxfp8_dequantize.argtypes = [p, p, p, i64, i64, i32, p]
+    L.dw_mxfp8_colsum_workspace.argtypes = [i64, i64]
+    L.dw_mxfp8_colsum_workspace.restype = sz
+    L.dw_mxfp8_quantize_both_colsum.argtypes = [p, p, p, p, p, i64, i64, i32, i32, p, i32, p, sz, p]
     L.dw_mxfp8_gemm.argtypes = [p, p, p, p, p, p, i64, i64, i64, f32, f32, p, sz, p, p]
     L.dw_mxfp8_gemm_workspace.argtypes = [i64, i64, i64]
     L.dw_mxfp8_gemm_workspace.restype = sz
@@ -73,6 +84,23 @@ def load() -> ctypes.CDLL:
     L.dw_mxfp8_gemm_splitk_static.argtypes = [p, p, p, p, p, p, i64, i64, i64, f32, f32, i32, p, p]
     _lib = L
     return L
+
+
+_ext = None
+
+
+def ext():
+    """The torch-tensor layer over the library (deepwell_b200._C).  Raises NativeLibraryError if it is not built."""
+    global _ext
+    if _ext is None:
+        load()
+        try:
+            from . import _C
+        except ImportError as e:
+            raise NativeLibraryError(f"deepwell_b200/_C.so is missing or does not load ({e}): build it with "
+                                     "`python deepwell_b200/_build.py`.  There is no fallback path.") from e
+        _ext = _C
+    return _ext
 
 
 def check(code: int, what: str) -> None:
@@ -97,43 +125,17 @@ def scale_bytes(rows: int, k: int, layout: int) -> int:
 def quantize(x: torch.Tensor, direction: int = DIR_ROW, rule: int = RULE_OCP_FLOOR,
              layout: int = SF_FLAT) -> Tuple[torch.Tensor, torch.Tensor]:
     """bf16 [rows, cols] -> (codes float8_e4m3fn, scales uint8).  See dw_mxfp8_quantize."""
-    _require_cuda(x, "input")
-    if x.dtype != torch.bfloat16 or x.dim() != 2:
-        raise RuntimeError("input must be a 2-D bfloat16 tensor")
-    x = x.contiguous()
-    rows, cols = x.shape
-    op_rows, op_k = (rows, cols) if direction == DIR_ROW else (cols, rows)
-    code_shape = (cols, rows) if direction == DIR_COL_T else (rows, cols)
-    codes = torch.empty(code_shape, dtype=torch.uint8, device=x.device)
-    nbytes = scale_bytes(op_rows, op_k, layout)
-    scales = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
-    with torch.cuda.device(x.device):
-        check(load().dw_mxfp8_quantize(x.data_ptr(), codes.data_ptr(), scales.data_ptr(), rows, cols,
-                                       direction, rule, layout, _stream(x.device)), "dw_mxfp8_quantize")
-    if layout == SF_FLAT:
-        scales = scales.view(op_rows, (op_k + 31) // 32)
-    return codes.view(torch.float8_e4m3fn), scales
+    return ext().quantize(x, direction, rule, layout)
 
 
 def quantize_both(x: torch.Tensor, rule: int = RULE_OCP_FLOOR, layout: int = SF_TILED):
     """One read of x -> (codes_row, scales_row, codes_col_t, scales_col).  See dw_mxfp8_quantize_both."""
-    _require_cuda(x, "input")
-    if x.dtype != torch.bfloat16 or x.dim() != 2:
-        raise RuntimeError("input must be a 2-D bfloat16 tensor")
-    x = x.contiguous()
-    rows, cols = x.shape
-    dev = x.device
-    cr = torch.empty((rows, cols), dtype=torch.uint8, device=dev)
-    ct = torch.empty((cols, rows), dtype=torch.uint8, device=dev)
-    sr = torch.empty(scale_bytes(rows, cols, layout), dtype=torch.uint8, device=dev)
-    sc = torch.empty(scale_bytes(cols, rows, layout), dtype=torch.uint8, device=dev)
-    with torch.cuda.device(dev):
-        check(load().dw_mxfp8_quantize_both(x.data_ptr(), cr.data_ptr(), sr.data_ptr(), ct.data_ptr(), sc.data_ptr(),
-                                            rows, cols, rule, layout, _stream(dev)), "dw_mxfp8_quantize_both")
-    if layout == SF_FLAT:
-        sr = sr.view(rows, (cols + 31) // 32)
-        sc = sc.view(cols, (rows + 31) // 32)
-    return cr.view(torch.float8_e4m3fn), sr, ct.view(torch.float8_e4m3fn), sc
+    return ext().quantize_both(x, rule, layout)
+
+
+def quantize_both_colsum(x: torch.Tensor, rule: int = RULE_OCP_FLOOR, layout: int = SF_TILED, out_dtype=torch.float32):
+    """quantize_both plus the column sums of x ([cols], fp32 or bf16) from the same read.  See dw_mxfp8_quantize_both_colsum."""
+    return ext().quantize_both_colsum(x, rule, layout, out_dtype == torch.bfloat16)
 
 
 def dequantize(codes: torch.Tensor, scales: torch.Tensor, layout: int = SF_FLAT) -> torch.Tensor:
@@ -158,11 +160,16 @@ _status_words = {}
 
 def status_word(device) -> torch.Tensor:
     """Per-device int32 the GEMM kernel sets if one of its bounded waits expires."""
-    key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
-    w = _status_words.get(key)
+    w = _status_words.get(device)
     if w is None:
-        w = torch.zeros(1, dtype=torch.int32, device=f"cuda:{key}")
-        _status_words[key] = w
+        dev = torch.device(device)
+        key = dev.index if dev.index is not None else torch.cuda.current_device()
+        w = _status_words.get(key)
+        if w is None:
+            w = torch.zeros(1, dtype=torch.int32, device=f"cuda:{key}")
+            _status_words[key] = w
+        if dev.index is not None:
+            _status_words[device] = w         # torch.device and "cuda:N" keys hit on the first lookup next time
     return w
 
 
@@ -170,32 +177,7 @@ def gemm(a_codes: torch.Tensor, a_sf: torch.Tensor, b_codes: torch.Tensor, b_sf:
          out: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None, alpha: float = 1.0,
          beta: float = 0.0) -> torch.Tensor:
     """D[M,N] = alpha * A[M,K] . B[N,K]^T + beta * D + bias; operands as produced by quantize(..., SF_TILED)."""
-    for t, n in ((a_codes, "A"), (b_codes, "B"), (a_sf, "A scales"), (b_sf, "B scales")):
-        _require_cuda(t, n)
-    if a_codes.dim() != 2 or b_codes.dim() != 2:
-        raise RuntimeError("operands must be 2-D")
-    M, K = a_codes.shape
-    N, Kb = b_codes.shape
-    if K != Kb:
-        raise RuntimeError(f"contraction mismatch: A is [{M},{K}], B is [{N},{Kb}]")
-    dev = a_codes.device
-    if a_sf.numel() < scale_bytes(M, K, SF_TILED) or b_sf.numel() < scale_bytes(N, K, SF_TILED):
-        raise RuntimeError("scale buffers must be in the tiled (tcgen05) layout")
-    if out is None:
-        out = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
-    elif out.shape != (M, N) or out.dtype != torch.bfloat16 or not out.is_contiguous():
-        raise RuntimeError("out must be a contiguous bfloat16 [M, N] tensor")
-    if bias is not None and (bias.dtype != torch.bfloat16 or bias.numel() != N or not bias.is_contiguous()):
-        raise RuntimeError("bias must be a contiguous bfloat16 [N] tensor")
-    sw = status_word(dev)
-    ws_bytes = int(load().dw_mxfp8_gemm_workspace(M, N, K))      # non-zero when the GEMM will split K
-    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev) if ws_bytes else None
-    with torch.cuda.device(dev):
-        check(load().dw_mxfp8_gemm(a_codes.data_ptr(), a_sf.data_ptr(), b_codes.data_ptr(), b_sf.data_ptr(),
-                                   out.data_ptr(), None if bias is None else bias.data_ptr(), M, N, K,
-                                   float(alpha), float(beta), None if ws is None else ws.data_ptr(), ws_bytes,
-                                   sw.data_ptr(), _stream(dev)), "dw_mxfp8_gemm")
-    return out
+    return ext().gemm(a_codes, a_sf, b_codes, b_sf, out, bias, float(alpha), float(beta), status_word(a_codes.device))
 
 
 ACTIVATIONS = {"none": 0, "relu": 1, "gelu": 2, "silu": 3}
@@ -238,6 +220,7 @@ def check_status(device=None) -> None:
         check(rc, f"GEMM kernel (status word {code & 0xFF}, CTA {code >> 8})")
 
 
-def set_gemm_variant(v: int, group_m: int = 0, splits: int = 0) -> None:
-    """Kernel variant (0 = automatic), raster band height and split-K count for later GEMMs."""
-    check(load().dw_mxfp8_gemm_set_variant(int(v) | (int(group_m) << 8) | (int(splits) << 16)), "dw_mxfp8_gemm_set_variant")
+def set_gemm_variant(v: int, group_m: int = 0, splits: int = 0, direct_stores: bool = False) -> None:
+    """Kernel variant (0 = automatic), raster band height, split-K count and output store path for later GEMMs."""
+    check(load().dw_mxfp8_gemm_set_variant(int(v) | (int(group_m) << 8) | (int(splits) << 16) | (int(bool(direct_stores)) << 24)),
+          "dw_mxfp8_gemm_set_variant")

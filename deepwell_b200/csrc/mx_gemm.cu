@@ -11,7 +11,10 @@
 //   warp 1      MMA issuer (one thread): tcgen05.cp moves the stage's scales into TMEM, then four
 //               tcgen05.mma.kind::mxf8f6f4.block_scale (K = 32 each) accumulate into TMEM;
 //               tcgen05.commit hands the stage back to the producer
-//   warps 2-5   epilogue: tcgen05.ld the fp32 accumulator, alpha/beta/bias, bf16, global stores
+//   warps 2-9   epilogue, two warps per TMEM lane quadrant, each on half of the columns: tcgen05.ld
+//               the fp32 accumulator, alpha/beta/bias/activation, bf16, then shared memory and a TMA
+//               store per 32 x 32 box (per-thread stores for ragged N, beta reads, split-K partials
+//               and the fused quantised output)
 //
 // kCtas == 2 pairs two CTAs (a cluster of 2 along M) on one 256 x BN tile with cta_group::2: each
 // CTA stages its own half of A and its own half of B; the leader CTA issues the MMAs for both.
@@ -51,8 +54,14 @@ struct GemmParams {
     //   [2] MMA issuer: shared accumulator columns drained (previous tile)
     //   [3] MMA issuer: operand data   [4] epilogue warp 2: accumulator finished   [7] kernel cycles
     long long* wait_cycles;
+    // 1: the bf16 output leaves through shared memory and TMA stores (tm_d is valid); 0: per-thread stores
+    int tma_store;
 };
 constexpr int kWaitCounters = 8;
+// warp 0: TMA producer, warp 1: MMA issuer, warps 2-9: epilogue (two warps per TMEM lane quadrant,
+// each taking half of the accumulator's columns)
+constexpr int kEpilogueWarps = 8;
+constexpr int kGemmThreads = 64 + 32 * kEpilogueWarps;
 
 template <int BN, int kCtas, int kGroup>
 struct GemmCfg {
@@ -62,7 +71,11 @@ struct GemmCfg {
     static constexpr int kBRows = BN / kCtas;             // B rows staged by one CTA
     static constexpr int kBBytes = kBRows * kBK;
     static constexpr int kSfaBytes = 512;
-    static constexpr int kSfbTiles = BN / 128;
+    // 128-row scale tiles of B that a BN-wide column tile can touch: with BN = 192 every other tile
+    // starts 64 rows into its first scale tile.  (BN must be a multiple of 64: a 224-wide tile, whose
+    // scales would start at an odd tensor-memory column, raised "misaligned address" on B200.)
+    static_assert(BN % 64 == 0, "column tile width");
+    static constexpr int kSfbTiles = (BN % 128 == 0) ? BN / 128 : (BN + 64 + 127) / 128;
     static constexpr int kSfbBytes = kSfbTiles * 512;
     static constexpr int kStageBytes = (kABytes + kBBytes + kSfaBytes + kSfbBytes + 1023) / 1024 * 1024;
     static constexpr int kFit = 212 * 1024 / kStageBytes;
@@ -82,7 +95,12 @@ struct GemmCfg {
     static constexpr int kSfSetCols = 16;                  // columns per scale set (A: 4, B: up to 8)
     static constexpr int kTmemCols = 512;
     static constexpr int kBarrierBytes = 256;
-    static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
+    // Output staging for the TMA-store epilogue: per epilogue warp one slot of 32 rows x 32 bf16
+    // columns (64-byte rows, 64-byte swizzle).
+    static constexpr int kOutSlotBytes = 32 * 64;
+    static constexpr int kOutBytes = 8 * kOutSlotBytes;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kOutBytes + kBarrierBytes + 1024;  // + alignment slack
+    static_assert(kSmemBytes <= 227 * 1024, "shared memory per CTA");
     static constexpr uint32_t kTxBytes = kCtas * (kABytes + kBBytes + kSfaBytes + kSfbBytes);
     static_assert(kSfBase + 2 * kSfSetCols <= kTmemCols && 4 + 4 * kSfbTiles <= kSfSetCols, "TMEM columns");
     static_assert(kAccStride + BN <= kSfBase, "accumulators must not reach the scale columns");
@@ -101,10 +119,10 @@ __device__ __forceinline__ float apply_activation(float x, int act) {
 enum : int { kErrProducer = 1, kErrMmaFull = 2, kErrMmaAcc = 3, kErrEpilogue = 4 };
 
 template <int BN, int kCtas, int kGroup>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(kGemmThreads, 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
-               const GemmParams p) {
+               const __grid_constant__ CUtensorMap tm_d, const GemmParams p) {
     using Cfg = GemmCfg<BN, kCtas, kGroup>;
     constexpr int kStages = Cfg::kStages, kAcc = Cfg::kAccStages;
     extern __shared__ uint8_t smem_raw[];
@@ -120,23 +138,25 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     auto stage_b = [&](int s) { return stage_a(s) + Cfg::kABytes; };
     auto stage_sfa = [&](int s) { return stage_b(s) + Cfg::kBBytes; };
     auto stage_sfb = [&](int s) { return stage_sfa(s) + Cfg::kSfaBytes; };
-    const uint32_t bar_base = smem_base + kStages * Cfg::kStageBytes;
+    const uint32_t out_base = smem_base + kStages * Cfg::kStageBytes;          // 1024-byte aligned
+    const uint32_t bar_base = out_base + Cfg::kOutBytes;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int g) { return bar_base + 8u * (kStages + g); };   // one per group of stages
     auto accf_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
     auto acce_bar = [&](int a) { return bar_base + 8u * (2 * kStages + kAcc + a); };
     const uint32_t ovl_bar = bar_base + 8u * (2 * kStages + 2 * kAcc);   // shared accumulator columns drained
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + kStages * Cfg::kStageBytes + 8 * (2 * kStages + 2 * kAcc + 1));
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem_gen + kStages * Cfg::kStageBytes + Cfg::kOutBytes + 8 * (2 * kStages + 2 * kAcc + 1));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) ptx::mbar_init(full_bar(s), 1);
         for (int g = 0; g < Cfg::kGroups; ++g) ptx::mbar_init(empty_bar(g), 1);
-        for (int a = 0; a < kAcc; ++a) { ptx::mbar_init(accf_bar(a), 1); ptx::mbar_init(acce_bar(a), 4 * kCtas); }
+        for (int a = 0; a < kAcc; ++a) { ptx::mbar_init(accf_bar(a), 1); ptx::mbar_init(acce_bar(a), kEpilogueWarps * kCtas); }
         ptx::mbar_init(ovl_bar, 4 * kCtas);
         *abort_flag = 0;
         ptx::fence_barrier_init();
         ptx::prefetch_tmap(&tm_a); ptx::prefetch_tmap(&tm_b); ptx::prefetch_tmap(&tm_sfa); ptx::prefetch_tmap(&tm_sfb);
+        if (p.tma_store) ptx::prefetch_tmap(&tm_d);
     }
     if (warp == 1) {  // TMEM allocation: one warp, the same warp in both CTAs of a pair
         ptx::tmem_alloc<kCtas>(smem_u32(tmem_slot), Cfg::kTmemCols);
@@ -189,7 +209,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 const int row_a = static_cast<int>(tm * (128 * kCtas) + rank * 128);
                 const int row_b = static_cast<int>(tn * BN + rank * Cfg::kBRows);
                 const int sfa_row = static_cast<int>(tm * kCtas + rank) * nkb;
-                const int sfb_row = static_cast<int>(tn * Cfg::kSfbTiles) * nkb;
+                const int sfb_row = static_cast<int>((tn * BN) / 128u) * nkb;     // first scale tile the column tile touches
                 const int kb_first = static_cast<int>(split * p.kb_per_split);
                 const int kb_end = min(nkb, kb_first + static_cast<int>(p.kb_per_split));
                 for (int kb0 = kb_first; kb0 < kb_end && !err; kb0 += kStages) {
@@ -239,6 +259,14 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 const uint32_t split = unit / p.num_tiles;
                 const int kb_first = static_cast<int>(split * p.kb_per_split);
                 const int kb_end = min(nkb, kb_first + static_cast<int>(p.kb_per_split));
+                // A column tile that starts 32 g rows into its first scale tile reads its B scales from
+                // column g of the copied tiles on (one TMEM column holds the scales of 32 rows); g is 0 or 2.
+                uint32_t sfb_shift = 0;
+                if (BN % 128 != 0) {
+                    uint32_t tm, tn;
+                    tile_coords(unit - split * p.num_tiles, tm, tn);
+                    sfb_shift = ((tn * BN) % 128u) / 32u;
+                }
                 // this accumulator fully drained (two tiles ago) ...
                 if (!timed_wait(acce_bar(acc), acc_phase ^ 1u, 0)) { err = kErrMmaAcc; break; }
                 // ... and the columns it shares with the other accumulator drained (previous tile)
@@ -268,7 +296,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                             for (uint32_t k = 0; k < 4; ++k) {
                                 // +2 descriptor units = 32 bytes along K inside the 128-byte swizzle atom
                                 ptx::tc_mma_mxf8<kCtas>(d_tmem, a_lo0 + s * kStageStep + 2 * k, b_lo0 + s * kStageStep + 2 * k,
-                                                        ptx::idesc_with_sf_ids(idesc, k, k), sfa_t, sfb_t, acc_now | k);
+                                                        ptx::idesc_with_sf_ids(idesc, k, k), sfa_t, sfb_t + sfb_shift, acc_now | k);
                             }
                             // Last stage of a group (or of the tile): the group is free again once the MMAs
                             // issued so far have read it.  (Measured: releasing stages one at a time,
@@ -290,11 +318,15 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             }
         }
     } else {
-        // ================= epilogue (4 warps = 128 TMEM lanes) =================
+        // ================= epilogue (8 warps: 4 TMEM lane quadrants x 2 column halves) =================
         const uint32_t q = warp & 3u;                    // TMEM lane quadrant this warp may read
+        const uint32_t half = (warp - 2u) >> 2;          // which half of the accumulator's columns
         uint32_t acc = 0, acc_phase = 0;
         const bool vec_ok = (p.N % 8) == 0;
-        constexpr int kChunks = BN / 32;
+        constexpr int kChunks = BN / 32, kHalfChunks = (kChunks + 1) / 2;
+        const int ch_begin = static_cast<int>(half) * kHalfChunks;
+        const int ch_count = min(kChunks, ch_begin + kHalfChunks) - ch_begin;
+        const uint32_t slot = out_base + (warp - 2u) * Cfg::kOutSlotBytes;
         for (uint32_t unit = worker; unit < num_units && !err; unit += num_workers) {
             const uint32_t split = unit / p.num_tiles, tile = unit - split * p.num_tiles;
             uint32_t tm, tn;
@@ -304,17 +336,18 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             if (!timed_wait(accf_bar(acc), acc_phase, 0)) { err = kErrEpilogue; break; }
             ptx::tc_fence_after();
             const uint32_t t_row = tmem_base + acc * Cfg::kAccStride + ((q * 32u) << 16);
-            // chunk order: the 32 columns shared with the other accumulator first (the last chunk of
-            // accumulator 0, the first chunk of accumulator 1), then the rest
-            const int first_chunk = (Cfg::kOverlap && acc == 0) ? kChunks - 1 : 0;
+            // The 32 columns shared with the other accumulator (the last chunk of accumulator 0, the
+            // first chunk of accumulator 1) are drained first by the warps that own them.
+            const bool shared_last = Cfg::kOverlap && acc == 0 && half == 1;     // shared chunk is this warp's last one
+            const bool owns_shared = Cfg::kOverlap && (acc == 0 ? half == 1 : half == 0);
 #pragma unroll 1
-            for (int it = 0; it < kChunks; ++it) {
-                const int ch = (it == 0) ? first_chunk : ((Cfg::kOverlap && acc == 0) ? it - 1 : it);
+            for (int it = 0; it < ch_count; ++it) {
+                const int ch = ch_begin + (shared_last ? (it == 0 ? ch_count - 1 : it - 1) : it);
                 const int c = ch * 32;
                 uint32_t r[32];
                 ptx::tc_ld_32x32b_x32(t_row + c, r);
                 ptx::tc_wait_ld();
-                if (Cfg::kOverlap && it == 0) {          // shared columns are in registers: release them
+                if (owns_shared && it == 0) {            // shared columns are in registers: release them
                     ptx::tc_fence_before();
                     __syncwarp();
                     if (lane == 0) {
@@ -375,11 +408,32 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 #pragma unroll
                         for (int i = 0; i < 16; ++i)
                             asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o[i]) : "f"(f[2 * i + 1]), "f"(f[2 * i]));
-                        if (p.d != nullptr) {
+                        if (p.d != nullptr && !p.tma_store) {
                             uint16_t* dst = p.d + row * p.N + col;
 #pragma unroll
                             for (int v = 0; v < 4; ++v)
                                 *reinterpret_cast<uint4*>(dst + 8 * v) = make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
+                        }
+                    }
+                    if (p.tma_store && row - lane < p.M) {
+                        // This warp's 32 rows x 32 columns go to its staging slot (row r at 64 r, its four
+                        // 16-byte pieces permuted by the 64-byte swizzle so that the stores of a quarter
+                        // warp cover all banks), then one TMA store writes the box as whole 64-byte row
+                        // segments and clips rows beyond M.  The slot is refilled only after the previous
+                        // store has read it.
+                        if (lane == 0) ptx::bulk_wait_read<0>();
+                        __syncwarp();
+                        if (in_rows) {
+                            const uint32_t row_addr = slot + lane * 64u, sw = (lane >> 1) & 3u;
+#pragma unroll
+                            for (uint32_t v = 0; v < 4; ++v)
+                                ptx::sts_v4(row_addr + ((v ^ sw) << 4), o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
+                        }
+                        ptx::fence_proxy_async();
+                        __syncwarp();
+                        if (lane == 0) {
+                            ptx::tma_store_2d(&tm_d, slot, static_cast<int>(col), static_cast<int>(row - lane));
+                            ptx::bulk_commit();
                         }
                     }
                     if (p.q_codes != nullptr) {
@@ -424,6 +478,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             }
             if (++acc == kAcc) { acc = 0; acc_phase ^= 1u; }
         }
+        if (p.tma_store && lane == 0) ptx::bulk_wait<0>();   // staged output has left shared memory and is written
     }
 
     // ================= common exit =================
@@ -521,8 +576,21 @@ static bool make_sf_map(CUtensorMap* m, const void* base, int64_t tiles) {
                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// bf16 D [M, N] row-major for the epilogue's stores: box = 32 rows x 32 columns (64 bytes), 64-byte swizzle
+static bool make_output_map(CUtensorMap* m, const void* base, int64_t M, int64_t N) {
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(M)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(N) * 2u};
+    const cuuint32_t box[2] = {32u, 32u};
+    const cuuint32_t estr[2] = {1u, 1u};
+    return encode_fn()(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static int g_tma_store = 1;
 static int g_group_m = 0;  // row tiles per raster band (0 = default)
-// 0 auto; 1: 1 CTA, BN 128; 2: 1 CTA, BN 256; 3: CTA pair (256-row tile), BN 256; 4: CTA pair, BN 128
+// 0 auto; 1: 1 CTA, BN 128; 2: 1 CTA, BN 256; 3: CTA pair (256-row tile), BN 256; 4: CTA pair, BN 128;
+// 5: CTA pair, BN 192 (two whole accumulators in tensor memory, unlike 3)
 static int g_variant = 0;
 
 static int sm_count() {
@@ -538,11 +606,19 @@ static int sm_count() {
 template <int BN, int kCtas, int kGroup>
 static int launch_gemm(const void* a, const void* a_sf, const void* b, const void* b_sf, GemmParams p, cudaStream_t st) {
     using Cfg = GemmCfg<BN, kCtas, kGroup>;
-    CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb;
+    CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb, tm_d;
     const int64_t kt = (p.K / 32 + 3) / 4;
     if (!make_operand_map(&tm_a, a, p.M, p.K, 128) || !make_operand_map(&tm_b, b, p.N, p.K, Cfg::kBRows) ||
         !make_sf_map(&tm_sfa, a_sf, ((p.M + 127) / 128) * kt) || !make_sf_map(&tm_sfb, b_sf, ((p.N + 127) / 128) * kt))
         return DW_ERR_LAUNCH;
+    // D goes out by TMA when its rows are 16-byte multiples (the tensor map's stride rule) and it is
+    // written by the GEMM kernel itself (not by the split-K reduction)
+    p.tma_store = (p.d != nullptr && p.splits <= 1 && p.N % 8 == 0 && g_tma_store) ? 1 : 0;
+    if (p.tma_store) {
+        if (!make_output_map(&tm_d, p.d, p.M, p.N)) return DW_ERR_LAUNCH;
+    } else {
+        tm_d = tm_a;                                        // unused by the kernel
+    }
     p.tiles_m = static_cast<uint32_t>((p.M + 128 * kCtas - 1) / (128 * kCtas));
     p.tiles_n = static_cast<uint32_t>((p.N + BN - 1) / BN);
     p.num_tiles = p.tiles_m * p.tiles_n;
@@ -571,7 +647,7 @@ static int launch_gemm(const void* a, const void* a_sf, const void* b, const voi
     const int workers = std::min<int64_t>(static_cast<int64_t>(p.num_tiles) * p.splits, sm_count() / kCtas);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(workers * kCtas));
-    cfg.blockDim = dim3(192);
+    cfg.blockDim = dim3(kGemmThreads);
     cfg.dynamicSmemBytes = Cfg::kSmemBytes;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -579,7 +655,7 @@ static int launch_gemm(const void* a, const void* a_sf, const void* b, const voi
     attr[0].val.clusterDim.x = kCtas; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (cudaLaunchKernelEx(&cfg, mx_gemm_kernel<BN, kCtas, kGroup>, tm_a, tm_b, tm_sfa, tm_sfb, p) != cudaSuccess) {
+    if (cudaLaunchKernelEx(&cfg, mx_gemm_kernel<BN, kCtas, kGroup>, tm_a, tm_b, tm_sfa, tm_sfb, tm_d, p) != cudaSuccess) {
         cudaGetLastError();
         return DW_ERR_LAUNCH;
     }
@@ -600,10 +676,24 @@ static int g_splits = 0;   // forced split count (0 = automatic)
 
 static GemmPlan plan_gemm(int64_t M, int64_t N, int64_t K) {
     GemmPlan pl;
+    const int64_t nkb = (K + 127) / 128;
     pl.variant = g_variant != 0 ? g_variant : ((N <= 128) ? 1 : (M <= 128 ? 2 : 3));
-    const int ctas = (pl.variant >= 3) ? 2 : 1, bn = (pl.variant == 1 || pl.variant == 4) ? 128 : 256;
+    if (g_variant == 0 && pl.variant == 3) {
+        // 256 x 256 tiles (3) against 256 x 192 tiles (5).  Cost of a round of tiles in units of
+        // (columns x k-blocks): variant 3's two accumulators share 32 tensor-memory columns, so each
+        // tile waits for the previous tile's first epilogue step (about 5 k-blocks of MMA time, measured);
+        // variant 5 has no such wait but moves 17% more operand bytes per flop, which on long problems
+        // costs more than the wait (measured 4-13% slower at M = 16384, K = 4096).
+        // Problems small enough for split-K keep variant 3, which the split heuristic below was measured with.
+        const int64_t pairs = sm_count() / 2, tm = (M + 255) / 256;
+        const bool would_split = tm * ((N + 255) / 256) * 4 <= pairs && nkb >= 32;
+        const int64_t rounds3 = (tm * ((N + 255) / 256) + pairs - 1) / pairs, rounds5 = (tm * ((N + 191) / 192) + pairs - 1) / pairs;
+        const double cost3 = static_cast<double>(rounds3) * 256.0 * (nkb + 5), cost5 = static_cast<double>(rounds5) * 192.0 * (nkb + 1) * 1.15;
+        if (cost5 < cost3 && !would_split) pl.variant = 5;
+    }
+    const int ctas = (pl.variant >= 3) ? 2 : 1, bn = (pl.variant == 1 || pl.variant == 4) ? 128 : (pl.variant == 5 ? 192 : 256);
     const int64_t tiles = ((M + 128 * ctas - 1) / (128 * ctas)) * ((N + bn - 1) / bn);
-    const int64_t workers = sm_count() / ctas, nkb = (K + 127) / 128;
+    const int64_t workers = sm_count() / ctas;
     int64_t splits = 1;
     if (g_splits > 0) splits = std::min<int64_t>(g_splits, nkb);
     // measured on B200: worth it only below a quarter of the GPU (the reduction pass costs ~10 us)
@@ -634,7 +724,8 @@ static int run_gemm(const void* a_codes, const void* a_sf, const void* b_codes, 
         case 1: return launch_gemm<128, 1, 1>(a_codes, a_sf, b_codes, b_sf, p, st);
         case 2: return launch_gemm<256, 1, 1>(a_codes, a_sf, b_codes, b_sf, p, st);
         case 3: return launch_gemm<256, 2, 1>(a_codes, a_sf, b_codes, b_sf, p, st);
-        default: return launch_gemm<128, 2, 1>(a_codes, a_sf, b_codes, b_sf, p, st);
+        case 4: return launch_gemm<128, 2, 1>(a_codes, a_sf, b_codes, b_sf, p, st);
+        default: return launch_gemm<192, 2, 1>(a_codes, a_sf, b_codes, b_sf, p, st);
     }
 }
 
@@ -655,9 +746,11 @@ static int check_gemm_args(const void* a_codes, const void* a_sf, const void* b_
 using namespace dw;
 
 extern "C" DW_API int dw_mxfp8_gemm_set_variant(int variant) {
-    // bits [0,8): kernel variant; bits [8,16): row tiles per raster band; bits [16,24): split-K count (0 = automatic)
+    // bits [0,8): kernel variant; bits [8,16): row tiles per raster band; bits [16,24): split-K count (0 = automatic);
+    // bit 24: write D with per-thread stores instead of TMA stores
     const int v = variant & 0xFF, gm = (variant >> 8) & 0xFF, sp = (variant >> 16) & 0xFF;
-    if (variant < 0 || v > 4) return DW_ERR_BAD_ARG;
+    if (variant < 0 || v > 5) return DW_ERR_BAD_ARG;
+    g_tma_store = ((variant >> 24) & 1) ? 0 : 1;
     g_variant = v;
     g_group_m = gm;
     g_splits = sp;
@@ -709,7 +802,9 @@ extern "C" DW_API int dw_mxfp8_gemm_fused(const void* a_codes, const void* a_sf,
     if (out_codes == nullptr && N % 8 != 0 && activation != DW_ACT_NONE && d_bf16 == nullptr) return DW_ERR_BAD_ARG;
     FusedOut fo;
     fo.act = activation; fo.rule = scale_rule; fo.codes = out_codes; fo.scales = out_scales;
-    const GemmPlan pl = plan_gemm(M, N, K);
+    GemmPlan pl = plan_gemm(M, N, K);
+    // the scale padding of the quantised output is written per 128-column group: keep column tiles that are multiples of 128
+    if (out_codes != nullptr && pl.variant > 4) pl.variant = 3;
     return run_gemm(a_codes, a_sf, b_codes, b_sf, d_bf16, bias_bf16, M, N, K, alpha, beta, pl.variant, 1, nullptr, status_word,
                     static_cast<cudaStream_t>(stream), fo);
 }

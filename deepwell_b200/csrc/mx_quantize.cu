@@ -145,19 +145,22 @@ __global__ void mx_sf_pad_kernel(uint8_t* __restrict__ scales, int64_t rows, int
 // or the four blocks of two consecutive rows, land in 8 different 16-byte bank groups.
 __device__ __forceinline__ uint32_t tile_chunk(uint32_t c, uint32_t r) { return c ^ (r & 7u) ^ ((c >> 3) << 1); }
 
-constexpr int kTileSmemBytes = 2 * 128 * 16 * 16 + 1024;   // two 32 KB tiles + two 512-byte scale staging areas
+constexpr int kTileSmemBytes = 2 * 128 * 16 * 16 + 1024 + 2048;   // two 32 KB tiles + two 512-byte scale staging areas + column sums
 
-template <bool kDoRow, bool kDoCol>
+// kColSum: also leave the fp32 sum of every column over this tile's 128 rows in colsum_partial[tile row][column]
+// (the bias gradient of a linear layer is the column sum of the output gradient that is being quantised here).
+template <bool kDoRow, bool kDoCol, bool kColSum = false>
 __global__ void __launch_bounds__(256)
 mx_quant_tile_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes_row, uint8_t* __restrict__ scales_row,
                      uint8_t* __restrict__ codes_col_t, uint8_t* __restrict__ scales_col, int64_t rows, int64_t cols,
-                     uint32_t tiles_c, uint32_t num_tiles, int rule, int layout) {
+                     uint32_t tiles_c, uint32_t num_tiles, int rule, int layout, float* __restrict__ colsum_partial = nullptr) {
     // Persistent CTA, two tile buffers: the 16-byte cp.async copies of the next tile are in flight
     // while this tile is quantised, so the SM always has loads outstanding.
     extern __shared__ __align__(16) uint8_t tile_smem[];
     typedef uint4 (*TilePtr)[16];
     uint8_t* sf_row = tile_smem + 2 * 128 * 16 * 16;
     uint8_t* sf_col = sf_row + 512;
+    float* cs_stage = reinterpret_cast<float*>(sf_col + 512);       // [4 row blocks][128 columns]
 
     const uint32_t t = threadIdx.x;
     const uint32_t cc = t & 15u;
@@ -254,6 +257,16 @@ mx_quant_tile_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes
 #pragma unroll
         for (int i = 0; i < 32; ++i)      // chunk index XORed with the row, as written by issue_tile
             w[i] = tw[(rb * 32 + i) * 64 + ((tile_chunk(p >> 2, i) << 2) | (p & 3u))];
+        if (kColSum) {      // rows beyond the matrix were zero-filled, so they add nothing
+            float sum_a = 0.0f, sum_b = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                sum_a += __uint_as_float(w[i] << 16);
+                sum_b += __uint_as_float(w[i] & 0xFFFF0000u);
+            }
+            cs_stage[rb * 128 + 2 * p] = sum_a;
+            cs_stage[rb * 128 + 2 * p + 1] = sum_b;
+        }
         uint32_t m = w[0];
 #pragma unroll
         for (int i = 1; i < 32; ++i) m = absmax_bf16x2(m, w[i]);
@@ -294,6 +307,9 @@ mx_quant_tile_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes
         sf_col[(ca & 31u) * 16 + (ca >> 5) * 4 + rb] = static_cast<uint8_t>(sb_a);
         sf_col[(cb & 31u) * 16 + (cb >> 5) * 4 + rb] = static_cast<uint8_t>(sb_b);
         __syncthreads();
+        if (kColSum && t < 128 && c0 + t < cols)
+            colsum_partial[static_cast<int64_t>(tr) * cols + c0 + t] =
+                (cs_stage[t] + cs_stage[128 + t]) + (cs_stage[256 + t] + cs_stage[384 + t]);
         if (layout == DW_SF_TILED) {
             if (t < 32) {
                 uint4* dst = reinterpret_cast<uint4*>(scales_col + (static_cast<int64_t>(tc) * kt_col + tr) * 512);
@@ -448,19 +464,20 @@ static int quantize_row_fast(const uint16_t* x, uint8_t* codes, uint8_t* scales,
     return launch_status();
 }
 
-template <bool kDoRow, bool kDoCol>
+template <bool kDoRow, bool kDoCol, bool kColSum = false>
 static int launch_tile_kernel(const uint16_t* x, uint8_t* cr, uint8_t* sr, uint8_t* ct, uint8_t* sc, int64_t rows, int64_t cols,
-                              uint32_t tiles_c, uint32_t tiles, int rule, int layout, cudaStream_t st) {
+                              uint32_t tiles_c, uint32_t tiles, int rule, int layout, cudaStream_t st,
+                              float* colsum_partial = nullptr) {
     static std::once_flag once;
     static cudaError_t attr_err = cudaSuccess;
     std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute(mx_quant_tile_kernel<kDoRow, kDoCol>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        attr_err = cudaFuncSetAttribute(mx_quant_tile_kernel<kDoRow, kDoCol, kColSum>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         kTileSmemBytes);
     });
     if (attr_err != cudaSuccess) return DW_ERR_LAUNCH;
     const uint32_t grid = std::min<uint32_t>(tiles, static_cast<uint32_t>(num_sms()) * 3u);   // 3 CTAs of 65 KB per SM
-    mx_quant_tile_kernel<kDoRow, kDoCol><<<grid, 256, kTileSmemBytes, st>>>(x, cr, sr, ct, sc, rows, cols, tiles_c, tiles, rule,
-                                                                           layout);
+    mx_quant_tile_kernel<kDoRow, kDoCol, kColSum><<<grid, 256, kTileSmemBytes, st>>>(x, cr, sr, ct, sc, rows, cols, tiles_c, tiles,
+                                                                                    rule, layout, colsum_partial);
     return launch_status();
 }
 
@@ -536,6 +553,64 @@ extern "C" DW_API int dw_mxfp8_quantize_both(const void* x_bf16, void* codes_row
     int rc = dw_mxfp8_quantize(x_bf16, codes_row, scales_row, rows, cols, DW_DIR_ROW, scale_rule, scale_layout, stream);
     if (rc != DW_OK) return rc;
     return dw_mxfp8_quantize(x_bf16, codes_col_t, scales_col, rows, cols, DW_DIR_COL_T, scale_rule, scale_layout, stream);
+}
+
+// out[c] = sum over the row tiles of partial[tile][c].  A block covers 32 columns with 8 threads per column:
+// thread y adds tiles y, y+8, ... in order, then the eight sums are added in order, so the result is reproducible.
+__global__ void __launch_bounds__(256)
+mx_colsum_reduce_kernel(const float* __restrict__ partial, int64_t tiles_r, int64_t cols, void* __restrict__ out, int out_bf16) {
+    __shared__ float part[8][32];
+    const uint32_t tx = threadIdx.x & 31u, ty = threadIdx.x >> 5;
+    const int64_t c = blockIdx.x * 32ll + tx;
+    float acc = 0.0f;
+    if (c < cols)
+        for (int64_t tr = ty; tr < tiles_r; tr += 8) acc += partial[tr * cols + c];
+    part[ty][tx] = acc;
+    __syncthreads();
+    if (ty != 0 || c >= cols) return;
+#pragma unroll
+    for (int y = 1; y < 8; ++y) acc += part[y][tx];
+    if (out_bf16) {
+        uint32_t ob;
+        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(ob) : "f"(0.0f), "f"(acc));
+        static_cast<uint16_t*>(out)[c] = static_cast<uint16_t>(ob & 0xFFFFu);
+    } else {
+        static_cast<float*>(out)[c] = acc;
+    }
+}
+
+extern "C" DW_API size_t dw_mxfp8_colsum_workspace(int64_t rows, int64_t cols) {
+    if (rows <= 0 || cols <= 0) return 0;
+    return static_cast<size_t>((rows + 127) / 128) * static_cast<size_t>(cols) * sizeof(float);
+}
+
+extern "C" DW_API int dw_mxfp8_quantize_both_colsum(const void* x_bf16, void* codes_row, void* scales_row, void* codes_col_t,
+                                                    void* scales_col, int64_t rows, int64_t cols, int scale_rule,
+                                                    int scale_layout, void* colsum_out, int colsum_is_bf16, void* workspace,
+                                                    size_t workspace_bytes, void* stream) {
+    if (rows <= 0 || cols <= 0) return DW_ERR_BAD_ARG;
+    if (!x_bf16 || !codes_row || !scales_row || !codes_col_t || !scales_col || !colsum_out || !workspace) return DW_ERR_BAD_ARG;
+    if (scale_rule != DW_RULE_OCP_FLOOR && scale_rule != DW_RULE_REF_CEIL) return DW_ERR_BAD_ARG;
+    if (scale_layout != DW_SF_FLAT && scale_layout != DW_SF_TILED) return DW_ERR_BAD_ARG;
+    if (rows * cols >= (1ll << 35)) return DW_ERR_TOO_LARGE;
+    if (workspace_bytes < dw_mxfp8_colsum_workspace(rows, cols) || !aligned(workspace, 4) || !aligned(colsum_out, 4))
+        return DW_ERR_BAD_ARG;
+    // only the tiled kernel sums columns: the shapes and alignments it needs are those of a linear layer's gradients
+    if (!(tile_path_ok(x_bf16, rows, cols) && aligned(codes_row, 8) && aligned(codes_col_t, 16) &&
+          (scale_layout == DW_SF_FLAT || (aligned(scales_row, 16) && aligned(scales_col, 16)))))
+        return DW_ERR_BAD_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const uint32_t tiles_c = static_cast<uint32_t>((cols + 127) / 128);
+    const int64_t tiles_r = (rows + 127) / 128;
+    const int rc = launch_tile_kernel<true, true, true>(static_cast<const uint16_t*>(x_bf16), static_cast<uint8_t*>(codes_row),
+                                                        static_cast<uint8_t*>(scales_row), static_cast<uint8_t*>(codes_col_t),
+                                                        static_cast<uint8_t*>(scales_col), rows, cols, tiles_c,
+                                                        static_cast<uint32_t>(tiles_r) * tiles_c, scale_rule, scale_layout, st,
+                                                        static_cast<float*>(workspace));
+    if (rc != DW_OK) return rc;
+    mx_colsum_reduce_kernel<<<static_cast<unsigned>((cols + 31) / 32), 256, 0, st>>>(static_cast<const float*>(workspace), tiles_r,
+                                                                                      cols, colsum_out, colsum_is_bf16);
+    return launch_status();
 }
 
 extern "C" DW_API int dw_mxfp8_dequantize(const void* codes, const void* scales, void* out_bf16, int64_t rows, int64_t cols,

@@ -1,0 +1,193 @@
+// Thin torch-extension layer over the C ABI of libdw_mxfp8.so (module deepwell_b200._C).
+//
+// Same role as the reference's csrc/python_bindings.cpp: tensors in, tensors out, outputs allocated
+// with the caller's options, everything on c10::cuda::getCurrentCUDAStream() (reference :88, :96,
+// :211-216).  It holds no kernel and no arithmetic: every function checks its arguments, allocates
+// the outputs and calls one or two entry points of include/dw_mxfp8.h.  It exists because the
+// per-call cost of doing the same from Python (ctypes + several torch.empty) is larger than the GPU
+// time of a GPT-2-sized linear layer.
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <torch/extension.h>
+
+#include <tuple>
+
+#include "../../include/dw_mxfp8.h"
+
+namespace {
+
+using torch::Tensor;
+
+void check_rc(int rc, const char* what) {
+  TORCH_CHECK(rc == DW_OK, what, " failed: ", dw_mxfp8_error_string(rc), " (code ", rc, ")");
+}
+
+Tensor bytes_like(const Tensor& ref, std::initializer_list<int64_t> shape) {
+  return torch::empty(shape, ref.options().dtype(torch::kUInt8));
+}
+
+void* stream_of(const Tensor& t) { return c10::cuda::getCurrentCUDAStream(t.get_device()).stream(); }
+
+const Tensor& require_bf16_2d(const Tensor& x, const char* name) {
+  TORCH_CHECK(x.is_cuda(), name, " must be on CUDA");
+  TORCH_CHECK(x.dim() == 2 && x.scalar_type() == torch::kBFloat16, name, " must be a 2-D bfloat16 tensor");
+  return x;
+}
+
+// bf16 [rows, cols] -> (codes float8_e4m3fn, scales uint8); see dw_mxfp8_quantize
+std::tuple<Tensor, Tensor> quantize(const Tensor& x_in, int64_t direction, int64_t rule, int64_t layout) {
+  require_bf16_2d(x_in, "input");
+  const c10::cuda::CUDAGuard guard(x_in.device());
+  const Tensor x = x_in.contiguous();
+  const int64_t rows = x.size(0), cols = x.size(1);
+  const bool row = direction == DW_DIR_ROW;
+  const int64_t op_rows = row ? rows : cols, op_k = row ? cols : rows;
+  Tensor codes = direction == DW_DIR_COL_T ? bytes_like(x, {cols, rows}) : bytes_like(x, {rows, cols});
+  Tensor scales = bytes_like(x, {static_cast<int64_t>(dw_mxfp8_scale_bytes(op_rows, op_k, static_cast<int>(layout)))});
+  check_rc(dw_mxfp8_quantize(x.data_ptr(), codes.data_ptr(), scales.data_ptr(), rows, cols, static_cast<int>(direction),
+                             static_cast<int>(rule), static_cast<int>(layout), stream_of(x)),
+           "dw_mxfp8_quantize");
+  if (layout == DW_SF_FLAT) scales = scales.view({op_rows, (op_k + 31) / 32});
+  return {codes.view(torch::kFloat8_e4m3fn), scales};
+}
+
+// one read of x -> (codes_row, scales_row, codes_col_t, scales_col); see dw_mxfp8_quantize_both
+std::tuple<Tensor, Tensor, Tensor, Tensor> quantize_both(const Tensor& x_in, int64_t rule, int64_t layout) {
+  require_bf16_2d(x_in, "input");
+  const c10::cuda::CUDAGuard guard(x_in.device());
+  const Tensor x = x_in.contiguous();
+  const int64_t rows = x.size(0), cols = x.size(1);
+  Tensor cr = bytes_like(x, {rows, cols}), ct = bytes_like(x, {cols, rows});
+  Tensor sr = bytes_like(x, {static_cast<int64_t>(dw_mxfp8_scale_bytes(rows, cols, static_cast<int>(layout)))});
+  Tensor sc = bytes_like(x, {static_cast<int64_t>(dw_mxfp8_scale_bytes(cols, rows, static_cast<int>(layout)))});
+  check_rc(dw_mxfp8_quantize_both(x.data_ptr(), cr.data_ptr(), sr.data_ptr(), ct.data_ptr(), sc.data_ptr(), rows, cols,
+                                  static_cast<int>(rule), static_cast<int>(layout), stream_of(x)),
+           "dw_mxfp8_quantize_both");
+  if (layout == DW_SF_FLAT) {
+    sr = sr.view({rows, (cols + 31) / 32});
+    sc = sc.view({cols, (rows + 31) / 32});
+  }
+  return {cr.view(torch::kFloat8_e4m3fn), sr, ct.view(torch::kFloat8_e4m3fn), sc};
+}
+
+// quantize_both plus the column sums of x ([cols], fp32 or bf16); see dw_mxfp8_quantize_both_colsum
+std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> quantize_both_colsum(const Tensor& x_in, int64_t rule, int64_t layout,
+                                                                        bool sum_bf16) {
+  require_bf16_2d(x_in, "input");
+  const c10::cuda::CUDAGuard guard(x_in.device());
+  const Tensor x = x_in.contiguous();
+  const int64_t rows = x.size(0), cols = x.size(1);
+  TORCH_CHECK(rows > 0 && rows % 32 == 0 && cols > 0 && cols % 32 == 0, "rows and cols must be positive multiples of 32");
+  Tensor cr = bytes_like(x, {rows, cols}), ct = bytes_like(x, {cols, rows});
+  Tensor sr = bytes_like(x, {static_cast<int64_t>(dw_mxfp8_scale_bytes(rows, cols, static_cast<int>(layout)))});
+  Tensor sc = bytes_like(x, {static_cast<int64_t>(dw_mxfp8_scale_bytes(cols, rows, static_cast<int>(layout)))});
+  Tensor sum = torch::empty({cols}, x.options().dtype(sum_bf16 ? torch::kBFloat16 : torch::kFloat32));
+  const size_t ws_bytes = dw_mxfp8_colsum_workspace(rows, cols);
+  Tensor ws = bytes_like(x, {static_cast<int64_t>(ws_bytes)});
+  check_rc(dw_mxfp8_quantize_both_colsum(x.data_ptr(), cr.data_ptr(), sr.data_ptr(), ct.data_ptr(), sc.data_ptr(), rows, cols,
+                                         static_cast<int>(rule), static_cast<int>(layout), sum.data_ptr(), sum_bf16 ? 1 : 0,
+                                         ws.data_ptr(), ws_bytes, stream_of(x)),
+           "dw_mxfp8_quantize_both_colsum");
+  if (layout == DW_SF_FLAT) {
+    sr = sr.view({rows, (cols + 31) / 32});
+    sc = sc.view({cols, (rows + 31) / 32});
+  }
+  return {cr.view(torch::kFloat8_e4m3fn), sr, ct.view(torch::kFloat8_e4m3fn), sc, sum};
+}
+
+// D[M,N] = alpha * A[M,K] . B[N,K]^T + beta * D + bias; operands with DW_SF_TILED scales; see dw_mxfp8_gemm
+Tensor gemm(const Tensor& a, const Tensor& a_sf, const Tensor& b, const Tensor& b_sf, const c10::optional<Tensor>& out_in,
+            const c10::optional<Tensor>& bias, double alpha, double beta, const Tensor& status) {
+  TORCH_CHECK(a.is_cuda() && b.is_cuda() && a_sf.is_cuda() && b_sf.is_cuda(), "operands must be on CUDA");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.element_size() == 1 && b.element_size() == 1, "operands must be 2-D one-byte tensors");
+  const int64_t M = a.size(0), K = a.size(1), N = b.size(0);
+  TORCH_CHECK(b.size(1) == K, "contraction mismatch: A is [", M, ",", K, "], B is [", N, ",", b.size(1), "]");
+  TORCH_CHECK(a.is_contiguous() && b.is_contiguous(), "operands must be contiguous");
+  TORCH_CHECK(a_sf.numel() >= static_cast<int64_t>(dw_mxfp8_scale_bytes(M, K, DW_SF_TILED)) &&
+                  b_sf.numel() >= static_cast<int64_t>(dw_mxfp8_scale_bytes(N, K, DW_SF_TILED)),
+              "scale buffers must be in the tiled (tcgen05) layout");
+  const c10::cuda::CUDAGuard guard(a.device());
+  Tensor out;
+  if (out_in.has_value()) {
+    out = *out_in;
+    TORCH_CHECK(out.is_cuda() && out.scalar_type() == torch::kBFloat16 && out.is_contiguous() && out.dim() == 2 &&
+                    out.size(0) == M && out.size(1) == N,
+                "out must be a contiguous bfloat16 [M, N] tensor");
+  } else {
+    out = torch::empty({M, N}, a.options().dtype(torch::kBFloat16));
+  }
+  const void* bias_ptr = nullptr;
+  if (bias.has_value()) {
+    TORCH_CHECK(bias->is_cuda() && bias->scalar_type() == torch::kBFloat16 && bias->numel() == N && bias->is_contiguous(),
+                "bias must be a contiguous bfloat16 [N] tensor");
+    bias_ptr = bias->data_ptr();
+  }
+  const size_t ws_bytes = dw_mxfp8_gemm_workspace(M, N, K);       // non-zero when the GEMM will split K
+  Tensor ws;
+  if (ws_bytes) ws = bytes_like(a, {static_cast<int64_t>(ws_bytes)});
+  check_rc(dw_mxfp8_gemm(a.data_ptr(), a_sf.data_ptr(), b.data_ptr(), b_sf.data_ptr(), out.data_ptr(), bias_ptr, M, N, K,
+                         static_cast<float>(alpha), static_cast<float>(beta), ws_bytes ? ws.data_ptr() : nullptr, ws_bytes,
+                         status.data_ptr(), stream_of(a)),
+           "dw_mxfp8_gemm");
+  return out;
+}
+
+// Forward of the MXFP8 linear layer: quantise x (both forms when the weight gradient will need the
+// column-wise one), GEMM against the cached row-wise weight operand, bias in the epilogue.
+// Returns (y [m, N] bf16, x column-wise codes, x column-wise scales); the last two are empty tensors
+// when save_col is false.  Rows are padded with zeros to a multiple of 32 for the column-wise form.
+std::tuple<Tensor, Tensor, Tensor> linear_forward(const Tensor& x2d, const Tensor& w_codes, const Tensor& w_sf,
+                                                  const c10::optional<Tensor>& bias, bool save_col, int64_t rule,
+                                                  const Tensor& status) {
+  require_bf16_2d(x2d, "input");
+  const int64_t m = x2d.size(0);
+  Tensor xr, xrs, xc, xcs;
+  if (save_col) {
+    const int64_t pad = (32 - m % 32) % 32;
+    const Tensor xp = pad ? torch::constant_pad_nd(x2d, {0, 0, 0, pad}) : x2d;
+    std::tie(xr, xrs, xc, xcs) = quantize_both(xp, rule, DW_SF_TILED);
+  } else {
+    std::tie(xr, xrs) = quantize(x2d, DW_DIR_ROW, rule, DW_SF_TILED);
+  }
+  Tensor y = gemm(xr, xrs, w_codes, w_sf, c10::nullopt, bias, 1.0, 0.0, status);
+  if (y.size(0) != m) y = y.narrow(0, 0, m);
+  return {y, xc, xcs};
+}
+
+// Backward: dX = dY . W (contraction over N, W column-wise), dW = dY^T . X (contraction over the tokens,
+// both operands column-wise), db = column sums of dY (db_mode 0: not wanted, 1: bf16, 2: fp32; taken by the
+// quantiser from its own read of dY when dW is wanted too).  Undefined tensors are returned for gradients that are not needed.
+std::tuple<Tensor, Tensor, Tensor> linear_backward(const Tensor& dy_in, const c10::optional<Tensor>& w_col_codes,
+                                                   const c10::optional<Tensor>& w_col_sf,
+                                                   const c10::optional<Tensor>& x_col_codes,
+                                                   const c10::optional<Tensor>& x_col_sf, int64_t m, int64_t rule,
+                                                   int64_t db_mode, const Tensor& status) {
+  require_bf16_2d(dy_in, "grad_output");
+  const bool need_dx = w_col_codes.has_value(), need_dw = x_col_codes.has_value(), need_db = db_mode != 0;
+  const int64_t pad = (32 - dy_in.size(0) % 32) % 32;
+  const Tensor dy = pad ? torch::constant_pad_nd(dy_in, {0, 0, 0, pad}) : dy_in.contiguous();
+  Tensor dr, drs, dc, dcs, dx, dw, db;
+  if (need_dw && need_db) std::tie(dr, drs, dc, dcs, db) = quantize_both_colsum(dy, rule, DW_SF_TILED, db_mode == 1);
+  else if (need_dw) std::tie(dr, drs, dc, dcs) = quantize_both(dy, rule, DW_SF_TILED);
+  else if (need_dx) std::tie(dr, drs) = quantize(dy, DW_DIR_ROW, rule, DW_SF_TILED);
+  if (need_db && !db.defined()) db = db_mode == 1 ? dy_in.sum({0}) : dy_in.sum({0}, false, torch::kFloat32);
+  if (need_dx) {
+    dx = gemm(dr, drs, *w_col_codes, *w_col_sf, c10::nullopt, c10::nullopt, 1.0, 0.0, status);
+    if (dx.size(0) != m) dx = dx.narrow(0, 0, m);
+  }
+  if (need_dw) dw = gemm(dc, dcs, *x_col_codes, *x_col_sf, c10::nullopt, c10::nullopt, 1.0, 0.0, status);
+  return {dx, dw, db};
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.doc() = "torch-tensor layer over libdw_mxfp8.so (MX quantisation + block-scaled GEMM for sm_100a)";
+  m.def("quantize", &quantize, py::arg("x"), py::arg("direction"), py::arg("rule"), py::arg("layout"));
+  m.def("quantize_both", &quantize_both, py::arg("x"), py::arg("rule"), py::arg("layout"));
+  m.def("quantize_both_colsum", &quantize_both_colsum, py::arg("x"), py::arg("rule"), py::arg("layout"), py::arg("sum_bf16"));
+  m.def("gemm", &gemm, py::arg("a"), py::arg("a_sf"), py::arg("b"), py::arg("b_sf"), py::arg("out") = py::none(),
+        py::arg("bias") = py::none(), py::arg("alpha") = 1.0, py::arg("beta") = 0.0, py::arg("status"));
+  m.def("linear_forward", &linear_forward);
+  m.def("linear_backward", &linear_backward);
+}

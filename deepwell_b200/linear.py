@@ -22,67 +22,53 @@ from typing import Optional, Tuple
 
 import torch
 import torch.nn as nn
-import torch.nn.functional as F
 
 from . import _native as nv
 
 
-def _pad_rows_to_32(t: torch.Tensor) -> torch.Tensor:
-    m = t.shape[0]
-    pad = (-m) % 32
-    return t if pad == 0 else F.pad(t, (0, 0, 0, pad))
-
-
 class _MXFP8LinearFn(torch.autograd.Function):
+    """One call into deepwell_b200._C per direction (linear_forward / linear_backward of
+    csrc/python_bindings.cpp): the quantiser and GEMM launches and their output allocations happen
+    there, so the host cost per layer is one Python->C++ transition each way."""
+
     @staticmethod
     def forward(ctx, x2d: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], module: "DWLinear"):
         need_x_grad, need_w_grad = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
         w_row, w_col = module._quantized_weight(need_col=need_x_grad)
-        xb = x2d.to(torch.bfloat16)
-        m = xb.shape[0]
-        if need_w_grad:
-            xp = _pad_rows_to_32(xb)
-            xr_c, xr_s, xc_c, xc_s = nv.quantize_both(xp, module.scale_rule, nv.SF_TILED)
-            x_col = (xc_c, xc_s)
-        else:
-            xp = xb
-            xr_c, xr_s = nv.quantize(xb, nv.DIR_ROW, module.scale_rule, nv.SF_TILED)
-            x_col = None
-        bias_b = None if bias is None else bias.to(torch.bfloat16)
-        y = nv.gemm(xr_c, xr_s, w_row[0], w_row[1], bias=bias_b)
-        if y.shape[0] != m:
-            y = y[:m]
+        bf16 = torch.bfloat16
+        xb = x2d if x2d.dtype is bf16 else x2d.to(bf16)
+        bias_b = bias if bias is None or bias.dtype is bf16 else bias.to(bf16)
+        y, xc_c, xc_s = nv.ext().linear_forward(xb, w_row[0], w_row[1], bias_b, need_w_grad, module.scale_rule,
+                                                nv.status_word(xb.device))
         ctx.module = module
-        ctx.m = m
+        ctx.m = xb.shape[0]
         ctx.x_dtype, ctx.w_dtype = x2d.dtype, weight.dtype
-        ctx.has_bias = bias is not None
         ctx.bias_dtype = None if bias is None else bias.dtype
-        ctx.x_col = x_col
+        ctx.x_col = (xc_c, xc_s) if need_w_grad else None
         ctx.w_col = w_col
-        return y if x2d.dtype == torch.bfloat16 else y.to(x2d.dtype)
+        return y if x2d.dtype is bf16 else y.to(x2d.dtype)
 
     @staticmethod
     def backward(ctx, dy: torch.Tensor):
         module = ctx.module
-        need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
-        dyb = _pad_rows_to_32(dy.to(torch.bfloat16).contiguous())
-        dx = dw = db = None
-        if need_dw:
-            dr_c, dr_s, dc_c, dc_s = nv.quantize_both(dyb, module.scale_rule, nv.SF_TILED)
-        else:
-            dr_c, dr_s = nv.quantize(dyb, nv.DIR_ROW, module.scale_rule, nv.SF_TILED)
+        need_dx, need_dw, need_db = ctx.needs_input_grad[:3]
+        bf16 = torch.bfloat16
+        dyb = dy if dy.dtype is bf16 else dy.to(bf16)
+        w_cc = w_cs = x_cc = x_cs = None
         if need_dx:
-            w_col = ctx.w_col if ctx.w_col is not None else module._quantized_weight(need_col=True)[1]
-            dx = nv.gemm(dr_c, dr_s, w_col[0], w_col[1])[: ctx.m]
-            if ctx.x_dtype != torch.bfloat16:
-                dx = dx.to(ctx.x_dtype)
+            w_cc, w_cs = ctx.w_col if ctx.w_col is not None else module._quantized_weight(need_col=True)[1]
         if need_dw:
-            xc_c, xc_s = ctx.x_col
-            dw = nv.gemm(dc_c, dc_s, xc_c, xc_s)
-            if ctx.w_dtype != torch.bfloat16:
-                dw = dw.to(ctx.w_dtype)
-        if ctx.has_bias and ctx.needs_input_grad[2]:
-            db = dy.sum(dim=0).to(ctx.bias_dtype)
+            x_cc, x_cs = ctx.x_col
+        need_db = need_db and ctx.bias_dtype is not None
+        db_mode = 0 if not need_db else (1 if ctx.bias_dtype is bf16 else 2)       # bf16 sums only for a bf16 bias
+        dx, dw, db = nv.ext().linear_backward(dyb, w_cc, w_cs, x_cc, x_cs, ctx.m, module.scale_rule, db_mode,
+                                              nv.status_word(dyb.device))
+        if need_dx and ctx.x_dtype is not bf16:
+            dx = dx.to(ctx.x_dtype)
+        if need_dw and ctx.w_dtype is not bf16:
+            dw = dw.to(ctx.w_dtype)
+        if need_db and db.dtype is not ctx.bias_dtype:
+            db = db.to(ctx.bias_dtype)
         return dx, dw, db, None
 
 
@@ -94,7 +80,7 @@ class DWLinear(nn.Module):
         super().__init__()
         if in_features % 32 or out_features % 32:
             raise ValueError("DWLinear needs in_features and out_features to be multiples of 32 (the MX block size)")
-        nv.load()
+        nv.ext()
         self.in_features, self.out_features = in_features, out_features
         kw = {"device": device, "dtype": dtype}
         self.weight = nn.Parameter(torch.empty(out_features, in_features, **kw))
@@ -119,7 +105,7 @@ class DWLinear(nn.Module):
         nn.Module.__init__(mod)
         if linear.in_features % 32 or linear.out_features % 32:
             raise ValueError("DWLinear needs in_features and out_features to be multiples of 32")
-        nv.load()
+        nv.ext()
         mod.in_features, mod.out_features = linear.in_features, linear.out_features
         mod.weight = linear.weight
         mod.bias = linear.bias

@@ -73,6 +73,24 @@ int dw_mxfp8_quantize_both(const void *x_bf16, void *codes_row, void *scales_row
                            void *scales_col, int64_t rows, int64_t cols, int scale_rule,
                            int scale_layout, void *stream);
 
+/* dw_mxfp8_quantize_both plus the sum of every column of x, from the same read: for an output
+ * gradient dY [tokens, out_features] the column sums are the bias gradient, which otherwise costs
+ * one more pass over dY.  colsum_out: [cols], fp32 (colsum_is_bf16 == 0) or bf16 (== 1, rounded once
+ * from the fp32 sum).  The sums are accumulated in fp32 in a fixed order, so repeated calls give
+ * identical bits.
+ * workspace: dw_mxfp8_colsum_workspace(rows, cols) bytes, 4-byte aligned.
+ * Needs rows % 32 == 0, cols % 32 == 0 and 16-byte aligned x, payload and (tiled) scale pointers
+ * (DW_ERR_BAD_ARG otherwise); all four outputs are required.
+ * The reference's linear replacement has a forward only (OptimizedLinear,
+ * src/deepwell/kernels/production_kernels.py:145-194); this is the backward companion of
+ * dw_mxfp8_quantize_both. */
+size_t dw_mxfp8_colsum_workspace(int64_t rows, int64_t cols);
+int dw_mxfp8_quantize_both_colsum(const void *x_bf16, void *codes_row, void *scales_row,
+                                  void *codes_col_t, void *scales_col, int64_t rows, int64_t cols,
+                                  int scale_rule, int scale_layout, void *colsum_out,
+                                  int colsum_is_bf16, void *workspace, size_t workspace_bytes,
+                                  void *stream);
+
 /* codes [rows, cols] (row-wise blocks) + scales -> bf16 [rows, cols].
  * Replaces dequantize_from_mxfp8_bf16, csrc/mxfp8_quantization.cu:267-284. */
 int dw_mxfp8_dequantize(const void *codes, const void *scales, void *out_bf16, int64_t rows,
@@ -157,7 +175,8 @@ int dw_mxfp8_check_status(const void *status_word, void *stream);
 int dw_mxfp8_gemm_set_timing_buffer(void *device_buffer, size_t bytes);
 
 /* Selects the GEMM kernel variant (bits 0-7), raster band height (bits 8-15) and split-K count
- * (bits 16-23) for later dw_mxfp8_gemm calls in this process (0 = automatic).  Counterpart of BlackwellGemmKernel::set_cluster_shape /
+ * (bits 16-23) for later dw_mxfp8_gemm calls in this process (0 = automatic); bit 24 set: the output
+ * is written with per-thread stores instead of TMA stores (for comparison and for debugging).  Counterpart of BlackwellGemmKernel::set_cluster_shape /
  * enable_tmem_residency, csrc/cutlass_kernels.cpp:265-272 (flags the reference stores and ignores). */
 int dw_mxfp8_gemm_set_variant(int variant);
 

@@ -26,7 +26,9 @@ def load_build_module():
 @pytest.fixture(scope="session")
 def native_lib():
     """Builds (if stale) and loads the C-ABI library."""
-    load_build_module().build()            # before the package is imported: its import loads the library
+    b = load_build_module()                # before the package is imported: its import loads the library
+    b.build()
+    b.build_ext()
     from deepwell_b200 import _native
     return _native.load()
 

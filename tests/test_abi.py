@@ -74,3 +74,20 @@ def test_product_does_not_import_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h")):
                 text = open(os.path.join(dirpath, f)).read()
                 assert "oracle" not in text.replace("the oracle", ""), f"{f} refers to the oracle package"
+
+
+def test_tensor_layer_loads_and_refuses_cpu_tensors(native_lib):
+    """deepwell_b200._C (csrc/python_bindings.cpp) imports, exports the per-layer calls and has no CPU path."""
+    import torch
+    from deepwell_b200 import _native
+    ext = _native.ext()
+    for name in ("quantize", "quantize_both", "gemm", "linear_forward", "linear_backward"):
+        assert callable(getattr(ext, name)), name
+    x = torch.zeros(32, 32, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="must be on CUDA"):
+        ext.quantize(x, _native.DIR_ROW, _native.RULE_OCP_FLOOR, _native.SF_FLAT)
+    with pytest.raises(RuntimeError, match="must be on CUDA"):
+        ext.quantize_both(x, _native.RULE_OCP_FLOOR, _native.SF_TILED)
+    u8 = torch.zeros(32, 32, dtype=torch.uint8)
+    with pytest.raises(RuntimeError, match="must be on CUDA"):
+        ext.gemm(u8, u8, u8, u8, None, None, 1.0, 0.0, torch.zeros(1, dtype=torch.int32))

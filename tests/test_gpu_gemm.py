@@ -11,7 +11,7 @@ from oracle import mx_oracle as o
 
 pytestmark = pytest.mark.gpu
 RTOL = 1e-2
-VARIANTS = [1, 2, 3, 4]      # 1 CTA x BN128, 1 CTA x BN256, CTA pair x BN256, CTA pair x BN128
+VARIANTS = [1, 2, 3, 4, 5]   # 1 CTA x BN128, 1 CTA x BN256, CTA pair x BN256, CTA pair x BN128, CTA pair x BN192
 
 
 @pytest.fixture(scope="module")
@@ -82,6 +82,29 @@ def test_alpha_beta_bias(nv, variant):
     run(nv, 384, 640, 512, alpha=0.5, beta=2.0, use_bias=True)
     run(nv, 200, 104, 64, alpha=-1.25, beta=0.0, use_bias=True)       # N % 8 == 0 but ragged tiles
     run(nv, 96, 100, 64, alpha=1.0, beta=1.0, use_bias=False)          # N % 8 != 0: scalar store path
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+def test_tma_store_and_direct_store_epilogues_agree(nv, variant):
+    """The bf16 output written through shared memory + TMA stores equals the per-thread-store path bit for bit,
+    also where the last row/column tiles are ragged (the TMA store clips them)."""
+    for M, N, K in [(512, 768, 256), (300, 200, 160), (129, 2056, 128), (1000, 520, 96)]:
+        g = torch.Generator("cpu").manual_seed(M + N + K)
+        x = torch.randn(M, K, generator=g).bfloat16().cuda()
+        w = (torch.randn(N, K, generator=g) * 0.02).bfloat16().cuda()
+        bias = torch.randn(N, generator=g).bfloat16().cuda()
+        xc, xs = nv.quantize(x, nv.DIR_ROW, 0, nv.SF_TILED)
+        wc, ws = nv.quantize(w, nv.DIR_ROW, 0, nv.SF_TILED)
+        outs = []
+        for direct in (False, True):
+            nv.set_gemm_variant(variant, direct_stores=direct)
+            guard = torch.full((M + 1, N), -7.0, dtype=torch.bfloat16, device="cuda")      # one row past the output
+            nv.gemm(xc, xs, wc, ws, out=guard[:M], bias=bias)
+            nv.check_status()
+            assert (guard[M] == -7.0).all()
+            outs.append(guard[:M].clone())
+        nv.set_gemm_variant(0)
+        assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16)), (M, N, K)
 
 
 @pytest.mark.parametrize("variant", [0, 3])

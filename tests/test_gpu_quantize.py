@@ -179,3 +179,33 @@ def test_largest_sweep_point_2_pow_32_elements(nv):
     xs = x[:, csel].t().contiguous()                        # [3, rows]: the sampled columns as rows
     ec, ecs = c.quantize_rowwise(bits_of(xs), 0)
     assert np.array_equal(host(tc[csel]), ec) and np.array_equal(host(ts[csel]), ecs)
+
+
+@pytest.mark.parametrize("rows,cols", [(32, 32), (160, 96), (4096, 768), (8192, 3072), (1000 * 32, 128)])
+def test_quantize_both_with_column_sums(nv, rows, cols):
+    """dw_mxfp8_quantize_both_colsum: the four quantised outputs are those of dw_mxfp8_quantize_both bit for bit;
+    the column sums match a float64 sum within fp32 accumulation error (tolerance: 1e-5 x the column's sum of
+    magnitudes, plus bf16 rounding of the result in bf16 mode), and two calls give identical bits."""
+    g = torch.Generator("cuda").manual_seed(rows * 7 + cols)
+    x = torch.randn(rows, cols, device="cuda", generator=g)
+    x[torch.rand(rows, cols, device="cuda", generator=g) < 0.01] *= 50
+    x = (x + 0.25).bfloat16()                     # non-zero mean so that the sums do not cancel to nothing
+    ref4 = nv.quantize_both(x, 0, nv.SF_TILED)
+    got = nv.quantize_both_colsum(x, 0, nv.SF_TILED, out_dtype=torch.float32)
+    again = nv.quantize_both_colsum(x, 0, nv.SF_TILED, out_dtype=torch.float32)
+    for a, b in zip(ref4, got[:4]):
+        assert torch.equal(a.view(torch.uint8), b.view(torch.uint8))
+    assert torch.equal(got[4].view(torch.int32), again[4].view(torch.int32))
+    exact = x.double().sum(0)
+    bound = 1e-5 * x.double().abs().sum(0) + 1e-30
+    assert ((got[4].double() - exact).abs() <= bound).all()
+    as_bf16 = nv.quantize_both_colsum(x, 0, nv.SF_TILED, out_dtype=torch.bfloat16)[4]
+    assert as_bf16.dtype == torch.bfloat16
+    assert torch.equal(as_bf16.view(torch.int16), got[4].bfloat16().view(torch.int16))
+
+
+def test_column_sums_reject_shapes_outside_the_tile_kernel(nv, native_lib):
+    x = torch.zeros(48, 40, dtype=torch.bfloat16, device="cuda")
+    p = x.data_ptr()
+    rc = native_lib.dw_mxfp8_quantize_both_colsum(p, p, p, p, p, 48, 40, 0, 1, p, 0, p, 1 << 20, None)
+    assert rc == -1
