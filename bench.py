@@ -283,6 +283,107 @@ def run_quantize_sweep(args):
 # ----------------------------------------------------------------------------------------------
 # GPU arm
 # ----------------------------------------------------------------------------------------------
+# ----------------------------------------------------------------------------------------------
+# Secondary workload: the end-to-end deepwell.optimize() training step of a pre-LN decoder
+def build_decoder(vocab, hidden, heads, ffn, layers):
+    import torch.nn as nn
+    import torch.nn.functional as F
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.ln1, self.ln2 = nn.LayerNorm(hidden), nn.LayerNorm(hidden)
+            self.qkv, self.proj = nn.Linear(hidden, 3 * hidden), nn.Linear(hidden, hidden)
+            self.up, self.down = nn.Linear(hidden, ffn), nn.Linear(ffn, hidden)
+
+        def forward(self, x):
+            b, s, h = x.shape
+            q, k, v = self.qkv(self.ln1(x)).view(b, s, 3, heads, h // heads).permute(2, 0, 3, 1, 4)
+            a = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+            x = x + self.proj(a.transpose(1, 2).reshape(b, s, h))
+            return x + self.down(F.gelu(self.up(self.ln2(x))))
+
+    class Decoder(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.embed = nn.Embedding(vocab, hidden)
+            self.blocks = nn.ModuleList([Block() for _ in range(layers)])
+            self.ln_f = nn.LayerNorm(hidden)
+            self.head = nn.Linear(hidden, vocab, bias=False)
+
+        def forward(self, ids):
+            x = self.embed(ids)
+            for blk in self.blocks:
+                x = blk(x)
+            return self.head(self.ln_f(x))
+
+    return Decoder()
+
+
+def run_decoder_step(args):
+    """BASELINE config 5: random-init 12-layer pre-LN decoder (hidden 1024, 16 heads, FFN 4096, vocab 32000), batch 8 x
+    sequence 2048 uniform token ids; every nn.Linear replaced by deepwell.optimize(precision='mxfp8').  One step = ids
+    host->device, forward, cross-entropy, backward, fused AdamW step, loss device->host.  The same model with its
+    bf16 nn.Linear layers is timed beside it.  Prints one JSON line; attention (torch SDPA), LayerNorm, GELU, the loss
+    and the optimizer are PyTorch's own in both arms: only the linear layers differ."""
+    import copy
+    import torch.nn.functional as F
+    import deepwell_b200 as dw
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (B200); there is no CPU fallback for the product path")
+    torch.cuda.set_device(0)
+    vocab, hidden, heads, ffn, layers, batch, seq = 32000, 1024, 16, 4096, 12, 8, 2048
+    torch.manual_seed(1234)
+    base = build_decoder(vocab, hidden, heads, ffn, layers).cuda().bfloat16()
+    arms = {"bf16_nn_linear": copy.deepcopy(base), "mxfp8_dwlinear": dw.optimize(copy.deepcopy(base), precision="mxfp8", verbose=False)}
+    del base
+    n_dw = sum(isinstance(m, dw.DWLinear) for m in arms["mxfp8_dwlinear"].modules())
+    lin_params = sum(m.weight.numel() for m in arms["mxfp8_dwlinear"].modules() if isinstance(m, dw.DWLinear))
+    ids_host = torch.randint(0, vocab, (args.steps + args.warmup, batch, seq), generator=torch.Generator().manual_seed(7)).pin_memory()
+    out, losses = {}, {}
+    sampler = ClockSampler(0)
+    sampler.start()
+    for name, net in arms.items():
+        opt = torch.optim.AdamW(net.parameters(), lr=1e-4, fused=True)
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        cur = []
+        for i in range(args.steps + args.warmup):
+            if i == args.warmup:
+                torch.cuda.synchronize()
+                ev0.record()
+            ids = ids_host[i].cuda(non_blocking=True)
+            opt.zero_grad(set_to_none=True)
+            logits = net(ids)
+            loss = F.cross_entropy(logits[:, :-1].reshape(-1, vocab).float(), ids[:, 1:].reshape(-1))
+            loss.backward()
+            opt.step()
+            cur.append(loss.item())
+        ev1.record()
+        torch.cuda.synchronize()
+        out[name] = ev0.elapsed_time(ev1) / args.steps
+        losses[name] = cur
+        del opt
+        arms[name] = None
+        torch.cuda.empty_cache()
+    clocks = sampler.stop()
+    tokens = batch * seq
+    ms = out["mxfp8_dwlinear"]
+    print(json.dumps({
+        "metric": "decoder_train_tokens_per_s", "value": tokens / ms * 1e3, "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "mxfp8 linears (e4m3+e8m0, fp32 accumulate), bf16 elsewhere", "data": "synthetic",
+        "config": {"workload": "preln_decoder_12x1024_ffn4096_vocab32000_b8_s2048_train_step", "dwlinear_modules": n_dw,
+                   "linear_tflop_per_step": 6.0 * lin_params * tokens / 1e12, "optimizer": "AdamW(fused)",
+                   "l2": "activations and weights far larger than L2"},
+        "bf16_nn_linear": {"ms_per_step": out["bf16_nn_linear"], "tokens_per_s": tokens / out["bf16_nn_linear"] * 1e3},
+        "speedup_vs_bf16_nn_linear": out["bf16_nn_linear"] / ms,
+        "loss_first_last": {k: [v[0], v[-1]] for k, v in losses.items()},
+        "e2e": {"value": tokens / ms * 1e3, "unit": "tokens/s", "h2d_bytes_per_step": tokens * 8, "d2h_bytes_per_step": 4,
+                "api": "deepwell_b200.optimize(model, precision='mxfp8'); ids host->device and loss.item() every step"},
+        "clocks": clocks}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -299,6 +400,8 @@ def main():
     ap.add_argument("--serial", action="store_true", help="quantise and GEMM on one stream (no overlap between layers)")
     ap.add_argument("--profile-case", default=None, choices=["gemm", "quant_row", "quant_both", "quant_col"],
                     help="run a few launches of one kernel on a small case (for an ncu capture) and exit")
+    ap.add_argument("--workload", default="linears", choices=["linears", "decoder_step"],
+                    help="linears: the headline Llama-3-8B linear shapes; decoder_step: end-to-end optimize() training step (1 GPU)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -313,6 +416,10 @@ def main():
         return
     if args.sweep_quantize:
         run_quantize_sweep(args)
+        return
+    if args.workload == "decoder_step":
+        if rank == 0:
+            run_decoder_step(args)
         return
 
     import torch.distributed as dist

@@ -230,23 +230,9 @@ mx_quant_tile_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes
             }
             sf_row[(r & 31u) * 16 + (r >> 5) * 4 + b] = static_cast<uint8_t>(sb);
         }
-        __syncthreads();
-    }
-
-    if (kDoRow) {  // scales of the row-wise operand [rows, cols/32]
-        if (layout == DW_SF_TILED) {
-            if (t < 32) {
-                uint4* dst = reinterpret_cast<uint4*>(scales_row + (static_cast<int64_t>(tr) * kt_row + tc) * 512);
-                dst[t] = reinterpret_cast<const uint4*>(sf_row)[t];
-            }
-        } else if (t < 128) {
-            const int64_t gr = r0 + t, kb0 = static_cast<int64_t>(tc) * 4;
-            if (gr < rows) {
-#pragma unroll
-                for (int b = 0; b < 4; ++b)
-                    if (kb0 + b < kb_row) scales_row[gr * kb_row + kb0 + b] = sf_row[(t & 31u) * 16 + (t >> 5) * 4 + b];
-            }
-        }
+        // Measured: on long runs of tiles the passes run slightly faster when the warps enter the column pass
+        // together; on short runs (a few tiles per CTA) the extra barrier costs ~10 %.
+        if (kDoCol && num_tiles > 8u * gridDim.x) __syncthreads();
     }
 
     if (kDoCol) {
@@ -306,25 +292,46 @@ mx_quant_tile_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes
         const uint32_t ca = 2 * p, cb = 2 * p + 1;
         sf_col[(ca & 31u) * 16 + (ca >> 5) * 4 + rb] = static_cast<uint8_t>(sb_a);
         sf_col[(cb & 31u) * 16 + (cb >> 5) * 4 + rb] = static_cast<uint8_t>(sb_b);
-        __syncthreads();
+    }
+    // One barrier per tile after both passes: the tile buffer is free for the copy issued at the top of the
+    // next iteration, and the staged scale bytes (and column sums) are complete.  The next tile's passes
+    // write the staging areas only after the barrier at the top of the loop, which the threads that copy the
+    // staged bytes out (below) reach only when they are done.
+    __syncthreads();
+    if (kDoRow) {  // scales of the row-wise operand [rows, cols/32]: warp 0 (tiled) or warps 0-3 (flat)
+        if (layout == DW_SF_TILED) {
+            if (t < 32) {
+                uint4* dst = reinterpret_cast<uint4*>(scales_row + (static_cast<int64_t>(tr) * kt_row + tc) * 512);
+                dst[t] = reinterpret_cast<const uint4*>(sf_row)[t];
+            }
+        } else if (t < 128) {
+            const int64_t gr = r0 + t, kb0 = static_cast<int64_t>(tc) * 4;
+            if (gr < rows) {
+#pragma unroll
+                for (int b = 0; b < 4; ++b)
+                    if (kb0 + b < kb_row) scales_row[gr * kb_row + kb0 + b] = sf_row[(t & 31u) * 16 + (t >> 5) * 4 + b];
+            }
+        }
+    }
+    if (kDoCol) {  // scales of the column-wise operand [cols, rows/32]: warp 7 (tiled) or warps 4-7 (flat)
+        const uint32_t u = 255u - t;
         if (kColSum && t < 128 && c0 + t < cols)
             colsum_partial[static_cast<int64_t>(tr) * cols + c0 + t] =
                 (cs_stage[t] + cs_stage[128 + t]) + (cs_stage[256 + t] + cs_stage[384 + t]);
         if (layout == DW_SF_TILED) {
-            if (t < 32) {
+            if (u < 32) {
                 uint4* dst = reinterpret_cast<uint4*>(scales_col + (static_cast<int64_t>(tc) * kt_col + tr) * 512);
-                dst[t] = reinterpret_cast<const uint4*>(sf_col)[t];
+                dst[u] = reinterpret_cast<const uint4*>(sf_col)[u];
             }
-        } else if (t < 128) {
-            const int64_t gcl = c0 + t, kb0 = static_cast<int64_t>(tr) * 4;
+        } else if (u < 128) {
+            const int64_t gcl = c0 + u, kb0 = static_cast<int64_t>(tr) * 4;
             if (gcl < cols) {
 #pragma unroll
                 for (int b = 0; b < 4; ++b)
-                    if (kb0 + b < kb_col) scales_col[gcl * kb_col + kb0 + b] = sf_col[(t & 31u) * 16 + (t >> 5) * 4 + b];
+                    if (kb0 + b < kb_col) scales_col[gcl * kb_col + kb0 + b] = sf_col[(u & 31u) * 16 + (u >> 5) * 4 + b];
             }
         }
     }
-    __syncthreads();   // every read of this buffer and of the staging areas is done before they are reused
     }
 }
 
