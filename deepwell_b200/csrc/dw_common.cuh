@@ -58,13 +58,25 @@ __device__ __forceinline__ uint32_t e8m0_inverse_bf16x2(uint32_t byte) {
     return h | (h << 16);
 }
 
+// The two bf16 lanes of `w`, each times the bf16 power of two in the same lane of `inv2`, as fp32.  The
+// mixed-precision FMA reads the bf16 halves directly, so no shift/mask unpacking is spent on the integer
+// pipe; the product of a bf16 and a power of two is exact in fp32, and the -0.0 addend keeps the sign of a
+// zero product (+0.0 would turn -0.0 into +0.0).
+__device__ __forceinline__ void scale_pair(uint32_t w, uint32_t inv2, float& lo, float& hi) {
+    asm("{\n\t.reg .b16 a0, a1, s0, s1;\n\t"
+        "mov.b32 {a0, a1}, %2;\n\t"
+        "mov.b32 {s0, s1}, %3;\n\t"
+        "fma.rn.f32.bf16 %0, a0, s0, %4;\n\t"
+        "fma.rn.f32.bf16 %1, a1, s1, %4;\n\t}"
+        : "=f"(lo), "=f"(hi) : "r"(w), "r"(inv2), "f"(-0.0f));
+}
+
 // One bf16x2 word times a power of two (`inv2` from e8m0_inverse_bf16x2) -> two E4M3 codes in
-// bits [0,16).  The bf16 product is exact wherever it matters: a result that is subnormal in bf16
-// is far below half the smallest E4M3 step and encodes as zero either way.
+// bits [0,16), element 0 in the low byte.
 __device__ __forceinline__ uint32_t quant_word(uint32_t w, uint32_t inv2) {
-    uint32_t q;
-    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(q) : "r"(w), "r"(inv2));
-    return cvt_e4m3x2(__uint_as_float(q << 16), __uint_as_float(q & 0xFFFF0000u));
+    float lo, hi;
+    scale_pair(w, inv2, lo, hi);
+    return cvt_e4m3x2(lo, hi);
 }
 
 // amax pattern (15-bit magnitude) over n bf16x2 words, NaN elements dropped as fmaxf would.

@@ -267,11 +267,11 @@ mx_quant_tile_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes
             uint32_t ca[2], cb[2];
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                uint32_t s0, s1;   // rows 4i+2h and 4i+2h+1, both columns scaled at once
-                asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(s0) : "r"(w[4 * i + 2 * h]), "r"(inv2));
-                asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(s1) : "r"(w[4 * i + 2 * h + 1]), "r"(inv2));
-                ca[h] = cvt_e4m3x2(__uint_as_float(s0 << 16), __uint_as_float(s1 << 16));
-                cb[h] = cvt_e4m3x2(__uint_as_float(s0 & 0xFFFF0000u), __uint_as_float(s1 & 0xFFFF0000u));
+                float a0, b0, a1, b1;   // rows 4i+2h and 4i+2h+1: column a in the low lane, column b in the high lane
+                scale_pair(w[4 * i + 2 * h], inv2, a0, b0);
+                scale_pair(w[4 * i + 2 * h + 1], inv2, a1, b1);
+                ca[h] = cvt_e4m3x2(a0, a1);
+                cb[h] = cvt_e4m3x2(b0, b1);
             }
             qa[i] = __byte_perm(ca[0], ca[1], 0x5410);
             qb[i] = __byte_perm(cb[0], cb[1], 0x5410);
