@@ -37,7 +37,7 @@ ABI_SYMBOLS = (
     "dw_mxfp8_quantize", "dw_mxfp8_quantize_both", "dw_mxfp8_dequantize", "dw_mxfp8_gemm",
     "dw_mxfp8_gemm_workspace", "dw_mxfp8_check_status", "dw_mxfp8_gemm_set_variant",
     "dw_mxfp8_gemm_set_timing_buffer", "dw_mxfp8_gemm_splitk_static", "dw_mxfp8_gemm_fused",
-    "dw_mxfp8_colsum_workspace", "dw_mxfp8_quantize_both_colsum",
+    "dw_mxfp8_colsum_workspace", "dw_mxfp8_quantize_both_colsum", "dw_mxfp8_gemm_grouped",
 )
 
 _lib = None
@@ -81,6 +81,7 @@ def load() -> ctypes.CDLL:
     L.dw_mxfp8_gemm_set_variant.argtypes = [i32]
     L.dw_mxfp8_gemm_set_timing_buffer.argtypes = [p, sz]
     L.dw_mxfp8_gemm_fused.argtypes = [p, p, p, p, p, p, i64, i64, i64, f32, f32, i32, p, p, i32, p, p]
+    L.dw_mxfp8_gemm_grouped.argtypes = [p, p, p, p, p, p, i64, i64, i64, i32, i32, f32, p, p]
     L.dw_mxfp8_gemm_splitk_static.argtypes = [p, p, p, p, p, p, i64, i64, i64, f32, f32, i32, p, p]
     _lib = L
     return L
@@ -126,6 +127,23 @@ def quantize(x: torch.Tensor, direction: int = DIR_ROW, rule: int = RULE_OCP_FLO
              layout: int = SF_FLAT) -> Tuple[torch.Tensor, torch.Tensor]:
     """bf16 [rows, cols] -> (codes float8_e4m3fn, scales uint8).  See dw_mxfp8_quantize."""
     return ext().quantize(x, direction, rule, layout)
+
+
+def quantize_into(x: torch.Tensor, codes: torch.Tensor, scales: torch.Tensor, direction: int = DIR_ROW,
+                  rule: int = RULE_OCP_FLOOR, layout: int = SF_TILED) -> None:
+    """dw_mxfp8_quantize into caller-provided buffers (views into larger operands, e.g. one expert's slice of a
+    stacked weight): codes and scales must be contiguous byte tensors of the right size."""
+    _require_cuda(x, "input")
+    if x.dtype != torch.bfloat16 or x.dim() != 2 or not x.is_contiguous():
+        raise RuntimeError("input must be a contiguous 2-D bfloat16 tensor")
+    rows, cols = x.shape
+    op_rows, op_k = (rows, cols) if direction == DIR_ROW else (cols, rows)
+    if codes.numel() * codes.element_size() != rows * cols or not codes.is_contiguous() or not scales.is_contiguous() \
+            or scales.numel() < scale_bytes(op_rows, op_k, layout):
+        raise RuntimeError("output buffers do not match the operand")
+    with torch.cuda.device(x.device):
+        check(load().dw_mxfp8_quantize(x.data_ptr(), codes.data_ptr(), scales.data_ptr(), rows, cols, direction, rule, layout,
+                                       _stream(x.device)), "dw_mxfp8_quantize")
 
 
 def quantize_both(x: torch.Tensor, rule: int = RULE_OCP_FLOOR, layout: int = SF_TILED):
@@ -178,6 +196,28 @@ def gemm(a_codes: torch.Tensor, a_sf: torch.Tensor, b_codes: torch.Tensor, b_sf:
          beta: float = 0.0) -> torch.Tensor:
     """D[M,N] = alpha * A[M,K] . B[N,K]^T + beta * D + bias; operands as produced by quantize(..., SF_TILED)."""
     return ext().gemm(a_codes, a_sf, b_codes, b_sf, out, bias, float(alpha), float(beta), status_word(a_codes.device))
+
+
+def gemm_grouped(a_codes: torch.Tensor, a_sf: torch.Tensor, b_codes: torch.Tensor, b_sf: torch.Tensor,
+                 tile_group: torch.Tensor, num_groups: int, rows_per_tile: int = 256, alpha: float = 1.0) -> torch.Tensor:
+    """One launch over the groups: a_codes [M_total, K] (groups concatenated, each padded to rows_per_tile),
+    b_codes [num_groups * N, K], tile_group int32 [M_total / rows_per_tile] on the device.  See dw_mxfp8_gemm_grouped."""
+    for t, n in ((a_codes, "A"), (b_codes, "B"), (a_sf, "A scales"), (b_sf, "B scales"), (tile_group, "tile_group")):
+        _require_cuda(t, n)
+    M, K = a_codes.shape
+    GN, Kb = b_codes.shape
+    if K != Kb or GN % num_groups:
+        raise RuntimeError(f"shape mismatch: A is [{M},{K}], stacked B is [{GN},{Kb}] for {num_groups} groups")
+    N = GN // num_groups
+    if tile_group.dtype != torch.int32 or tile_group.numel() != M // rows_per_tile or not tile_group.is_contiguous():
+        raise RuntimeError("tile_group must be a contiguous int32 tensor with one entry per row tile")
+    dev = a_codes.device
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    with torch.cuda.device(dev):
+        check(load().dw_mxfp8_gemm_grouped(a_codes.data_ptr(), a_sf.data_ptr(), b_codes.data_ptr(), b_sf.data_ptr(),
+                                           out.data_ptr(), tile_group.data_ptr(), M, N, K, int(num_groups), int(rows_per_tile),
+                                           float(alpha), status_word(dev).data_ptr(), _stream(dev)), "dw_mxfp8_gemm_grouped")
+    return out
 
 
 ACTIVATIONS = {"none": 0, "relu": 1, "gelu": 2, "silu": 3}

@@ -56,6 +56,11 @@ struct GemmParams {
     long long* wait_cycles;
     // 1: the bf16 output leaves through shared memory and TMA stores (tm_d is valid); 0: per-thread stores
     int tma_store;
+    // Grouped GEMM (one launch over the experts of an MoE layer): A is the row-wise concatenation of the
+    // groups' activations, each group padded to whole row tiles; tile_group[row tile] names the group whose
+    // weight (rows [g N, (g + 1) N) of B) that tile multiplies.  nullptr: one ordinary GEMM.
+    const int* tile_group;
+    uint32_t num_groups;
 };
 constexpr int kWaitCounters = 8;
 // warp 0: TMA producer, warp 1: MMA issuer, warps 2-9: epilogue (two warps per TMEM lane quadrant,
@@ -207,9 +212,12 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 uint32_t tm, tn;
                 tile_coords(tile, tm, tn);
                 const int row_a = static_cast<int>(tm * (128 * kCtas) + rank * 128);
-                const int row_b = static_cast<int>(tn * BN + rank * Cfg::kBRows);
+                uint32_t b_first = tn * BN;                                       // first row of B for this column tile
+                if (p.tile_group != nullptr)
+                    b_first += min(static_cast<uint32_t>(max(p.tile_group[tm], 0)), p.num_groups - 1u) * static_cast<uint32_t>(p.N);
+                const int row_b = static_cast<int>(b_first + rank * Cfg::kBRows);
                 const int sfa_row = static_cast<int>(tm * kCtas + rank) * nkb;
-                const int sfb_row = static_cast<int>((tn * BN) / 128u) * nkb;     // first scale tile the column tile touches
+                const int sfb_row = static_cast<int>(b_first / 128u) * nkb;       // first scale tile the column tile touches
                 const int kb_first = static_cast<int>(split * p.kb_per_split);
                 const int kb_end = min(nkb, kb_first + static_cast<int>(p.kb_per_split));
                 for (int kb0 = kb_first; kb0 < kb_end && !err; kb0 += kStages) {
@@ -608,8 +616,9 @@ static int launch_gemm(const void* a, const void* a_sf, const void* b, const voi
     using Cfg = GemmCfg<BN, kCtas, kGroup>;
     CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb, tm_d;
     const int64_t kt = (p.K / 32 + 3) / 4;
-    if (!make_operand_map(&tm_a, a, p.M, p.K, 128) || !make_operand_map(&tm_b, b, p.N, p.K, Cfg::kBRows) ||
-        !make_sf_map(&tm_sfa, a_sf, ((p.M + 127) / 128) * kt) || !make_sf_map(&tm_sfb, b_sf, ((p.N + 127) / 128) * kt))
+    const int64_t b_rows = p.tile_group != nullptr ? p.N * p.num_groups : p.N;
+    if (!make_operand_map(&tm_a, a, p.M, p.K, 128) || !make_operand_map(&tm_b, b, b_rows, p.K, Cfg::kBRows) ||
+        !make_sf_map(&tm_sfa, a_sf, ((p.M + 127) / 128) * kt) || !make_sf_map(&tm_sfb, b_sf, ((b_rows + 127) / 128) * kt))
         return DW_ERR_LAUNCH;
     // D goes out by TMA when its rows are 16-byte multiples (the tensor map's stride rule) and it is
     // written by the GEMM kernel itself (not by the split-K reduction)
@@ -705,7 +714,10 @@ static GemmPlan plan_gemm(int64_t M, int64_t N, int64_t K) {
 
 static long long* g_timing = nullptr;   // optional per-CTA wait counters (dw_mxfp8_gemm_set_timing_buffer)
 
-struct FusedOut { int act = DW_ACT_NONE; int rule = DW_RULE_OCP_FLOOR; void* codes = nullptr; void* scales = nullptr; };
+struct FusedOut {
+    int act = DW_ACT_NONE; int rule = DW_RULE_OCP_FLOOR; void* codes = nullptr; void* scales = nullptr;
+    const int* tile_group = nullptr; uint32_t num_groups = 0;
+};
 
 static int run_gemm(const void* a_codes, const void* a_sf, const void* b_codes, const void* b_sf, void* d_bf16,
                     const void* bias_bf16, int64_t M, int64_t N, int64_t K, float alpha, float beta, int variant,
@@ -720,6 +732,7 @@ static int run_gemm(const void* a_codes, const void* a_sf, const void* b_codes, 
     p.M = M; p.N = N; p.K = K; p.alpha = alpha; p.beta = beta;
     p.splits = splits; p.partial = partial;
     p.wait_cycles = g_timing;
+    p.tile_group = fo.tile_group; p.num_groups = fo.num_groups;
     switch (variant) {
         case 1: return launch_gemm<128, 1, 1>(a_codes, a_sf, b_codes, b_sf, p, st);
         case 2: return launch_gemm<256, 1, 1>(a_codes, a_sf, b_codes, b_sf, p, st);
@@ -806,6 +819,24 @@ extern "C" DW_API int dw_mxfp8_gemm_fused(const void* a_codes, const void* a_sf,
     // the scale padding of the quantised output is written per 128-column group: keep column tiles that are multiples of 128
     if (out_codes != nullptr && pl.variant > 4) pl.variant = 3;
     return run_gemm(a_codes, a_sf, b_codes, b_sf, d_bf16, bias_bf16, M, N, K, alpha, beta, pl.variant, 1, nullptr, status_word,
+                    static_cast<cudaStream_t>(stream), fo);
+}
+
+extern "C" DW_API int dw_mxfp8_gemm_grouped(const void* a_codes, const void* a_sf, const void* b_codes, const void* b_sf,
+                                            void* d_bf16, const int* tile_group, int64_t M_total, int64_t N, int64_t K,
+                                            int num_groups, int rows_per_tile, float alpha, void* status_word, void* stream) {
+    if (M_total < 0 || N <= 0 || K <= 0 || num_groups <= 0 || tile_group == nullptr) return DW_ERR_BAD_ARG;
+    if (rows_per_tile != 128 && rows_per_tile != 256) return DW_ERR_BAD_ARG;
+    if (M_total % rows_per_tile != 0 || N % 128 != 0) return DW_ERR_BAD_ARG;   // whole row tiles per group; whole scale tiles per weight
+    if (M_total == 0) return DW_OK;
+    const int rc = check_gemm_args(a_codes, a_sf, b_codes, b_sf, d_bf16, nullptr, M_total, N, K);
+    if (rc != DW_OK) return rc;
+    if (static_cast<int64_t>(num_groups) * N >= (1ll << 31)) return DW_ERR_TOO_LARGE;
+    FusedOut fo;
+    fo.tile_group = tile_group; fo.num_groups = static_cast<uint32_t>(num_groups);
+    // the row tile of the kernel must be the granularity of tile_group: 1 CTA x 128 rows or a CTA pair x 256 rows
+    const int variant = rows_per_tile == 128 ? 2 : 3;
+    return run_gemm(a_codes, a_sf, b_codes, b_sf, d_bf16, nullptr, M_total, N, K, alpha, 0.0f, variant, 1, nullptr, status_word,
                     static_cast<cudaStream_t>(stream), fo);
 }
 

@@ -76,6 +76,51 @@ def mxfp8_gemm_bf16(a: torch.Tensor, b_kn: torch.Tensor, c: Optional[torch.Tenso
     return nv.gemm(a_codes, a_sf, b_codes, b_sf, out=out, bias=bias, alpha=alpha, beta=beta)
 
 
+def mxfp8_grouped_gemm_bf16(a_list: Sequence[torch.Tensor], b_list: Sequence[torch.Tensor], alpha: float = 1.0,
+                            scale_rule: int = nv.RULE_OCP_FLOOR) -> List[torch.Tensor]:
+    """[alpha * A_g[m_g,K] @ B_g[K,N] for g] in ONE GEMM launch when every group has the same K and N
+    (the experts of an MoE layer): the activations are concatenated (each group padded with zero rows to a
+    whole row tile) and quantised once, the weights are quantised into one stacked operand, and
+    dw_mxfp8_gemm_grouped lets each row tile multiply its own group's weight.  Groups of different widths
+    fall back to one launch per group.  Returns views into one output buffer."""
+    G = len(a_list)
+    if G == 0:
+        return []
+    K, N = b_list[0].shape
+    uniform = all(b.shape == (K, N) and a.dim() == 2 and a.shape[1] == K for a, b in zip(a_list, b_list))
+    if not uniform or N % 128 or K % 32:
+        return [mxfp8_gemm_bf16(a, b, None, alpha, 0.0, scale_rule=scale_rule) for a, b in zip(a_list, b_list)]
+    dev = a_list[0].device
+    sizes = [int(a.shape[0]) for a in a_list]
+    rpt = 256 if sum(sizes) >= 512 * G else 128          # small groups: 128-row tiles waste less padding
+    pieces, tile_group, offsets, row = [], [], [], 0
+    for g, (a, m) in enumerate(zip(a_list, sizes)):
+        padded = -(-m // rpt) * rpt
+        offsets.append(row)
+        pieces.append(a.to(torch.bfloat16))
+        if padded != m:
+            pieces.append(torch.zeros(padded - m, K, dtype=torch.bfloat16, device=dev))
+        tile_group += [g] * (padded // rpt)
+        row += padded
+    if row == 0:
+        return [torch.empty(0, N, dtype=torch.bfloat16, device=dev) for _ in a_list]
+    a_codes, a_sf = nv.quantize(torch.cat(pieces, dim=0), nv.DIR_ROW, scale_rule, nv.SF_TILED)
+    b_codes = torch.empty(G * N, K, dtype=torch.uint8, device=dev)
+    per_group = nv.scale_bytes(N, K, nv.SF_TILED)        # N % 128 == 0: every group owns whole scale tiles
+    b_sf = torch.empty(G * per_group, dtype=torch.uint8, device=dev)
+    for g, b in enumerate(b_list):
+        bq = b.to(torch.bfloat16)
+        if bq.stride(0) == 1 and bq.stride(1) == K:      # transposed view of an [N, K] weight: already K-major
+            nv.quantize_into(bq.t(), b_codes[g * N:(g + 1) * N], b_sf[g * per_group:(g + 1) * per_group],
+                             nv.DIR_ROW, scale_rule, nv.SF_TILED)
+        else:
+            nv.quantize_into(bq.contiguous(), b_codes[g * N:(g + 1) * N], b_sf[g * per_group:(g + 1) * per_group],
+                             nv.DIR_COL_T, scale_rule, nv.SF_TILED)
+    groups = torch.tensor(tile_group, dtype=torch.int32).to(dev, non_blocking=True)
+    d = nv.gemm_grouped(a_codes, a_sf, b_codes, b_sf, groups, G, rows_per_tile=rpt, alpha=alpha)
+    return [d[o:o + m] for o, m in zip(offsets, sizes)]
+
+
 class BlackwellGemmKernel:
     """csrc/python_bindings.cpp:35-113 (PyBlackwellGemmKernel)."""
 
@@ -142,7 +187,8 @@ class BlackwellGemmKernel:
 
 
 class BlackwellGroupedGemmKernel:
-    """csrc/python_bindings.cpp:116-194: one GEMM per group, same kernel, launched back to back."""
+    """csrc/python_bindings.cpp:116-194.  MXFP8 groups of equal K and N run as one grouped launch
+    (mxfp8_grouped_gemm_bf16); the reference loops one cuBLAS call per group (csrc/cutlass_kernels.cpp:310-341)."""
 
     def __init__(self) -> None:
         nv.load()
@@ -161,16 +207,13 @@ class BlackwellGroupedGemmKernel:
                      beta: float = 0.0) -> List[torch.Tensor]:
         if len(a_list) != len(b_list):
             raise RuntimeError("a_list and b_list differ in length")
-        outs = []
         for a, b in zip(a_list, b_list):
             if not a.is_cuda or not b.is_cuda:
                 raise RuntimeError("All inputs must be on CUDA")
-            if self.dtype == "mxfp8":
-                o = mxfp8_gemm_bf16(a, b, None, alpha, 0.0)
-                outs.append(o if a.dtype == torch.bfloat16 else o.to(a.dtype))
-            else:
-                outs.append(alpha * torch.matmul(a, b))
-        return outs
+        if self.dtype == "mxfp8":
+            outs = mxfp8_grouped_gemm_bf16(a_list, b_list, alpha)
+            return [o if a.dtype == torch.bfloat16 else o.to(a.dtype) for o, a in zip(outs, a_list)]
+        return [alpha * torch.matmul(a, b) for a, b in zip(a_list, b_list)]
 
     def set_expert_parallel_strategy(self, enable: bool) -> None:
         self.expert_parallel = bool(enable)

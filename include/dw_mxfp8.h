@@ -131,6 +131,19 @@ int dw_mxfp8_gemm_fused(const void *a_codes, const void *a_sf, const void *b_cod
                         float beta, int activation, void *out_codes, void *out_scales, int scale_rule,
                         void *status_word, void *stream);
 
+/* Grouped GEMM, one launch for all experts of an MoE layer:  D[rows of group g] = alpha * A[rows of group g] . B_g^T.
+ * a_codes [M_total, K] is the row-wise concatenation of the groups' activations (quantised as one matrix,
+ * DW_SF_TILED scales), every group padded with zero rows to a multiple of rows_per_tile (128 or 256);
+ * tile_group[M_total / rows_per_tile] (device int32) names the group of each row tile; b_codes
+ * [num_groups * N, K] stacks the groups' weights ([N, K] each, quantised as one matrix), N % 128 == 0.
+ * d_bf16 [M_total, N].  rows_per_tile = 256 runs the CTA-pair kernel, 128 the single-CTA one (less padding
+ * for small groups).  Out-of-range group ids are clamped.
+ * Replaces BlackwellGroupedGemmKernel::grouped_gemm (csrc/cutlass_kernels.cpp:310-341: a loop of fp16
+ * cublasHgemm calls, one per group), bound at csrc/python_bindings.cpp:116-194. */
+int dw_mxfp8_gemm_grouped(const void *a_codes, const void *a_sf, const void *b_codes, const void *b_sf,
+                          void *d_bf16, const int *tile_group, int64_t M_total, int64_t N, int64_t K,
+                          int num_groups, int rows_per_tile, float alpha, void *status_word, void *stream);
+
 /* Replaces BlackwellGemmKernel::get_workspace_size, csrc/cutlass_kernels.cpp:229-231. */
 size_t dw_mxfp8_gemm_workspace(int64_t M, int64_t N, int64_t K);
 

@@ -266,3 +266,38 @@ def test_fused_mlp_chain_never_stores_the_activation(nv):
     ref = torch.nn.functional.gelu(x.float() @ w1.float().t() + b1.float()) @ w2.float().t()
     # sanity against unquantised fp32: E4M3 keeps 3 mantissa bits, so two quantised layers sit near 5 % (Frobenius)
     assert ((y_fused.float() - ref).norm() / ref.norm()).item() < 0.08
+
+
+@pytest.mark.parametrize("sizes", [[300, 0, 128, 1, 700], [2048, 1024, 4096, 512], [64, 64, 64, 64, 64, 64, 64, 64]])
+def test_grouped_gemm_one_launch_equals_one_gemm_per_group(nv, sizes):
+    """dw_mxfp8_gemm_grouped (the experts of an MoE layer in one launch) against the ordinary GEMM run once per
+    group: same kernel and accumulation order, so the bf16 outputs are identical; one group also goes to the oracle.
+    Sizes cover an empty group, a one-row group, ragged groups and both row-tile granularities (128, 256)."""
+    from deepwell_b200 import cutlass_kernels as ck
+    K, N = 512, 384
+    g = torch.Generator("cpu").manual_seed(sum(sizes))
+    a_list = [torch.randn(m, K, generator=g).bfloat16().cuda() for m in sizes]
+    w_list = [(torch.randn(N, K, generator=g) * 0.05).bfloat16().cuda() for _ in sizes]       # [N, K] weights
+    nv.set_gemm_variant(0)
+    got = ck.mxfp8_grouped_gemm_bf16(a_list, [w.t() for w in w_list], alpha=0.5)
+    nv.check_status()
+    assert [tuple(o.shape) for o in got] == [(m, N) for m in sizes]
+    for variant in (2, 3):            # the grouped launch uses the 1-CTA kernel for 128-row tiles, the CTA pair for 256
+        nv.set_gemm_variant(variant)
+        for a, w, o_ in zip(a_list, w_list, got):
+            if a.shape[0] == 0:
+                continue
+            ref = ck.mxfp8_gemm_bf16(a, w.t(), None, 0.5, 0.0)
+            assert torch.equal(ref.view(torch.int16), o_.view(torch.int16))
+    nv.set_gemm_variant(0)
+    big = max(range(len(sizes)), key=lambda i: sizes[i])
+    assert_close(got[big].cpu(), oracle_gemm(nv, a_list[big], w_list[big], alpha=0.5))
+
+
+def test_grouped_gemm_rejects_bad_arguments(nv, native_lib):
+    p16 = 16
+    L = native_lib
+    assert L.dw_mxfp8_gemm_grouped(p16, p16, p16, p16, p16, p16, 300, 128, 128, 2, 256, 1.0, None, None) == -1   # M not whole tiles
+    assert L.dw_mxfp8_gemm_grouped(p16, p16, p16, p16, p16, p16, 512, 96, 128, 2, 256, 1.0, None, None) == -1    # N % 128
+    assert L.dw_mxfp8_gemm_grouped(p16, p16, p16, p16, p16, p16, 512, 128, 128, 2, 192, 1.0, None, None) == -1   # tile height
+    assert L.dw_mxfp8_gemm_grouped(p16, p16, p16, p16, p16, None, 512, 128, 128, 2, 256, 1.0, None, None) == -1  # no tile_group
