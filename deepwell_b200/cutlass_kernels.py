@@ -77,12 +77,13 @@ def mxfp8_gemm_bf16(a: torch.Tensor, b_kn: torch.Tensor, c: Optional[torch.Tenso
 
 
 def mxfp8_grouped_gemm_bf16(a_list: Sequence[torch.Tensor], b_list: Sequence[torch.Tensor], alpha: float = 1.0,
-                            scale_rule: int = nv.RULE_OCP_FLOOR) -> List[torch.Tensor]:
+                            scale_rule: int = nv.RULE_OCP_FLOOR, weight_cache: Optional[dict] = None) -> List[torch.Tensor]:
     """[alpha * A_g[m_g,K] @ B_g[K,N] for g] in ONE GEMM launch when every group has the same K and N
     (the experts of an MoE layer): the activations are concatenated (each group padded with zero rows to a
     whole row tile) and quantised once, the weights are quantised into one stacked operand, and
     dw_mxfp8_gemm_grouped lets each row tile multiply its own group's weight.  Groups of different widths
-    fall back to one launch per group.  Returns views into one output buffer."""
+    fall back to one launch per group.  Returns views into one output buffer.  `weight_cache` (a dict the caller
+    keeps) lets repeated calls with unchanged weight tensors reuse the stacked quantised operand."""
     G = len(a_list)
     if G == 0:
         return []
@@ -105,17 +106,33 @@ def mxfp8_grouped_gemm_bf16(a_list: Sequence[torch.Tensor], b_list: Sequence[tor
     if row == 0:
         return [torch.empty(0, N, dtype=torch.bfloat16, device=dev) for _ in a_list]
     a_codes, a_sf = nv.quantize(torch.cat(pieces, dim=0), nv.DIR_ROW, scale_rule, nv.SF_TILED)
-    b_codes = torch.empty(G * N, K, dtype=torch.uint8, device=dev)
-    per_group = nv.scale_bytes(N, K, nv.SF_TILED)        # N % 128 == 0: every group owns whole scale tiles
-    b_sf = torch.empty(G * per_group, dtype=torch.uint8, device=dev)
-    for g, b in enumerate(b_list):
-        bq = b.to(torch.bfloat16)
-        if bq.stride(0) == 1 and bq.stride(1) == K:      # transposed view of an [N, K] weight: already K-major
-            nv.quantize_into(bq.t(), b_codes[g * N:(g + 1) * N], b_sf[g * per_group:(g + 1) * per_group],
-                             nv.DIR_ROW, scale_rule, nv.SF_TILED)
+    # weights: one stacked K-major operand [G * N, K] from one quantiser launch (N % 128 == 0, so every group owns
+    # whole scale tiles and the stacked scale buffer is the concatenation of the groups' buffers)
+    key = tuple((b.data_ptr(), b._version, tuple(b.stride())) for b in b_list) + (scale_rule,)
+    cached = None if weight_cache is None else weight_cache.get("key")
+    if cached is not None and cached == key:
+        b_codes, b_sf = weight_cache["operand"]
+    else:
+        k_major = [b.stride(0) == 1 and b.stride(1) == K for b in b_list]     # transposed views of [N, K] weights
+        if N * K > (20 << 20):
+            # large experts: one quantiser launch per expert straight into its slice (stacking them first would
+            # copy more bytes than the extra launches cost)
+            b_codes = torch.empty(G * N, K, dtype=torch.uint8, device=dev)
+            per_group = nv.scale_bytes(N, K, nv.SF_TILED)
+            b_sf = torch.empty(G * per_group, dtype=torch.uint8, device=dev)
+            for g, b in enumerate(b_list):
+                bq = b.to(torch.bfloat16)
+                nv.quantize_into(bq.t() if k_major[g] else bq.contiguous(), b_codes[g * N:(g + 1) * N],
+                                 b_sf[g * per_group:(g + 1) * per_group], nv.DIR_ROW if k_major[g] else nv.DIR_COL_T,
+                                 scale_rule, nv.SF_TILED)
+        elif all(k_major):
+            stacked = torch.cat([b.t() for b in b_list], dim=0).to(torch.bfloat16)
+            b_codes, b_sf = nv.quantize(stacked, nv.DIR_ROW, scale_rule, nv.SF_TILED)
         else:
-            nv.quantize_into(bq.contiguous(), b_codes[g * N:(g + 1) * N], b_sf[g * per_group:(g + 1) * per_group],
-                             nv.DIR_COL_T, scale_rule, nv.SF_TILED)
+            stacked = torch.cat([b.to(torch.bfloat16) for b in b_list], dim=1)           # [K, G * N]
+            b_codes, b_sf = nv.quantize(stacked, nv.DIR_COL_T, scale_rule, nv.SF_TILED)
+        if weight_cache is not None:
+            weight_cache["key"], weight_cache["operand"] = key, (b_codes, b_sf)
     groups = torch.tensor(tile_group, dtype=torch.int32).to(dev, non_blocking=True)
     d = nv.gemm_grouped(a_codes, a_sf, b_codes, b_sf, groups, G, rows_per_tile=rpt, alpha=alpha)
     return [d[o:o + m] for o, m in zip(offsets, sizes)]
@@ -196,6 +213,7 @@ class BlackwellGroupedGemmKernel:
         self.dtype = "fp16"
         self.use_microscaling = False
         self.expert_parallel = True
+        self._weight_cache: dict = {}
 
     def initialize(self, problem_sizes: Sequence[Tuple[int, int, int]], dtype: str = "fp16",
                    use_microscaling: bool = False) -> None:
@@ -211,7 +229,7 @@ class BlackwellGroupedGemmKernel:
             if not a.is_cuda or not b.is_cuda:
                 raise RuntimeError("All inputs must be on CUDA")
         if self.dtype == "mxfp8":
-            outs = mxfp8_grouped_gemm_bf16(a_list, b_list, alpha)
+            outs = mxfp8_grouped_gemm_bf16(a_list, b_list, alpha, weight_cache=self._weight_cache)
             return [o if a.dtype == torch.bfloat16 else o.to(a.dtype) for o, a in zip(outs, a_list)]
         return [alpha * torch.matmul(a, b) for a, b in zip(a_list, b_list)]
 

@@ -301,3 +301,33 @@ def test_grouped_gemm_rejects_bad_arguments(nv, native_lib):
     assert L.dw_mxfp8_gemm_grouped(p16, p16, p16, p16, p16, p16, 512, 96, 128, 2, 256, 1.0, None, None) == -1    # N % 128
     assert L.dw_mxfp8_gemm_grouped(p16, p16, p16, p16, p16, p16, 512, 128, 128, 2, 192, 1.0, None, None) == -1   # tile height
     assert L.dw_mxfp8_gemm_grouped(p16, p16, p16, p16, p16, None, 512, 128, 128, 2, 256, 1.0, None, None) == -1  # no tile_group
+
+
+def test_grouped_gemm_weight_cache_and_quantize_into(nv):
+    """Repeated grouped calls with unchanged weights reuse the stacked operand; an in-place weight update is seen.
+    quantize_into writes one expert's slice of a stacked operand exactly as quantize would."""
+    from deepwell_b200 import cutlass_kernels as ck
+    K, N, G = 256, 256, 3
+    g = torch.Generator("cpu").manual_seed(99)
+    a_list = [torch.randn(m, K, generator=g).bfloat16().cuda() for m in (200, 56, 384)]
+    w_list = [(torch.randn(K, N, generator=g) * 0.05).bfloat16().cuda() for _ in range(G)]      # [K, N]: column-wise path
+    cache = {}
+    first = ck.mxfp8_grouped_gemm_bf16(a_list, w_list, weight_cache=cache)
+    operand = cache["operand"][0]
+    again = ck.mxfp8_grouped_gemm_bf16(a_list, w_list, weight_cache=cache)
+    assert cache["operand"][0] is operand
+    for x, y in zip(first, again):
+        assert torch.equal(x, y)
+    w_list[1].mul_(2.0)
+    third = ck.mxfp8_grouped_gemm_bf16(a_list, w_list, weight_cache=cache)
+    assert cache["operand"][0] is not operand
+    assert torch.equal(third[1].view(torch.int16), (first[1].float() * 2).bfloat16().view(torch.int16))    # exact: power of two
+    assert torch.equal(third[0], first[0]) and torch.equal(third[2], first[2])
+    # quantize_into == quantize
+    x = torch.randn(N, K, generator=g).bfloat16().cuda()
+    codes, scales = nv.quantize(x, nv.DIR_ROW, 0, nv.SF_TILED)
+    big_c = torch.zeros(3 * N, K, dtype=torch.uint8, device="cuda")
+    big_s = torch.zeros(3 * scales.numel(), dtype=torch.uint8, device="cuda")
+    nv.quantize_into(x, big_c[N:2 * N], big_s[scales.numel():2 * scales.numel()], nv.DIR_ROW, 0, nv.SF_TILED)
+    assert torch.equal(big_c[N:2 * N], codes.view(torch.uint8)) and torch.equal(big_s[scales.numel():2 * scales.numel()], scales)
+    assert int(big_c[:N].sum()) == 0 and int(big_c[2 * N:].sum()) == 0
