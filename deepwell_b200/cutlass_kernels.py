@@ -76,6 +76,9 @@ def mxfp8_gemm_bf16(a: torch.Tensor, b_kn: torch.Tensor, c: Optional[torch.Tenso
     return nv.gemm(a_codes, a_sf, b_codes, b_sf, out=out, bias=bias, alpha=alpha, beta=beta)
 
 
+_STACK_LIMIT = 20 << 20     # elements per expert weight above which the experts are quantised one launch each
+
+
 def mxfp8_grouped_gemm_bf16(a_list: Sequence[torch.Tensor], b_list: Sequence[torch.Tensor], alpha: float = 1.0,
                             scale_rule: int = nv.RULE_OCP_FLOOR, weight_cache: Optional[dict] = None) -> List[torch.Tensor]:
     """[alpha * A_g[m_g,K] @ B_g[K,N] for g] in ONE GEMM launch when every group has the same K and N
@@ -114,7 +117,7 @@ def mxfp8_grouped_gemm_bf16(a_list: Sequence[torch.Tensor], b_list: Sequence[tor
         b_codes, b_sf = weight_cache["operand"]
     else:
         k_major = [b.stride(0) == 1 and b.stride(1) == K for b in b_list]     # transposed views of [N, K] weights
-        if N * K > (20 << 20):
+        if N * K > _STACK_LIMIT:
             # large experts: one quantiser launch per expert straight into its slice (stacking them first would
             # copy more bytes than the extra launches cost)
             b_codes = torch.empty(G * N, K, dtype=torch.uint8, device=dev)

@@ -321,6 +321,14 @@ def test_grouped_gemm_weight_cache_and_quantize_into(nv):
     w_list[1].mul_(2.0)
     third = ck.mxfp8_grouped_gemm_bf16(a_list, w_list, weight_cache=cache)
     assert cache["operand"][0] is not operand
+    limit, ck._STACK_LIMIT = ck._STACK_LIMIT, 0           # the path for large experts: one quantiser launch per expert
+    try:
+        for mixed in (w_list, [w_list[0], w_list[1].t().contiguous().t(), w_list[2]]):     # [K, N] and K-major views
+            per_expert = ck.mxfp8_grouped_gemm_bf16(a_list, mixed)
+            for x, y in zip(third, per_expert):
+                assert torch.equal(x, y)
+    finally:
+        ck._STACK_LIMIT = limit
     assert torch.equal(third[1].view(torch.int16), (first[1].float() * 2).bfloat16().view(torch.int16))    # exact: power of two
     assert torch.equal(third[0], first[0]) and torch.equal(third[2], first[2])
     # quantize_into == quantize
