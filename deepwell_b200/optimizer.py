@@ -11,7 +11,7 @@ are left as they are (their inner nn.Linear projections are still visited).
 from __future__ import annotations
 
 import copy
-from typing import Dict, Optional
+from typing import Dict, Optional, Sequence
 
 import torch.nn as nn
 
@@ -19,7 +19,16 @@ from .linear import DWLinear
 
 
 class DeepwellOptimizer:
-    def __init__(self, precision: str = "bf16", target: str = "blackwell", verbose: bool = True, profile: bool = False):
+    def __init__(self, precision: str = "bf16", target: str = "blackwell", verbose: bool = True, profile: bool = False,
+                 policy=None, sensitive_layers: Optional[Sequence[str]] = None):
+        """``policy``: a precision policy in the reference's shape (an object with ``config.sensitive_layers``,
+        src/deepwell/precision/policy.py:102-109) or ``sensitive_layers``: substrings of qualified module names.
+        A Linear whose lower-cased name contains one of them stays in its own precision, as
+        PrecisionPolicy.assign_layer_precision decides (:138-151) — a policy the reference's optimize() never
+        consults.  Default: none, every eligible Linear is replaced."""
+        if sensitive_layers is None and policy is not None:
+            sensitive_layers = getattr(getattr(policy, "config", policy), "sensitive_layers", None)
+        self.sensitive_layers = [s.lower() for s in (sensitive_layers or [])]
         self.precision = precision
         self.target = target
         self.verbose = verbose
@@ -61,6 +70,11 @@ class DeepwellOptimizer:
     def _try_optimize_module(self, module: nn.Module, name: str) -> Optional[nn.Module]:
         if self.precision != "mxfp8" or type(module) is not nn.Linear:
             return None
+        if any(s in name.lower() for s in self.sensitive_layers):
+            self.skipped.append((name, "named sensitive by the precision policy"))
+            if self.verbose:
+                print(f"  [{name}] Linear kept in its own precision (sensitive layer)")
+            return None
         if module.in_features % 32 or module.out_features % 32:
             self.skipped.append((name, "in/out features not multiples of the 32-element MX block"))
             if self.verbose:
@@ -95,8 +109,10 @@ class DeepwellOptimizer:
 
 
 def optimize(model: nn.Module, precision: str = "bf16", target: str = "blackwell", verbose: bool = True,
-             profile: bool = False, inplace: bool = False) -> nn.Module:
+             profile: bool = False, inplace: bool = False, policy=None,
+             sensitive_layers: Optional[Sequence[str]] = None) -> nn.Module:
     """deepwell.optimize(model, precision="mxfp8"): every nn.Linear whose feature sizes are
-    multiples of 32 becomes a DWLinear sharing the same parameters."""
-    return DeepwellOptimizer(precision=precision, target=target, verbose=verbose, profile=profile).optimize(
-        model, inplace=inplace)
+    multiples of 32 becomes a DWLinear sharing the same parameters, except those a precision
+    policy names sensitive (``policy`` / ``sensitive_layers``, see DeepwellOptimizer)."""
+    return DeepwellOptimizer(precision=precision, target=target, verbose=verbose, profile=profile, policy=policy,
+                             sensitive_layers=sensitive_layers).optimize(model, inplace=inplace)

@@ -133,3 +133,28 @@ def test_legacy_linear_replacement_names(native_lib):
     assert isinstance(lin, dw.DWLinear) and lin.bias is None and isinstance(lin.kernel_manager, ProductionKernelManager)
     with pytest.raises(RuntimeError):
         ProductionKernelManager().gemm(torch.randn(4, 32), torch.randn(32, 32))
+
+
+def test_optimize_honours_a_precision_policy(native_lib):
+    """Layers a precision policy names sensitive stay unreplaced: by substring list, or by an object shaped like the
+    reference's PrecisionPolicy (policy.config.sensitive_layers, src/deepwell/precision/policy.py:102-109)."""
+    import types
+    import deepwell_b200 as dw
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.first_linear = nn.Linear(64, 64)
+            self.body = nn.Sequential(nn.Linear(64, 128), nn.Linear(128, 64))
+            self.logits = nn.Linear(64, 96)
+
+    opt = dw.DeepwellOptimizer(precision="mxfp8", verbose=False, sensitive_layers=["logits", "First_Linear"])
+    new = opt.optimize(Net())
+    assert type(new.first_linear) is nn.Linear and type(new.logits) is nn.Linear
+    assert isinstance(new.body[0], dw.DWLinear) and isinstance(new.body[1], dw.DWLinear)
+    assert opt.stats["linear_modules"] == 2 and {n for n, _ in opt.skipped} == {"first_linear", "logits"}
+    policy = types.SimpleNamespace(config=types.SimpleNamespace(sensitive_layers=["embedding", "logits"]))
+    new = dw.optimize(Net(), precision="mxfp8", verbose=False, policy=policy)
+    assert type(new.logits) is nn.Linear and isinstance(new.first_linear, dw.DWLinear)
+    everything = dw.optimize(Net(), precision="mxfp8", verbose=False)
+    assert sum(isinstance(m, dw.DWLinear) for m in everything.modules()) == 4
