@@ -167,6 +167,7 @@ mx_quant_tile_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes
     const int64_t kb_row = cols >> 5, kb_col = rows >> 5;           // k-blocks per operand row
     const int64_t kt_row = (kb_row + 3) >> 2, kt_col = (kb_col + 3) >> 2;
     const bool wide_rows = (reinterpret_cast<uintptr_t>(codes_row) & 31) == 0;   // 32-byte stores of the row payload
+    const bool wide_cols = (reinterpret_cast<uintptr_t>(codes_col_t) & 31) == 0; // and of the transposed payload (rows % 32 == 0)
 
     auto issue_tile = [&](uint32_t id, int buf) {
         const uint32_t itr = id / tiles_c, itc = id - itr * tiles_c;
@@ -278,16 +279,18 @@ mx_quant_tile_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes
         }
         const int64_t gcol = c0 + 2 * p, grow = r0 + rb * 32;
         if (grow < rows) {
-            if (gcol < cols) {
-                uint8_t* d = codes_col_t + gcol * rows + grow;
-                stg_v4(d, make_uint4(qa[0], qa[1], qa[2], qa[3]));
-                stg_v4(d + 16, make_uint4(qa[4], qa[5], qa[6], qa[7]));
-            }
-            if (gcol + 1 < cols) {
-                uint8_t* d = codes_col_t + (gcol + 1) * rows + grow;
-                stg_v4(d, make_uint4(qb[0], qb[1], qb[2], qb[3]));
-                stg_v4(d + 16, make_uint4(qb[4], qb[5], qb[6], qb[7]));
-            }
+            // 32 codes of one column = one whole 32-byte sector: a single 256-bit store when the payload allows
+            auto store32 = [&](uint8_t* d, const uint32_t (&q)[8]) {
+                if (wide_cols) {
+                    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(d), "r"(q[0]), "r"(q[1]), "r"(q[2]),
+                                 "r"(q[3]), "r"(q[4]), "r"(q[5]), "r"(q[6]), "r"(q[7]) : "memory");
+                } else {
+                    stg_v4(d, make_uint4(q[0], q[1], q[2], q[3]));
+                    stg_v4(d + 16, make_uint4(q[4], q[5], q[6], q[7]));
+                }
+            };
+            if (gcol < cols) store32(codes_col_t + gcol * rows + grow, qa);
+            if (gcol + 1 < cols) store32(codes_col_t + (gcol + 1) * rows + grow, qb);
         }
         const uint32_t ca = 2 * p, cb = 2 * p + 1;
         sf_col[(ca & 31u) * 16 + (ca >> 5) * 4 + rb] = static_cast<uint8_t>(sb_a);
