@@ -453,8 +453,15 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 #pragma unroll
                             for (int i = 0; i < 8; ++i) q[i] = quant_word(o[2 * i], inv) | (quant_word(o[2 * i + 1], inv) << 16);
                             uint8_t* qd = p.q_codes + row * p.N + col;
-                            stg_v4(qd, make_uint4(q[0], q[1], q[2], q[3]));
-                            stg_v4(qd + 16, make_uint4(q[4], q[5], q[6], q[7]));
+                            // 32 codes = one whole 32-byte sector (N % 32 == 0 and a 16-byte aligned base give 16-byte
+                            // alignment; a single 256-bit store needs 32)
+                            if ((reinterpret_cast<uintptr_t>(qd) & 31) == 0) {
+                                asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(qd), "r"(q[0]), "r"(q[1]),
+                                             "r"(q[2]), "r"(q[3]), "r"(q[4]), "r"(q[5]), "r"(q[6]), "r"(q[7]) : "memory");
+                            } else {
+                                stg_v4(qd, make_uint4(q[0], q[1], q[2], q[3]));
+                                stg_v4(qd + 16, make_uint4(q[4], q[5], q[6], q[7]));
+                            }
                             p.q_scales[sf_tiled_offset(row, col >> 5, p.q_kt)] = static_cast<uint8_t>(sb);
                         } else if (row < ((p.M + 127) & ~int64_t(127))) {
                             p.q_scales[sf_tiled_offset(row, col >> 5, p.q_kt)] = 127;     // padding rows of the last tile
