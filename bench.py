@@ -6,17 +6,25 @@
 Workload: the four Llama-3-8B linear shapes at M = 16384 tokens (QKV 4096->6144, O 4096->4096,
 fused gate+up 4096->28672, down 14336->4096), bf16 activations N(0,1), weights N(0,0.02),
 synthetic and seeded.  One step = for each of the four layers: quantise X row-wise, quantise the
-weight (shard) row-wise, run the block-scaled GEMM.  With N GPUs every weight is sharded along
-its output dimension across the ranks (X is replicated; no collective on the data path), so the
-total work is fixed: strong scaling.
+weight (shard) row-wise, run the block-scaled GEMM.  The layers are independent problems, so the
+quantisation of layer i+1 runs on a second stream under the GEMM of layer i (--serial: one stream).
+With N GPUs every weight is sharded along its output dimension across the ranks (X is replicated;
+no collective on the data path), so the total work is fixed: strong scaling.
 
 Prints ONE JSON line (rank 0).  `value` is whole-job TFLOP/s with inputs resident in HBM;
-`e2e` is the same through the public API with host buffers (pinned), H2D and D2H inside the
-timed region; `roofline` is measured live with CUDA events around every GEMM launch;
-`cpu_baseline` times the CPU restatement of the same path on the host cores (rank 0, N = 1).
+`e2e` is the same through the public API with pinned host buffers, the host->device copy of
+every X and the device->host copy of every Y inside the timed region, on their own streams;
+`roofline` is measured live with CUDA events around every GEMM launch (`achieved_alone`: the same
+launches with nothing else on the GPU); `roofline_quantize` times the row quantiser on the largest
+activation; `cpu_baseline` times the CPU restatement of the same path on the host cores (rank 0, N = 1).
 
 --impl reference times only that CPU path (the reference ships no GPU implementation of an
 MXFP8 GEMM and its CPU path is a Python module calling torch.matmul).
+
+Other modes (each prints its own JSON): --workload decoder_step (end-to-end optimize() training step of
+a 12-layer decoder beside the same model with bf16 nn.Linear), --sweep-quantize (quantise-only bandwidth
+sweep), --profile-case (a few launches of one kernel on a small case, for an ncu capture),
+--emulate-world W (tuning aid: rank 0's shard sizes of a W-GPU job on one GPU).
 """
 from __future__ import annotations
 

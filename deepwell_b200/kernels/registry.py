@@ -47,10 +47,11 @@ class KernelSpec:
 # (name, backend, op, min sm, precisions, microscaling, fused, max batch, tiles)
 _DEFAULT_TABLE = (
     ("cutlass_sm100_mxfp8_gemm", KernelBackend.CUTLASS, "gemm", 100, ["mxfp8", "e4m3", "e5m2"], True, True, None,
-     [(128, 256, 128), (256, 256, 128), (128, 128, 128)]),
+     [(256, 256, 128), (256, 192, 128), (128, 256, 128), (256, 128, 128), (128, 128, 128)]),
     ("cutlass_sm100_nvfp4_gemm", KernelBackend.CUTLASS, "gemm", 100, ["nvfp4", "mxfp4"], True, True, None,
      [(256, 128, 128), (128, 256, 128)]),
-    ("cutlass_sm100_grouped_gemm_mxfp8", KernelBackend.CUTLASS, "grouped_gemm", 100, ["mxfp8"], True, True, 128, None),
+    ("cutlass_sm100_grouped_gemm_mxfp8", KernelBackend.CUTLASS, "grouped_gemm", 100, ["mxfp8"], True, True, 128,
+     [(256, 256, 128), (128, 256, 128)]),
     ("cutlass_sm90_fp8_gemm", KernelBackend.CUTLASS, "gemm", 90, ["fp8", "e4m3", "e5m2"], False, True, None, None),
     ("te_mxfp8_linear", KernelBackend.TE, "linear", 90, ["mxfp8", "fp8", "fp16", "bf16"], True, True, None, None),
     ("te_attention", KernelBackend.TE, "attention", 80, ["fp16", "bf16", "fp8"], False, True, None, None),
