@@ -695,17 +695,26 @@ static GemmPlan plan_gemm(int64_t M, int64_t N, int64_t K) {
     const int64_t nkb = (K + 127) / 128;
     pl.variant = g_variant != 0 ? g_variant : ((N <= 128) ? 1 : (M <= 128 ? 2 : 3));
     if (g_variant == 0 && pl.variant == 3) {
-        // 256 x 256 tiles (3) against 256 x 192 tiles (5).  Cost of a round of tiles in units of
-        // (columns x k-blocks): variant 3's two accumulators share 32 tensor-memory columns, so each
-        // tile waits for the previous tile's first epilogue step (about 5 k-blocks of MMA time, measured);
-        // variant 5 has no such wait but moves 17% more operand bytes per flop, which on long problems
-        // costs more than the wait (measured 4-13% slower at M = 16384, K = 4096).
+        // 256 x 256 tiles on CTA pairs (3), 256 x 192 tiles on CTA pairs (5) or 128 x 256 tiles on single CTAs (2).
+        // Cost of the slowest worker in units of (256 columns x one k-block) of one SM's tensor time:
+        // rounds of tiles x (k-blocks x efficiency + per-tile overhead).  Variant 3's two accumulators share 32
+        // tensor-memory columns, so each tile waits for the previous tile's first epilogue step, a handoff that
+        // crosses the CTA pair (about 5 k-blocks, measured); variant 2 has the same wait inside one CTA (2.5)
+        // but a shallower ring (12 % slower mainloop); variant 5 has whole accumulators (4: epilogue tail) but
+        // moves 17 % more operand bytes per flop.  Fitted to measurements on B200: variant 2 wins for K <= 1024
+        // (16384 x 32000 x 1024: 519 vs 584 us), variant 5 for short problems with few tiles (8192 x 768 x 3072:
+        // 21 vs 26 us), variant 3 from K = 4096 on (variant 5 is 4-13 % slower at M = 16384).
         // Problems small enough for split-K keep variant 3, which the split heuristic below was measured with.
-        const int64_t pairs = sm_count() / 2, tm = (M + 255) / 256;
+        const int64_t sms = sm_count(), pairs = sms / 2, tm = (M + 255) / 256;
         const bool would_split = tm * ((N + 255) / 256) * 4 <= pairs && nkb >= 32;
-        const int64_t rounds3 = (tm * ((N + 255) / 256) + pairs - 1) / pairs, rounds5 = (tm * ((N + 191) / 192) + pairs - 1) / pairs;
-        const double cost3 = static_cast<double>(rounds3) * 256.0 * (nkb + 5), cost5 = static_cast<double>(rounds5) * 192.0 * (nkb + 1) * 1.15;
-        if (cost5 < cost3 && !would_split) pl.variant = 5;
+        auto rounds = [](int64_t tiles, int64_t workers) { return static_cast<double>((tiles + workers - 1) / workers); };
+        const double cost3 = rounds(tm * ((N + 255) / 256), pairs) * (nkb + 5.0);
+        const double cost5 = rounds(tm * ((N + 191) / 192), pairs) * 0.75 * (nkb + 4.0) * 1.15;
+        const double cost2 = rounds(((M + 127) / 128) * ((N + 255) / 256), sms) * (nkb * 1.12 + 2.5);
+        if (!would_split) {
+            if (cost5 < cost3 && cost5 <= cost2) pl.variant = 5;
+            else if (cost2 < cost3) pl.variant = 2;
+        }
     }
     const int ctas = (pl.variant >= 3) ? 2 : 1, bn = (pl.variant == 1 || pl.variant == 4) ? 128 : (pl.variant == 5 ? 192 : 256);
     const int64_t tiles = ((M + 128 * ctas - 1) / (128 * ctas)) * ((N + bn - 1) / bn);
