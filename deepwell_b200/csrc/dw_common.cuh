@@ -71,6 +71,17 @@ __device__ __forceinline__ void scale_pair(uint32_t w, uint32_t inv2, float& lo,
         : "=f"(lo), "=f"(hi) : "r"(w), "r"(inv2), "f"(-0.0f));
 }
 
+// lo += low bf16 lane of w, hi += high bf16 lane of w, in fp32 with one rounding each (the mixed-precision FMA
+// with a multiplier of 1.0 reads the bf16 lanes directly: no unpacking instructions).
+__device__ __forceinline__ void add_bf16x2(uint32_t w, float& lo, float& hi) {
+    asm("{\n\t.reg .b16 a0, a1, one;\n\t"
+        "mov.b32 {a0, a1}, %2;\n\t"
+        "mov.b16 one, 0x3F80;\n\t"
+        "fma.rn.f32.bf16 %0, a0, one, %0;\n\t"
+        "fma.rn.f32.bf16 %1, a1, one, %1;\n\t}"
+        : "+f"(lo), "+f"(hi) : "r"(w));
+}
+
 // One bf16x2 word times a power of two (`inv2` from e8m0_inverse_bf16x2) -> two E4M3 codes in
 // bits [0,16), element 0 in the low byte.
 __device__ __forceinline__ uint32_t quant_word(uint32_t w, uint32_t inv2) {
