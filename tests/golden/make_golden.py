@@ -1,7 +1,7 @@
 """Generates the golden fixtures of tests/golden/ (run in the build container, where the
 reference checkout is readable):
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 kat_quant.npz      known-answer matrix for the quantiser (ties, saturation, zero / subnormal /
                    NaN / Inf blocks, amax mantissas on both sides of 1.75, every exponent).
@@ -71,7 +71,9 @@ def kat_matrix():
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2 or not os.path.isdir(os.path.join(sys.argv[1], "src", "deepwell")):
+        raise SystemExit("usage: make_golden.py <root of the reference checkout>")
+    ref_root = sys.argv[1]
     # ---- KAT ----
     bits = kat_matrix()
     out = {"bits": bits}
