@@ -17,12 +17,19 @@ constexpr int kBlock = 32;  // elements per scaling block
 // ------------------------------------------------------------------------------------------
 
 // E8M0 byte from the bf16 pattern of a block's amax (sign cleared, NaN elements excluded).
-//   rule 0: e = floor(log2 amax) - 8     rule 1: e = ceil(log2(amax/448))
+//   rule 0: e = floor(log2 amax) - 8
+//   rule 1: e = ceil(log2(amax/448)) as the reference's kernel evaluates it when built with its own flags
+//           (--use_fast_math) for sm_100a, measured on every bf16 magnitude: a quotient amax/448 below 2^-126
+//           flushes to zero, which the kernel turns into scale 1.0 (amax pattern < 0x04E0 -> byte 127), and
+//           amax = 1.75 * 2^k <= 224, whose quotient is exactly a power of two below 1, lands one step higher.
 // byte = e + 127 clamped to [0, 254]; amax == 0 -> 127 (scale 1.0).
 __device__ __forceinline__ uint32_t e8m0_from_amax(uint32_t amax, int rule) {
-    const uint32_t ef = amax >> 7;
+    const uint32_t ef = amax >> 7, m7 = amax & 0x7Fu;
     int b = static_cast<int>(ef) - 8;
-    if (rule == DW_RULE_REF_CEIL && (amax & 0x7Fu) > 0x60u && ef > 0u && ef < 255u) b += 1;
+    if (rule == DW_RULE_REF_CEIL) {
+        if (amax < 0x04E0u) return 127u;
+        if ((m7 > 0x60u || (m7 == 0x60u && ef <= 134u)) && ef < 255u) b += 1;
+    }
     b = max(b, 0);
     return amax == 0u ? 127u : static_cast<uint32_t>(b);
 }

@@ -42,7 +42,10 @@ extern "C" {
 #define DW_DIR_COL    2  /* blocks along rows; codes in the input's layout [rows, cols]; scales as COL_T */
 
 #define DW_RULE_OCP_FLOOR 0  /* scale = 2^(floor(log2 amax) - 8)                                     */
-#define DW_RULE_REF_CEIL  1  /* scale = 2^ceil(log2(amax/448)), csrc/mxfp8_quantization.cu:109-114   */
+#define DW_RULE_REF_CEIL  1  /* scale = 2^ceil(log2(amax/448)), csrc/mxfp8_quantization.cu:109-114, bit for bit
+                                as the reference's kernel gives it when built with its own flags (--use_fast_math)
+                                for sm_100a: amax below 448 * 2^-126 -> scale 1; amax = 1.75 * 2^k <= 224 -> one
+                                step higher than the formula                                              */
 
 #define DW_SF_FLAT   0  /* scales[r * ceil(K/32) + kb], one byte each                                 */
 #define DW_SF_TILED  1  /* 512-byte tiles of 128 rows x 4 k-blocks, the tcgen05 scale-factor layout:

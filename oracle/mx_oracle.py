@@ -25,14 +25,22 @@ target of this build (E4M3 payloads, E8M0 scales, scale = 2^(floor(log2 amax) - 
   * scale is stored as one E8M0 byte (biased exponent), not an fp32 value.
 
 Two scale rules are provided.  "ocp_floor" is the contract rule; "ref_ceil" is the
-reference's `2^ceil(log2(amax/448))` (mxfp8_quantization.cu:109-114) evaluated
-exactly on the bf16 bit pattern: it equals ocp_floor except when the 7-bit bf16
-mantissa of amax exceeds 0x60 (m > 1.75), where it is one exponent higher.
+reference's `2^ceil(log2(amax/448))` (mxfp8_quantization.cu:109-114) as the reference's
+own kernel evaluates it (see e8m0_from_amax_bits): it equals ocp_floor except when the
+7-bit bf16 mantissa of amax exceeds 0x60 (m > 1.75), where it is one exponent higher,
+plus the two fast-math effects of the reference's build.
 
-Parity pin: the reference's own tests hold no golden vector for this path.  The
-oracle is pinned against (1) torch's independent float8_e4m3fn / float8_e8m0fnu
-CPU casts, (2) the reference's CPU GEMM module run in the build container
-(tests/golden/make_golden.py records both), (3) hand-derived known-answer vectors.
+Parity pin: the reference's own tests hold no golden vector for this path, so the
+reference itself was run.  (1) Its quantiser kernel, compiled from its source with its
+own flags (oracle/Makefile -> oracle/_ref/), runs on the GPU in
+tests/test_gpu_reference_quantizer.py; its output on every finite bf16 magnitude and on a
+seeded matrix is recorded in tests/golden/ref_quantizer.npz
+(tests/golden/make_reference_quantizer_golden.py) and tests/test_oracle.py holds this
+module to it: ref_ceil scales bit for bit, scaled values against the reference's int8
+payload.  (2) The reference's CPU GEMM module, run in the build container, is recorded in
+tests/golden/ref_gemm.npz (tests/golden/make_golden.py).  (3) What the reference does not
+have - a true E4M3 encoder, E8M0 bytes, the ocp_floor rule - is held against torch's
+independent float8_e4m3fn / float8_e8m0fnu CPU casts and hand-derived vectors.
 """
 from __future__ import annotations
 
@@ -130,9 +138,15 @@ def e8m0_from_amax_bits(amax_bits: np.ndarray, rule: str = "ocp_floor") -> np.nd
 
     byte = e + 127 with the scale 2^e, clamped to [0, 254].
       ocp_floor: e = floor(log2 amax) - 8
-      ref_ceil : e = ceil(log2(amax / 448))        (mxfp8_quantization.cu:109-114)
+      ref_ceil : e = ceil(log2(amax / 448))        (mxfp8_quantization.cu:109-114), with the two places where
+                 the reference's kernel, built with its own flags (--use_fast_math, setup.py:290) for sm_100a,
+                 leaves that formula (measured by running that kernel on every bf16 magnitude,
+                 tests/test_gpu_reference_quantizer.py): a quotient amax/448 below 2^-126 is flushed to zero and
+                 the kernel then writes scale 1.0 (:111-116), i.e. amax pattern < 0x04E0 -> byte 127; and
+                 amax = 1.75 * 2^k <= 224, whose quotient is exactly a power of two below 1, comes out one step
+                 higher (the approximate division and logarithm land just above the integer).
     amax == 0 -> scale 1.0 -> byte 127             (mxfp8_quantization.cu:119-122)
-    A bf16 subnormal amax has floor(log2) <= -127, so e + 127 < 0 -> byte 0 for both.
+    A bf16 subnormal amax has floor(log2) <= -127, so e + 127 < 0 -> byte 0 under ocp_floor.
     """
     if rule not in RULE_ID:
         raise ValueError(f"unknown scale rule {rule!r}")
@@ -141,8 +155,11 @@ def e8m0_from_amax_bits(amax_bits: np.ndarray, rule: str = "ocp_floor") -> np.nd
     m7 = a & 0x7F
     byte = ef - 8
     if rule == "ref_ceil":
-        byte = byte + ((m7 > 0x60) & (ef > 0) & (ef < 255)).astype(np.int32)
+        up = (m7 > 0x60) | ((m7 == 0x60) & (ef <= 134))
+        byte = byte + (up & (ef < 255)).astype(np.int32)
     byte = np.clip(byte, 0, 254)
+    if rule == "ref_ceil":
+        byte = np.where(a < 0x04E0, 127, byte)
     byte = np.where(a == 0, 127, byte)
     return byte.astype(np.uint8)
 

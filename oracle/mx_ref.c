@@ -17,10 +17,12 @@
  * (round-to-nearest-even, saturating) instead of the int8 truncation at :159, and
  * the scale is an E8M0 byte instead of an fp32 value.  Scale rule 0 ("ocp_floor")
  * is 2^(floor(log2 amax) - 8); rule 1 ("ref_ceil") is the reference's
- * 2^ceil(log2(amax/448)) evaluated exactly on the bf16 pattern.
+ * 2^ceil(log2(amax/448)) as the reference's own fast-math kernel evaluates it.
  *
- * Parity pin: unpinned by the reference's tests (they hold no vector for this
- * path); pinned against torch's float8 casts and the numpy oracle by the test-suite.
+ * Parity pin: the reference's tests hold no vector for this path; the reference's
+ * quantiser kernel itself was run (tests/golden/ref_quantizer.npz records its output,
+ * tests/test_oracle.py holds this file and the numpy oracle to it); the E4M3 / E8M0
+ * encodings, which the reference does not have, are held against torch's float8 casts.
  */
 #include <math.h>
 #include <stdint.h>
@@ -78,7 +80,10 @@ static inline uint8_t e8m0_from_amax(uint16_t a, int rule) {
     if (a == 0) return 127;
     int ef = a >> 7, m7 = a & 0x7F;
     int b = ef - 8;
-    if (rule == 1 && m7 > 0x60 && ef > 0 && ef < 255) b += 1;
+    if (rule == 1) {   /* ref_ceil as the reference's fast-math kernel evaluates it on sm_100a (see mx_oracle.py) */
+        if (a < 0x04E0) return 127;
+        if ((m7 > 0x60 || (m7 == 0x60 && ef <= 134)) && ef < 255) b += 1;
+    }
     if (b < 0) b = 0;
     if (b > 254) b = 254;
     return (uint8_t)b;

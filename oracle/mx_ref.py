@@ -19,6 +19,37 @@ def build(force: bool = False) -> str:
     return _LIB
 
 
+_REF_LIB = os.path.join(_HERE, "_ref", "libref_mxfp8_quant.so")
+_ref_lib = None
+
+
+def build_reference(reference_root: str, force: bool = False) -> str:
+    """Compiles the reference's own quantiser (csrc/mxfp8_quantization.cu, where it lies under `reference_root`)
+    plus oracle/ref_quant_shim.cu into oracle/_ref/libref_mxfp8_quant.so.  Needs nvcc, not a GPU."""
+    src = os.path.join(reference_root, "csrc", "mxfp8_quantization.cu")
+    if not os.path.exists(src):
+        raise FileNotFoundError(src)
+    if force and os.path.exists(_REF_LIB):
+        os.remove(_REF_LIB)
+    subprocess.check_call(["make", "-s", "-C", _HERE, "reference", f"REFERENCE={os.path.abspath(reference_root)}"])
+    return _REF_LIB
+
+
+def reference_quantizer():
+    """ctypes handle of the reference's quantiser built by build_reference(), or None if it was not built.
+    Entry points (device pointers): ref_quantize_to_mxfp8_bf16(out_i8, scales_f32, in_bf16, M, N, row_major, stream),
+    ref_dequantize_from_mxfp8_bf16(out_bf16, in_i8, scales_f32, M, N, row_major, stream); both return the CUDA
+    error code of the launch."""
+    global _ref_lib
+    if _ref_lib is None and os.path.exists(_REF_LIB):
+        L = ctypes.CDLL(_REF_LIB)
+        p, i32 = ctypes.c_void_p, ctypes.c_int
+        L.ref_quantize_to_mxfp8_bf16.argtypes = [p, p, p, i32, i32, i32, p]
+        L.ref_dequantize_from_mxfp8_bf16.argtypes = [p, p, p, i32, i32, i32, p]
+        _ref_lib = L
+    return _ref_lib
+
+
 def lib():
     global _lib
     if _lib is None:

@@ -35,7 +35,17 @@ def independent_quantize_rowwise(bits, rule):
     amax = a.amax(dim=2)
     with np.errstate(divide="ignore"):
         l2 = torch.log2(amax)
-    e = torch.floor(l2) - 8 if rule == "ocp_floor" else torch.ceil(torch.log2(amax / 448.0))
+    if rule == "ocp_floor":
+        e = torch.floor(l2) - 8
+    else:
+        # the formula, plus the two places where the reference's fast-math kernel leaves it on sm_100a
+        # (oracle/mx_oracle.py::e8m0_from_amax_bits): quotient below 2^-126 -> scale 1; quotient an exact power
+        # of two below 1 -> one step higher
+        quot = amax / 448.0
+        lq = torch.log2(quot)
+        e = torch.ceil(lq)
+        e = torch.where((lq == torch.round(lq)) & (quot < 1.0), e + 1, e)
+        e = torch.where(quot < 2.0 ** -126, torch.zeros_like(e), e)
     e = torch.where(torch.isinf(amax), torch.full_like(e, 120.0), e)
     byte = torch.clamp(e + 127, 0, 254)
     byte = torch.where(amax == 0, torch.full_like(byte, 127.0), byte).to(torch.uint8)

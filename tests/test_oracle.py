@@ -48,13 +48,18 @@ def test_known_answers_by_hand():
 
 
 def test_rules_differ_only_above_mantissa_1p75():
+    """ref_ceil against ocp_floor: one step higher above mantissa 1.75 (the ceiling of the logarithm), and the two
+    places where the reference's fast-math kernel leaves its own formula: amax = 1.75 * 2^k <= 224 also one step
+    higher, amax below 448 * 2^-126 (pattern 0x04E0) scale 1."""
     amax = np.arange(1, 0x7F80, dtype=np.uint16)
     a = o.e8m0_from_amax_bits(amax, "ocp_floor").astype(int)
     b = o.e8m0_from_amax_bits(amax, "ref_ceil").astype(int)
-    high = ((amax & 0x7F) > 0x60) & ((amax >> 7) > 0)
-    clamp = a == 0
-    assert np.all((b - a)[high & ~clamp] == 1)
-    assert np.all((b - a)[~high] == 0)
+    ef, m7 = amax >> 7, amax & 0x7F
+    flushed = amax < 0x04E0
+    high = ((m7 > 0x60) | ((m7 == 0x60) & (ef <= 134))) & ~flushed
+    assert np.all(b[flushed] == 127)
+    assert np.all((b - a)[high] == 1)
+    assert np.all((b - a)[~high & ~flushed] == 0)
     assert o.e8m0_from_amax_bits(np.array([0], np.uint16)).tolist() == [127]
 
 
@@ -160,3 +165,28 @@ def test_flat_factorisation_follows_reference():
     assert o.flat_factorisation(256 * 1000) == (256, 1000)
     assert o.flat_factorisation(256 * 1000 + 128) == (1, 256 * 1000 + 128)   # no power of two >= 256 divides
     assert o.flat_factorisation(65537 * 3) == (1, 65537 * 3)
+
+
+def test_ref_ceil_rule_against_the_recorded_output_of_the_reference_kernel():
+    """tests/golden/ref_quantizer.npz holds what the reference's own quantiser kernel wrote on a B200
+    (tests/golden/make_reference_quantizer_golden.py): the oracle's ref_ceil scales must equal it on every finite
+    bf16 magnitude and on the recorded matrix, row-wise and column-wise, and the oracle's scaled values must truncate
+    to the recorded int8 payload wherever that fits in int8."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ref_quantizer.npz"))
+    pats = np.arange(0x7F80, dtype=np.uint16)
+    got = o.e8m0_from_amax_bits(pats, "ref_ceil").astype(np.int32) - 127
+    assert np.array_equal(got, g["scale_log2_every_magnitude"].astype(np.int32))
+    bits = g["x_bits"]
+    codes, scales = o.quantize_rowwise(bits, "ref_ceil")
+    assert np.array_equal(scales.astype(np.int32) - 127, g["scale_log2"].astype(np.int32))
+    _, col_scales = o.quantize_colwise(bits, "ref_ceil")
+    assert np.array_equal(col_scales.astype(np.int32) - 127, g["col_scale_log2"].astype(np.int32))
+    x = o.bf16_bits_to_f32(bits).astype(np.float64).reshape(bits.shape[0], -1, 32)
+    scaled = x / np.exp2(g["scale_log2"].astype(np.float64))[:, :, None]
+    fits = np.abs(scaled) < 127
+    assert np.array_equal(np.trunc(scaled)[fits].astype(np.int8), g["payload"].reshape(scaled.shape)[fits])
+    # the C restatement follows the same rule
+    from oracle import mx_ref
+    ccodes, cscales = mx_ref.quantize_rowwise(bits, 1)
+    assert np.array_equal(cscales, scales) and np.array_equal(ccodes, codes)
