@@ -71,7 +71,7 @@ def total_flops(m=M_TOKENS):
 # clocks during the timed region
 # ----------------------------------------------------------------------------------------------
 class ClockSampler:
-    """Polls SM clock and throttle reasons of one GPU through NVML every 20 ms."""
+    """Polls SM clock and throttle reasons of one GPU through NVML every 5 ms."""
 
     REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
@@ -98,7 +98,7 @@ class ClockSampler:
                         self.reasons.add(name)
             except Exception:
                 pass
-            time.sleep(0.02)
+            time.sleep(0.005)
 
     def start(self):
         if self.ok:
