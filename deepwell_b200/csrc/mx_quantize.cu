@@ -169,33 +169,45 @@ mx_quant_tile_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes
     const bool wide_rows = (reinterpret_cast<uintptr_t>(codes_row) & 31) == 0;   // 32-byte stores of the row payload
     const bool wide_cols = (reinterpret_cast<uintptr_t>(codes_col_t) & 31) == 0; // and of the transposed payload (rows % 32 == 0)
 
-    auto issue_tile = [&](uint32_t id, int buf) {
+    // Copies rows [64 half, 64 half + 64) of tile `id` into buffer `buf` (16-byte cp.async, 4 per thread); the
+    // second half also closes the copy group.  The two halves of the next tile are issued before the row pass and
+    // before the column pass of the current one, which keeps the request stream to HBM even.
+    auto issue_half = [&](uint32_t id, int buf, int half) {
         const uint32_t itr = id / tiles_c, itc = id - itr * tiles_c;
         const int64_t ir0 = static_cast<int64_t>(itr) * 128, igc = static_cast<int64_t>(itc) * 128 + cc * 8;
         TilePtr dst = reinterpret_cast<TilePtr>(tile_smem + buf * (128 * 16 * 16));
+        if (ir0 + 128 <= rows && static_cast<int64_t>(itc) * 128 + 128 <= cols) {
+            // whole tile inside the matrix (the common case): no per-row guards; the rows of a thread are 16 rows
+            // apart, so they share the swizzled chunk position (row & 7 is the same) and differ by constant strides
+            // in both address spaces
+            const uint32_t row0 = (t >> 4) + 64 * half;
+            const uint16_t* src = x + (ir0 + row0) * cols + igc;
+            const uint32_t d0 = smem_u32(&dst[row0][tile_chunk(cc, row0)]);
+            const int64_t step = 16 * cols;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const uint32_t row = (t >> 4) + 16 * j;
-            const int64_t gr = ir0 + row;
-            const bool ok = gr < rows && igc < cols;
-            const uint16_t* src = ok ? x + gr * cols + igc : x;          // out of range: zero fill, nothing read
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
-                         ::"r"(smem_u32(&dst[row][tile_chunk(cc, row)])), "l"(src), "r"(ok ? 16 : 0) : "memory");
+            for (int j = 0; j < 4; ++j)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d0 + j * 4096), "l"(src + j * step) : "memory");
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t row = (t >> 4) + 64 * half + 16 * j;
+                const int64_t gr = ir0 + row;
+                const bool ok = gr < rows && igc < cols;
+                const uint16_t* src = ok ? x + gr * cols + igc : x;      // out of range: zero fill, nothing read
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+                             ::"r"(smem_u32(&dst[row][tile_chunk(cc, row)])), "l"(src), "r"(ok ? 16 : 0) : "memory");
+            }
         }
-        asm volatile("cp.async.commit_group;" ::: "memory");
+        if (half == 1) asm volatile("cp.async.commit_group;" ::: "memory");
     };
 
     int buf = 0;
-    if (blockIdx.x < num_tiles) issue_tile(blockIdx.x, 0);
+    if (blockIdx.x < num_tiles) { issue_half(blockIdx.x, 0, 0); issue_half(blockIdx.x, 0, 1); }
     for (uint32_t id = blockIdx.x; id < num_tiles; id += gridDim.x, buf ^= 1) {
     const uint32_t next = id + gridDim.x;
-    if (next < num_tiles) {
-        issue_tile(next, buf ^ 1);
-        asm volatile("cp.async.wait_group 1;" ::: "memory");
-    } else {
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");     // this tile (the only group in flight)
     __syncthreads();
+    if (next < num_tiles) issue_half(next, buf ^ 1, 0);
     TilePtr tile = reinterpret_cast<TilePtr>(tile_smem + buf * (128 * 16 * 16));
     const uint32_t tr = id / tiles_c, tc = id - tr * tiles_c;
     const int64_t r0 = static_cast<int64_t>(tr) * 128, c0 = static_cast<int64_t>(tc) * 128;
@@ -236,6 +248,7 @@ mx_quant_tile_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes
         if (kDoCol && num_tiles > 8u * gridDim.x) __syncthreads();
     }
 
+    if (next < num_tiles) issue_half(next, buf ^ 1, 1);
     if (kDoCol) {
         // thread = (column pair p, row block rb): 32 words down the rows, two columns at once
         const uint32_t p = t & 63u, rb = t >> 6;
