@@ -183,3 +183,47 @@ def test_optimize_decoder_training_step_tracks_bf16(dw):
         curves.append(cur)
     assert curves[1][-1] < curves[1][0] - 0.3, curves
     assert all(abs(a - b) <= 0.03 * abs(a) for a, b in zip(*curves)), curves
+
+
+def test_dwlinear_training_step_captured_in_a_cuda_graph(dw):
+    """Forward + backward of a DWLinear captured in a CUDA graph (all launches go to the capturing stream, outputs come
+    from torch's allocator, nothing synchronises) and replayed on new input values: same gradients as the eager run."""
+    torch.manual_seed(31)
+    m = dw.DWLinear.from_linear(nn.Linear(256, 384, bias=True).cuda().bfloat16())
+    x = torch.randn(512, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    gy = torch.randn(512, 384, device="cuda", dtype=torch.bfloat16)
+
+    def step():
+        x.grad = None
+        m.weight.grad = None
+        m.bias.grad = None
+        y = m(x)
+        y.backward(gy)
+        return y
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            step()
+    torch.cuda.current_stream().wait_stream(side)
+    x.grad = None
+    m.weight.grad = None
+    m.bias.grad = None
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        y_static = step()
+    # new values in the captured input buffers
+    with torch.no_grad():
+        x.copy_(torch.randn(512, 256, device="cuda").bfloat16())
+        gy.copy_(torch.randn(512, 384, device="cuda").bfloat16())
+    graph.replay()
+    torch.cuda.synchronize()
+    got = [y_static.clone(), x.grad.clone(), m.weight.grad.clone(), m.bias.grad.clone()]
+    y = step()
+    torch.cuda.synchronize()
+    want = [y, x.grad, m.weight.grad, m.bias.grad]
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
+    from deepwell_b200 import _native
+    _native.check_status()
