@@ -335,6 +335,33 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         const int ch_begin = static_cast<int>(half) * kHalfChunks;
         const int ch_count = min(kChunks, ch_begin + kHalfChunks) - ch_begin;
         const uint32_t slot = out_base + (warp - 2u) * Cfg::kOutSlotBytes;
+        // Kernel parameters the chunk loop branches on, read once into registers: fetched from the parameter bank
+        // inside the loop, the chain of dependent loads and branches took ~350 cycles per chunk (measured).
+        const int64_t M_ = p.M, N_ = p.N;
+        const uint16_t* const bias = p.bias;
+        // the common epilogue: D = bf16(accumulator + bias) through the TMA store and nothing else
+        const bool plain = p.splits <= 1 && vec_ok && p.tma_store != 0 && p.alpha == 1.0f && p.beta == 0.0f &&
+                           p.act == DW_ACT_NONE && p.q_codes == nullptr;
+        // This warp's 32 rows x 32 columns go to its staging slot (row r at 64 r, its four 16-byte pieces permuted
+        // by the 64-byte swizzle so that the stores of a quarter warp cover all banks), then one TMA store writes
+        // the box as whole 64-byte row segments and clips rows beyond M.  The slot is refilled only after the
+        // previous store has read it.
+        auto stage_and_store = [&](const uint32_t (&o)[16], bool in_rows, int64_t col, int64_t row0) {
+            if (lane == 0) ptx::bulk_wait_read<0>();
+            __syncwarp();
+            if (in_rows) {
+                const uint32_t row_addr = slot + lane * 64u, sw = (lane >> 1) & 3u;
+#pragma unroll
+                for (uint32_t v = 0; v < 4; ++v)
+                    ptx::sts_v4(row_addr + ((v ^ sw) << 4), o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
+            }
+            ptx::fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+                ptx::tma_store_2d(&tm_d, slot, static_cast<int>(col), static_cast<int>(row0));
+                ptx::bulk_commit();
+            }
+        };
         for (uint32_t unit = worker; unit < num_units && !err; unit += num_workers) {
             const uint32_t split = unit / p.num_tiles, tile = unit - split * p.num_tiles;
             uint32_t tm, tn;
@@ -353,9 +380,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             auto chunk_of = [&](int it) { return ch_begin + (shared_last ? (it == 0 ? ch_count - 1 : it - 1) : it); };
             auto load_bias = [&](int it, uint4 (&b)[4]) {
                 const int64_t bcol = col0 + chunk_of(it) * 32;
-                if (p.bias != nullptr && vec_ok && bcol + 32 <= p.N) {
+                if (bias != nullptr && vec_ok && bcol + 32 <= N_) {
 #pragma unroll
-                    for (int v = 0; v < 4; ++v) b[v] = *reinterpret_cast<const uint4*>(p.bias + bcol + 8 * v);
+                    for (int v = 0; v < 4; ++v) b[v] = *reinterpret_cast<const uint4*>(bias + bcol + 8 * v);
                 }
             };
             uint4 bias_next[4] = {};
@@ -379,6 +406,28 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     }
                 }
                 const int64_t col = col0 + c;
+                if (plain && col + 32 <= N_) {
+                    const bool in_rows = row < M_;
+                    uint32_t o[16];
+                    if (in_rows) {
+                        float f[32];
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(r[i]);
+                        if (bias != nullptr) {
+#pragma unroll
+                            for (int v = 0; v < 4; ++v) {
+                                const uint32_t ow[4] = {bias_now[v].x, bias_now[v].y, bias_now[v].z, bias_now[v].w};
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) add_bf16x2(ow[i], f[8 * v + 2 * i], f[8 * v + 2 * i + 1]);
+                            }
+                        }
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o[i]) : "f"(f[2 * i + 1]), "f"(f[2 * i]));
+                    }
+                    if (row - lane < M_) stage_and_store(o, in_rows, col, row - lane);
+                    continue;
+                }
                 if (p.splits > 1) {                      // split-K: raw fp32 partial sums, reduced afterwards
                     if (row < p.M && col < p.N) {
                         float* dst = p.partial + (static_cast<int64_t>(split) * p.M + row) * p.N + col;
@@ -440,27 +489,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                                 *reinterpret_cast<uint4*>(dst + 8 * v) = make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
                         }
                     }
-                    if (p.tma_store && row - lane < p.M) {
-                        // This warp's 32 rows x 32 columns go to its staging slot (row r at 64 r, its four
-                        // 16-byte pieces permuted by the 64-byte swizzle so that the stores of a quarter
-                        // warp cover all banks), then one TMA store writes the box as whole 64-byte row
-                        // segments and clips rows beyond M.  The slot is refilled only after the previous
-                        // store has read it.
-                        if (lane == 0) ptx::bulk_wait_read<0>();
-                        __syncwarp();
-                        if (in_rows) {
-                            const uint32_t row_addr = slot + lane * 64u, sw = (lane >> 1) & 3u;
-#pragma unroll
-                            for (uint32_t v = 0; v < 4; ++v)
-                                ptx::sts_v4(row_addr + ((v ^ sw) << 4), o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
-                        }
-                        ptx::fence_proxy_async();
-                        __syncwarp();
-                        if (lane == 0) {
-                            ptx::tma_store_2d(&tm_d, slot, static_cast<int>(col), static_cast<int>(row - lane));
-                            ptx::bulk_commit();
-                        }
-                    }
+                    if (p.tma_store && row - lane < p.M) stage_and_store(o, in_rows, col, row - lane);
                     if (p.q_codes != nullptr) {
                         // the bf16 outputs quantised in place as the next GEMM's row-wise operand
                         if (in_rows) {
