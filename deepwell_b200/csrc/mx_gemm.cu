@@ -743,20 +743,19 @@ static GemmPlan plan_gemm(int64_t M, int64_t N, int64_t K) {
     if (g_variant == 0 && pl.variant == 3) {
         // 256 x 256 tiles on CTA pairs (3), 256 x 192 tiles on CTA pairs (5) or 128 x 256 tiles on single CTAs (2).
         // Cost of the slowest worker in units of (256 columns x one k-block) of one SM's tensor time:
-        // rounds of tiles x (k-blocks x efficiency + per-tile overhead).  Variant 3's two accumulators share 32
-        // tensor-memory columns, so each tile waits for the previous tile's first epilogue step, a handoff that
-        // crosses the CTA pair (about 5 k-blocks, measured); variant 2 has the same wait inside one CTA (2.5)
-        // but a shallower ring (12 % slower mainloop); variant 5 has whole accumulators (4: epilogue tail) but
-        // moves 17 % more operand bytes per flop.  Fitted to measurements on B200: variant 2 wins for K <= 1024
-        // (16384 x 32000 x 1024: 519 vs 584 us), variant 5 for short problems with few tiles (8192 x 768 x 3072:
-        // 21 vs 26 us), variant 3 from K = 4096 on (variant 5 is 4-13 % slower at M = 16384).
+        // rounds of tiles x (k-blocks x efficiency + per-tile overhead), fitted to measurements on B200.  Variant 3's
+        // two accumulators share 32 tensor-memory columns, so each tile waits for the previous tile's first epilogue
+        // step (about 2 k-blocks); variant 5 has whole accumulators but more tiles and 17 % more operand bytes per
+        // flop; variant 2 has a shallower ring.  In practice 3 wins unless the tile count quantises badly on the
+        // 74 CTA pairs (8192 x 768 x 3072: 96 tiles of 256 x 256 = 2 rounds at 65 %; 128 tiles of 256 x 192 = 2
+        // rounds at 86 %: 20.7 us against 24.5).
         // Problems small enough for split-K keep variant 3, which the split heuristic below was measured with.
         const int64_t sms = sm_count(), pairs = sms / 2, tm = (M + 255) / 256;
         const bool would_split = tm * ((N + 255) / 256) * 4 <= pairs && nkb >= 32;
         auto rounds = [](int64_t tiles, int64_t workers) { return static_cast<double>((tiles + workers - 1) / workers); };
-        const double cost3 = rounds(tm * ((N + 255) / 256), pairs) * (nkb + 5.0);
-        const double cost5 = rounds(tm * ((N + 191) / 192), pairs) * 0.75 * (nkb + 4.0) * 1.15;
-        const double cost2 = rounds(((M + 127) / 128) * ((N + 255) / 256), sms) * (nkb * 1.12 + 2.5);
+        const double cost3 = rounds(tm * ((N + 255) / 256), pairs) * (nkb + 2.0);
+        const double cost5 = rounds(tm * ((N + 191) / 192), pairs) * 0.75 * (nkb + 3.0) * 1.05;
+        const double cost2 = rounds(((M + 127) / 128) * ((N + 255) / 256), sms) * (nkb * 1.05 + 2.7);
         if (!would_split) {
             if (cost5 < cost3 && cost5 <= cost2) pl.variant = 5;
             else if (cost2 < cost3) pl.variant = 2;
