@@ -38,6 +38,7 @@ ABI_SYMBOLS = (
     "dw_mxfp8_gemm_workspace", "dw_mxfp8_check_status", "dw_mxfp8_gemm_set_variant",
     "dw_mxfp8_gemm_set_timing_buffer", "dw_mxfp8_gemm_splitk_static", "dw_mxfp8_gemm_fused",
     "dw_mxfp8_colsum_workspace", "dw_mxfp8_quantize_both_colsum", "dw_mxfp8_gemm_grouped",
+    "dw_mxfp8_update_amax_history",
 )
 
 _lib = None
@@ -71,6 +72,7 @@ def load() -> ctypes.CDLL:
     L.dw_mxfp8_quantize.argtypes = [p, p, p, i64, i64, i32, i32, i32, p]
     L.dw_mxfp8_quantize_both.argtypes = [p, p, p, p, p, i64, i64, i32, i32, p]
     L.dw_mxfp8_dequantize.argtypes = [p, p, p, i64, i64, i32, p]
+    L.dw_mxfp8_update_amax_history.argtypes = [p, p, i32, i64, p]
     L.dw_mxfp8_colsum_workspace.argtypes = [i64, i64]
     L.dw_mxfp8_colsum_workspace.restype = sz
     L.dw_mxfp8_quantize_both_colsum.argtypes = [p, p, p, p, p, i64, i64, i32, i32, p, i32, p, sz, p]
@@ -154,6 +156,19 @@ def quantize_both(x: torch.Tensor, rule: int = RULE_OCP_FLOOR, layout: int = SF_
 def quantize_both_colsum(x: torch.Tensor, rule: int = RULE_OCP_FLOOR, layout: int = SF_TILED, out_dtype=torch.float32):
     """quantize_both plus the column sums of x ([cols], fp32 or bf16) from the same read.  See dw_mxfp8_quantize_both_colsum."""
     return ext().quantize_both_colsum(x, rule, layout, out_dtype == torch.bfloat16)
+
+
+def update_amax_history(x: torch.Tensor, amax_history: torch.Tensor) -> None:
+    """amax_history (float32, on x's device) shifted by one, newest max |x| at [0].  See dw_mxfp8_update_amax_history."""
+    _require_cuda(x, "input")
+    _require_cuda(amax_history, "amax_history")
+    if x.dtype != torch.bfloat16 or not x.is_contiguous():
+        raise RuntimeError("input must be a contiguous bfloat16 tensor")
+    if amax_history.dtype != torch.float32 or amax_history.dim() != 1 or not amax_history.is_contiguous():
+        raise RuntimeError("amax_history must be a contiguous 1-D float32 tensor")
+    with torch.cuda.device(x.device):
+        check(load().dw_mxfp8_update_amax_history(x.data_ptr(), amax_history.data_ptr(), amax_history.numel(), x.numel(),
+                                                  _stream(x.device)), "dw_mxfp8_update_amax_history")
 
 
 def dequantize(codes: torch.Tensor, scales: torch.Tensor, layout: int = SF_FLAT) -> torch.Tensor:

@@ -504,6 +504,39 @@ static int launch_tile_kernel(const uint16_t* x, uint8_t* cr, uint8_t* sr, uint8
     return launch_status();
 }
 
+// ------------------------------------------------------------------------------------------
+// amax history (MicroscaleManager::update_amax_history of the reference, an empty body there)
+// ------------------------------------------------------------------------------------------
+// history[i] = history[i - 1] for i = len-1 .. 1, history[0] = 0: one thread, the history is a few dozen floats
+__global__ void mx_amax_shift_kernel(float* __restrict__ history, int len) {
+    for (int i = len - 1; i > 0; --i) history[i] = history[i - 1];
+    history[0] = 0.0f;
+}
+
+// history[0] = max(history[0], max |x|) over n bf16 elements, NaN elements ignored.  Non-negative floats order like
+// their bit patterns, so the final combine is an integer atomicMax.
+__global__ void __launch_bounds__(256)
+mx_amax_kernel(const uint16_t* __restrict__ x, int64_t n, float* __restrict__ history) {
+    const int64_t tid = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x, step = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    uint32_t m = 0;                                            // two running magnitudes, one per bf16 lane
+    const bool vec = (reinterpret_cast<uintptr_t>(x) & 31) == 0;
+    const int64_t chunks = vec ? n / 16 : 0;
+    for (int64_t c = tid; c < chunks; c += step) {
+        uint32_t w[8];
+        ldg_nc_v8(x + c * 16, w);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) m = absmax_bf16x2(m, w[i]);
+    }
+    uint32_t a = fold_amax(m);
+    for (int64_t i = chunks * 16 + tid; i < n; i += step) {     // tail (and everything when x is not 32-byte aligned)
+        const uint32_t v = x[i] & 0x7FFFu;
+        if (v <= 0x7F80u) a = max(a, v);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) a = max(a, __shfl_xor_sync(0xFFFFFFFFu, a, off));
+    if ((threadIdx.x & 31u) == 0u && a != 0u) atomicMax(reinterpret_cast<unsigned int*>(history), a << 16);
+}
+
 static bool tile_path_ok(const void* x, int64_t rows, int64_t cols) {
     const int64_t tiles = ((rows + 127) / 128) * ((cols + 127) / 128);
     return rows % 32 == 0 && cols % 32 == 0 && aligned(x, 16) && tiles < (1ll << 31);
@@ -633,6 +666,20 @@ extern "C" DW_API int dw_mxfp8_quantize_both_colsum(const void* x_bf16, void* co
     if (rc != DW_OK) return rc;
     mx_colsum_reduce_kernel<<<static_cast<unsigned>((cols + 31) / 32), 256, 0, st>>>(static_cast<const float*>(workspace), tiles_r,
                                                                                       cols, colsum_out, colsum_is_bf16);
+    return launch_status();
+}
+
+extern "C" DW_API int dw_mxfp8_update_amax_history(const void* x_bf16, float* amax_history, int history_len, int64_t num_elements,
+                                                   void* stream) {
+    if (!amax_history || history_len <= 0 || num_elements < 0 || (num_elements > 0 && !x_bf16)) return DW_ERR_BAD_ARG;
+    if ((reinterpret_cast<uintptr_t>(amax_history) & 3) != 0 || (reinterpret_cast<uintptr_t>(x_bf16) & 1) != 0) return DW_ERR_BAD_ARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    mx_amax_shift_kernel<<<1, 1, 0, st>>>(amax_history, history_len);
+    if (launch_status() != DW_OK) return DW_ERR_LAUNCH;
+    if (num_elements == 0) return DW_OK;
+    const int64_t want = (num_elements / 16 + 255) / 256 + 1;
+    const int grid = static_cast<int>(std::min<int64_t>(want, static_cast<int64_t>(num_sms()) * 8));
+    mx_amax_kernel<<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(x_bf16), num_elements, amax_history);
     return launch_status();
 }
 

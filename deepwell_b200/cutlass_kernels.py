@@ -284,6 +284,28 @@ class MicroscaleManager:
         return out.view(input.shape)
 
 
+    def transpose_mxfp8(self, input: torch.Tensor, input_scales: torch.Tensor, block_size: int = 32,
+                        scale_layout: str = "flat", scale_rule: str = "ocp_floor"):
+        """Row-wise MX operand [rows, cols] -> the column-wise operand of the same values: payload transposed
+        [cols, rows], scaling blocks along the former rows.  A transpose of MX data needs requantisation (the blocks
+        change direction): dequantise, then quantise column-wise.  MicroscaleManager::transpose_mxfp8 of the reference
+        (csrc/cutlass_kernels.cpp:412-424) is an empty body.  When the bf16 source is at hand, quantize_both gives
+        both forms from one read and without the intermediate rounding."""
+        if block_size != 32:
+            raise RuntimeError("MXFP8 uses 32-element scaling blocks")
+        x = self.dequantize_mxfp8(input, input_scales, block_size, scale_layout)
+        x2 = x.reshape(-1, x.shape[-1]) if x.dim() != 2 else x
+        return nv.quantize(x2, nv.DIR_COL_T, nv.RULES[scale_rule], nv.LAYOUTS[scale_layout])
+
+    def update_amax_history(self, tensor: torch.Tensor, amax_history: torch.Tensor) -> torch.Tensor:
+        """Shifts ``amax_history`` (float32 [history_len], on the tensor's device) by one and stores max |tensor| at [0]
+        (MicroscaleManager::update_amax_history, csrc/cutlass_kernels.cpp:426-434, empty in the reference)."""
+        if not tensor.is_cuda:
+            raise RuntimeError("Input must be on CUDA")
+        nv.update_amax_history(tensor.to(torch.bfloat16).contiguous(), amax_history)
+        return amax_history
+
+
 def profile_kernel(kernel: BlackwellGemmKernel, warmup_iterations: int = 10, profile_iterations: int = 100) -> dict:
     """Times kernel.gemm on random operands with CUDA events (the reference returns constants,
     csrc/python_bindings.cpp:244-255)."""

@@ -99,6 +99,14 @@ int dw_mxfp8_quantize_both_colsum(const void *x_bf16, void *codes_row, void *sca
 int dw_mxfp8_dequantize(const void *codes, const void *scales, void *out_bf16, int64_t rows,
                         int64_t cols, int scale_layout, void *stream);
 
+/* Rolling history of a tensor's absolute maximum: amax_history[i] <- amax_history[i - 1] for i = len-1 .. 1,
+ * amax_history[0] <- max |x| over num_elements bf16 values (NaN ignored; 0 for an empty tensor).  amax_history is a
+ * device array of history_len floats.  Gives a body to MicroscaleManager::update_amax_history
+ * (csrc/cutlass_kernels.cpp:426-434, empty in the reference).  MX block scaling itself needs no history; the call
+ * serves per-tensor scaling policies (src/deepwell/precision/policy.py:50, amax_history_len). */
+int dw_mxfp8_update_amax_history(const void *x_bf16, float *amax_history, int history_len,
+                                 int64_t num_elements, void *stream);
+
 /* D[M,N] = bf16(alpha * A[M,K] . B[N,K]^T + beta * D + bias[N]).
  * A and B are E4M3 codes, both K-major (contraction dim contiguous), with DW_SF_TILED scales;
  * bias (bf16 [N]) may be NULL; with beta == 0 the previous content of D is not read.

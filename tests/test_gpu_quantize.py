@@ -209,3 +209,35 @@ def test_column_sums_reject_shapes_outside_the_tile_kernel(nv, native_lib):
     p = x.data_ptr()
     rc = native_lib.dw_mxfp8_quantize_both_colsum(p, p, p, p, p, 48, 40, 0, 1, p, 0, p, 1 << 20, None)
     assert rc == -1
+
+
+def test_amax_history_and_transpose_requantise(nv, native_lib):
+    """MicroscaleManager.update_amax_history: history shifted by one, newest max |x| first (bf16 values, so the fp32
+    maximum is exact), NaN ignored, unaligned and empty inputs; transpose_mxfp8: row-wise operand -> column-wise operand
+    equals dequantise + column-wise quantise in the oracle."""
+    from deepwell_b200 import cutlass_kernels as ck
+    mm = ck.MicroscaleManager()
+    hist = torch.tensor([3.0, 2.0, 1.0, 0.5], device="cuda")
+    g = torch.Generator("cuda").manual_seed(77)
+    x = (torch.randn(1000, 777, device="cuda", generator=g) * 3).bfloat16()
+    x[5, 5] = float("nan")
+    x[17, 100] = -123.5
+    mm.update_amax_history(x, hist)
+    assert hist.tolist() == [123.5, 3.0, 2.0, 1.0]
+    mm.update_amax_history(x.flatten()[1:-1], hist)                 # 2-byte aligned view, tail path
+    assert hist.tolist() == [123.5, 123.5, 3.0, 2.0]
+    mm.update_amax_history(torch.empty(0, dtype=torch.bfloat16, device="cuda"), hist)
+    assert hist.tolist() == [0.0, 123.5, 123.5, 3.0]
+    big = torch.randn(4096, 4096, device="cuda", generator=g).bfloat16()
+    mm.update_amax_history(big, hist)
+    assert hist[0].item() == big.float().abs().max().item()
+    assert native_lib.dw_mxfp8_update_amax_history(big.data_ptr(), None, 4, 16, None) == -1
+    assert native_lib.dw_mxfp8_update_amax_history(big.data_ptr(), hist.data_ptr(), 0, 16, None) == -1
+    # transpose with requantisation
+    a = (torch.randn(256, 160, device="cuda", generator=g) * 2).bfloat16()
+    codes, scales = mm.quantize_mxfp8(a)
+    ct, st = mm.transpose_mxfp8(codes, scales)
+    deq = o.f32_to_bf16_bits(o.dequantize_rowwise(codes.view(torch.uint8).cpu().numpy(), scales.cpu().numpy()))
+    ec, es = o.quantize_colwise(deq)
+    assert ct.shape == (160, 256) and np.array_equal(ct.view(torch.uint8).cpu().numpy(), ec)
+    assert np.array_equal(st.cpu().numpy().reshape(es.shape), es)
