@@ -8,9 +8,10 @@ import sys as _sys
 import deepwell_b200 as _impl
 from deepwell_b200 import DWLinear, DeepwellOptimizer, cutlass_kernels, kernels, optimize, optimize_for_blackwell  # noqa: F401
 from deepwell_b200 import optimizer as _optimizer
-from deepwell_b200.kernels import cutlass_bindings as _cb, production_kernels as _pk, registry as _reg
+from deepwell_b200.kernels import blackwell_production as _bp, cutlass_bindings as _cb, production_kernels as _pk, registry as _reg
 
 __version__ = _impl.__version__
 for _name, _mod in (("cutlass_kernels", cutlass_kernels), ("kernels", kernels), ("optimizer", _optimizer),
-                    ("kernels.cutlass_bindings", _cb), ("kernels.registry", _reg), ("kernels.production_kernels", _pk)):
+                    ("kernels.cutlass_bindings", _cb), ("kernels.registry", _reg), ("kernels.production_kernels", _pk),
+                    ("kernels.blackwell_production", _bp)):
     _sys.modules[__name__ + "." + _name] = _mod

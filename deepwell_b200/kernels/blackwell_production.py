@@ -1,0 +1,152 @@
+"""The linear-path classes of the reference's ``deepwell.kernels.blackwell_production`` over the MXFP8 kernels.
+
+Kept: BlackwellConfig (src/deepwell/kernels/blackwell_production.py:50-77, the fields this path reads),
+BlackwellGEMM.gemm with optional bias and activation fused into the GEMM epilogue (:189-229),
+BlackwellGroupedGEMM (:232-276), FusedLinearGELU (:487-527), FusedLayerNormLinear (:530-575) and
+optimize_model_for_blackwell (:578-624).  The attention classes of that module (BlackwellFlashAttention,
+DWSelfAttention) belong to a different path and are not part of this package.
+
+In the reference the fusion flags select arguments of a CUTLASS plan that is never built on a machine without the
+CUTLASS Python package; here ``activation`` reaches dw_mxfp8_gemm_fused, which applies bias and ReLU / exact GELU / SiLU
+to the fp32 accumulator before the bf16 rounding.
+"""
+from __future__ import annotations
+
+import dataclasses
+from typing import List, Optional, Sequence
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .. import _native as nv
+from ..cutlass_kernels import mxfp8_gemm_bf16, mxfp8_grouped_gemm_bf16
+from ..linear import DWLinear
+
+_ACTIVATIONS = {None: "none", "none": "none", "relu": "relu", "gelu": "gelu", "silu": "silu", "swish": "silu"}
+
+
+@dataclasses.dataclass
+class BlackwellConfig:
+    sm_version: int = 100
+    use_mxfp8: bool = True
+    use_fp4: bool = False
+    use_tcgen05: bool = True
+    preferred_cluster_size: int = 2
+    fuse_gelu: bool = True
+    fuse_layernorm: bool = True
+    fuse_bias: bool = True
+    persistent_kernel: bool = True
+
+
+class BlackwellGEMM:
+    """gemm(a [M,K], b [K,N], bias, activation) -> bf16 [M,N]; operands are quantised to MXFP8 along K."""
+
+    def __init__(self, config: Optional[BlackwellConfig] = None):
+        nv.ext()
+        self.config = config or BlackwellConfig()
+        if self.config.use_fp4:
+            raise RuntimeError("only the MXFP8 block-scaled kernel is built in this package")
+
+    def gemm(self, a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = None,
+             activation: Optional[str] = None) -> torch.Tensor:
+        if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[0]:
+            raise RuntimeError(f"Dimension mismatch: {tuple(a.shape)} x {tuple(b.shape)}")
+        if not a.is_cuda or not b.is_cuda:
+            raise RuntimeError("inputs must be on CUDA")
+        act = _ACTIVATIONS.get(activation)
+        if act is None:
+            raise RuntimeError(f"unknown activation {activation!r}")
+        bias_b = None if bias is None else bias.to(torch.bfloat16).contiguous()
+        fuse_act = act != "none" and (act != "gelu" or self.config.fuse_gelu)
+        if not fuse_act and (bias_b is None or self.config.fuse_bias):
+            out = mxfp8_gemm_bf16(a, b, None, 1.0, 0.0, bias=bias_b)
+        else:
+            a_codes, a_sf = nv.quantize(a.to(torch.bfloat16), nv.DIR_ROW, nv.RULE_OCP_FLOOR, nv.SF_TILED)
+            bb = b.to(torch.bfloat16)
+            if bb.stride(0) == 1 and bb.stride(1) == bb.shape[0]:
+                b_codes, b_sf = nv.quantize(bb.t(), nv.DIR_ROW, nv.RULE_OCP_FLOOR, nv.SF_TILED)
+            else:
+                b_codes, b_sf = nv.quantize(bb.contiguous(), nv.DIR_COL_T, nv.RULE_OCP_FLOOR, nv.SF_TILED)
+            fused_bias = bias_b if self.config.fuse_bias else None
+            out, _, _ = nv.gemm_fused(a_codes, a_sf, b_codes, b_sf, bias=fused_bias,
+                                      activation=act if fuse_act and fused_bias is bias_b else "none", quantize_out=False)
+            if fused_bias is None and bias_b is not None:      # bias outside the kernel: the activation follows it
+                out = out + bias_b
+                if fuse_act:
+                    out = getattr(F, act)(out)
+        if act != "none" and not fuse_act:
+            out = getattr(F, act)(out)
+        return out
+
+
+class BlackwellGroupedGEMM:
+    """grouped_gemm(inputs, weights): one launch for groups of equal K and N (the experts of an MoE layer)."""
+
+    def __init__(self, config: Optional[BlackwellConfig] = None):
+        nv.ext()
+        self.config = config or BlackwellConfig()
+        self._weight_cache: dict = {}
+
+    def grouped_gemm(self, inputs: Sequence[torch.Tensor], weights: Sequence[torch.Tensor]) -> List[torch.Tensor]:
+        if len(inputs) != len(weights):
+            raise RuntimeError("inputs and weights differ in length")
+        return mxfp8_grouped_gemm_bf16(inputs, weights, 1.0, weight_cache=self._weight_cache)
+
+
+class FusedLinearGELU(nn.Module):
+    """Linear + exact GELU.  Without autograd the bias and the GELU run in the GEMM epilogue on the fp32 accumulator
+    (one kernel after the quantiser); with autograd the layer is DWLinear followed by F.gelu, whose backward needs the
+    pre-activation the fused kernel does not keep."""
+
+    def __init__(self, in_features: int, out_features: int, config: Optional[BlackwellConfig] = None):
+        super().__init__()
+        self.config = config or BlackwellConfig()
+        self.linear = DWLinear(in_features, out_features, bias=True, dtype=torch.bfloat16)
+        nn.init.xavier_uniform_(self.linear.weight)
+        nn.init.zeros_(self.linear.bias)
+        self.in_features, self.out_features = in_features, out_features
+
+    @property
+    def weight(self) -> nn.Parameter:
+        return self.linear.weight
+
+    @property
+    def bias(self) -> nn.Parameter:
+        return self.linear.bias
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if not x.is_cuda:
+            raise RuntimeError("FusedLinearGELU runs on CUDA (sm_100a) only; there is no CPU path")
+        needs_grad = torch.is_grad_enabled() and (x.requires_grad or self.weight.requires_grad or self.bias.requires_grad)
+        if needs_grad or not self.config.fuse_gelu:
+            return F.gelu(self.linear(x))
+        lead = x.shape[:-1]
+        x2d = x.reshape(-1, self.in_features).to(torch.bfloat16)
+        (w_codes, w_sf), _ = self.linear._quantized_weight(need_col=False)
+        x_codes, x_sf = nv.quantize(x2d, nv.DIR_ROW, self.linear.scale_rule, nv.SF_TILED)
+        y, _, _ = nv.gemm_fused(x_codes, x_sf, w_codes, w_sf, bias=self.bias.detach().to(torch.bfloat16).contiguous(),
+                                activation="gelu", quantize_out=False)
+        return y.reshape(*lead, self.out_features).to(x.dtype)
+
+
+class FusedLayerNormLinear(nn.Module):
+    """LayerNorm followed by an MXFP8 linear layer.  The normalisation is torch's; the linear layer is DWLinear (the
+    reference's class of this name computes both with torch, src/deepwell/kernels/blackwell_production.py:554-575)."""
+
+    def __init__(self, normalized_shape: int, out_features: int, config: Optional[BlackwellConfig] = None):
+        super().__init__()
+        self.config = config or BlackwellConfig()
+        self.norm = nn.LayerNorm(normalized_shape, dtype=torch.bfloat16)
+        self.linear = DWLinear(normalized_shape, out_features, bias=True, dtype=torch.bfloat16)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.linear(self.norm(x))
+
+
+def optimize_model_for_blackwell(model: nn.Module, config: Optional[BlackwellConfig] = None) -> nn.Module:
+    """Every eligible nn.Linear of ``model`` becomes a DWLinear, in place (the reference's function of this name also
+    swaps attention modules, which are outside this package)."""
+    from ..optimizer import optimize
+    config = config or BlackwellConfig()
+    return optimize(model, precision="mxfp8" if config.use_mxfp8 else "bf16", verbose=False, inplace=True)

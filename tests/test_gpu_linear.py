@@ -25,6 +25,14 @@ def oracle_linear(x, w, b=None):
     return torch.from_numpy(y)
 
 
+def oracle_linear_f32(x, w, b=None):
+    """fp32 result of the dequantised product (+ bias) before the bf16 rounding."""
+    xc, xs = o.quantize_rowwise(bits_of(x))
+    wc, ws = o.quantize_rowwise(bits_of(w))
+    y = torch.from_numpy(o.dequantize_rowwise(xc, xs)) @ torch.from_numpy(o.dequantize_rowwise(wc, ws)).t()
+    return y if b is None else y + b.float().cpu()[None, :]
+
+
 def close(got, ref, rtol=1e-2):
     got, ref = got.double().cpu(), ref.double().cpu()
     return bool(((got - ref).abs() <= rtol * torch.maximum(ref.abs(), ref.abs().mean())).all())
@@ -227,3 +235,41 @@ def test_dwlinear_training_step_captured_in_a_cuda_graph(dw):
         assert torch.equal(a, b)
     from deepwell_b200 import _native
     _native.check_status()
+
+
+def test_blackwell_production_gemm_and_fused_linear_gelu(dw):
+    """deepwell.kernels.blackwell_production: BlackwellGEMM.gemm with bias + activation fused in the epilogue equals the
+    oracle's activation of the fp32 result (tolerance 1e-2 of the value scale, bf16 output); FusedLinearGELU without
+    autograd equals that, with autograd equals DWLinear + F.gelu and trains; BlackwellGroupedGEMM splits like a loop."""
+    from deepwell_b200.kernels.blackwell_production import (BlackwellConfig, BlackwellGEMM, BlackwellGroupedGEMM,
+                                                            FusedLayerNormLinear, FusedLinearGELU,
+                                                            optimize_model_for_blackwell)
+    torch.manual_seed(41)
+    x = torch.randn(300, 256, device="cuda").bfloat16()
+    w = (torch.randn(384, 256, device="cuda") * 0.05).bfloat16()
+    b = torch.randn(384, device="cuda").bfloat16()
+    pre = torch.from_numpy(o.bf16_bits_to_f32(o.mxfp8_linear(bits_of(x), bits_of(w), bias_bits=bits_of(b)))).float()
+    exact = oracle_linear_f32(x, w, b)
+    g = BlackwellGEMM(BlackwellConfig())
+    assert close(g.gemm(x, w.t(), bias=b), pre)
+    for act, fn in (("gelu", torch.nn.functional.gelu), ("relu", torch.relu), ("silu", torch.nn.functional.silu)):
+        assert close(g.gemm(x, w.t(), bias=b, activation=act), fn(exact), rtol=1e-2)
+    unfused = BlackwellGEMM(BlackwellConfig(fuse_gelu=False, fuse_bias=False))
+    assert close(unfused.gemm(x, w.t(), bias=b, activation="gelu"), torch.nn.functional.gelu(exact), rtol=2e-2)
+    layer = FusedLinearGELU(256, 384).cuda()
+    with torch.no_grad():
+        layer.weight.copy_(w)
+        layer.bias.copy_(b)
+        y_inf = layer(x.view(3, 100, 256))
+    assert y_inf.shape == (3, 100, 384) and close(y_inf.reshape(-1, 384), torch.nn.functional.gelu(exact), rtol=1e-2)
+    xg = x.clone().requires_grad_(True)
+    y_train = layer(xg)
+    y_train.float().square().mean().backward()
+    assert close(y_train, torch.nn.functional.gelu(pre), rtol=1e-2)
+    assert xg.grad is not None and layer.weight.grad is not None and layer.bias.grad is not None
+    outs = BlackwellGroupedGEMM().grouped_gemm([x, x[:77]], [w.t(), w.t()])
+    assert close(outs[0], g.gemm(x, w.t())) and outs[1].shape == (77, 384)
+    ln = FusedLayerNormLinear(256, 128).cuda()
+    assert ln(x).shape == (300, 128)
+    seq = optimize_model_for_blackwell(nn.Sequential(nn.Linear(256, 128), nn.GELU(), nn.Linear(128, 64)).cuda().bfloat16())
+    assert isinstance(seq[0], dw.DWLinear) and isinstance(seq[2], dw.DWLinear)
