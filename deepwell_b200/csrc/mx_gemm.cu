@@ -339,6 +339,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         // inside the loop, the chain of dependent loads and branches took ~350 cycles per chunk (measured).
         const int64_t M_ = p.M, N_ = p.N;
         const uint16_t* const bias = p.bias;
+        const int act = p.act;
         // the common epilogue: D = bf16(accumulator + bias) through the TMA store and nothing else
         const bool plain = p.splits <= 1 && vec_ok && p.tma_store != 0 && p.alpha == 1.0f && p.beta == 0.0f &&
                            p.act == DW_ACT_NONE && p.q_codes == nullptr;
@@ -475,9 +476,17 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                                 for (int i = 0; i < 4; ++i) add_bf16x2(ow[i], f[8 * v + 2 * i], f[8 * v + 2 * i + 1]);
                             }
                         }
-                        if (p.act != DW_ACT_NONE) {
+                        // one uniform branch per chunk, then a loop of a single function: with the selection inside
+                        // the loop every element paid for all three functions (ReLU cost as much as GELU)
+                        if (act == DW_ACT_RELU) {
 #pragma unroll
-                            for (int i = 0; i < 32; ++i) f[i] = apply_activation(f[i], p.act);
+                            for (int i = 0; i < 32; ++i) f[i] = fmaxf(f[i], 0.0f);
+                        } else if (act == DW_ACT_GELU) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) f[i] = apply_activation(f[i], DW_ACT_GELU);
+                        } else if (act == DW_ACT_SILU) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) f[i] = apply_activation(f[i], DW_ACT_SILU);
                         }
 #pragma unroll
                         for (int i = 0; i < 16; ++i)

@@ -130,6 +130,40 @@ class FusedLinearGELU(nn.Module):
         return y.reshape(*lead, self.out_features).to(x.dtype)
 
 
+class FusedMLP(nn.Module):
+    """up-projection -> activation -> down-projection.  Without autograd the hidden activation never exists in bf16:
+    the first GEMM's epilogue applies bias and activation to the fp32 accumulator and writes the result already
+    quantised (E4M3 codes + tiled E8M0 scales, bit-identical to quantising the bf16 result), and the second GEMM
+    consumes it as its A operand.  With autograd the three steps run separately (DWLinear, torch activation, DWLinear).
+    The reference runs its MLP as two GEMM calls with torch's GELU in between (src/deepwell/engine.py:132-209)."""
+
+    def __init__(self, in_features: int, hidden_features: int, out_features: Optional[int] = None,
+                 activation: str = "gelu", bias: bool = True, config: Optional[BlackwellConfig] = None):
+        super().__init__()
+        if _ACTIVATIONS.get(activation) in (None, "none"):
+            raise ValueError(f"activation must be one of relu, gelu, silu; got {activation!r}")
+        self.config = config or BlackwellConfig()
+        self.activation = _ACTIVATIONS[activation]
+        self.up = DWLinear(in_features, hidden_features, bias=bias, dtype=torch.bfloat16)
+        self.down = DWLinear(hidden_features, out_features or in_features, bias=bias, dtype=torch.bfloat16)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if not x.is_cuda:
+            raise RuntimeError("FusedMLP runs on CUDA (sm_100a) only; there is no CPU path")
+        if torch.is_grad_enabled() and (x.requires_grad or any(p.requires_grad for p in self.parameters())):
+            return self.down(getattr(F, self.activation)(self.up(x)))
+        lead = x.shape[:-1]
+        x2d = x.reshape(-1, self.up.in_features).to(torch.bfloat16)
+        (uw, us), _ = self.up._quantized_weight(need_col=False)
+        (dw_, ds), _ = self.down._quantized_weight(need_col=False)
+        bf16 = lambda p: None if p is None else p.detach().to(torch.bfloat16).contiguous()
+        xc, xs = nv.quantize(x2d, nv.DIR_ROW, self.up.scale_rule, nv.SF_TILED)
+        _, hc, hs = nv.gemm_fused(xc, xs, uw, us, bias=bf16(self.up.bias), activation=self.activation, quantize_out=True,
+                                  write_d=False, rule=self.up.scale_rule)
+        y = nv.gemm(hc, hs, dw_, ds, bias=bf16(self.down.bias))
+        return y.reshape(*lead, self.down.out_features).to(x.dtype)
+
+
 class FusedLayerNormLinear(nn.Module):
     """LayerNorm followed by an MXFP8 linear layer.  The normalisation is torch's; the linear layer is DWLinear (the
     reference's class of this name computes both with torch, src/deepwell/kernels/blackwell_production.py:554-575)."""

@@ -273,3 +273,28 @@ def test_blackwell_production_gemm_and_fused_linear_gelu(dw):
     assert ln(x).shape == (300, 128)
     seq = optimize_model_for_blackwell(nn.Sequential(nn.Linear(256, 128), nn.GELU(), nn.Linear(128, 64)).cuda().bfloat16())
     assert isinstance(seq[0], dw.DWLinear) and isinstance(seq[2], dw.DWLinear)
+
+
+def test_fused_mlp_inference_equals_the_unfused_layers(dw):
+    """FusedMLP without autograd (hidden activation quantised in the first GEMM's epilogue, never written in bf16)
+    against the same module with autograd enabled (DWLinear, torch GELU on the bf16 result, DWLinear): the fused path
+    applies the activation to the fp32 accumulator, so the hidden values differ by one bf16 rounding before they are
+    quantised; where that moves an E4M3 code (steps of 6-12 %) one term of the second contraction changes, so the
+    outputs are compared in norm: relative Frobenius error <= 3e-2 (the bit-level check of the fused epilogue is in
+    test_gpu_gemm.py); the fused path is deterministic."""
+    from deepwell_b200.kernels.blackwell_production import FusedMLP
+    torch.manual_seed(43)
+    mlp = FusedMLP(256, 1024, 256, activation="gelu").cuda()
+    x = torch.randn(4, 96, 256, device="cuda").bfloat16()
+    with torch.no_grad():
+        y1 = mlp(x)
+        y2 = mlp(x)
+    assert y1.shape == (4, 96, 256) and torch.equal(y1, y2)
+    y_ref = mlp(x)                       # parameters require grad: the unfused path
+    assert y_ref.requires_grad
+    err = (y1.float() - y_ref.detach().float()).norm() / y_ref.detach().float().norm()
+    assert err.item() <= 3e-2, err.item()
+    y_ref.float().square().mean().backward()
+    assert mlp.up.weight.grad is not None and mlp.down.weight.grad is not None
+    from deepwell_b200 import _native
+    _native.check_status()
