@@ -600,6 +600,12 @@ def main():
         # PCIe carries both directions at once, and the copies of other layers hide the compute.
         s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
         dev_x = [torch.empty(M_TOKENS, l["k"], dtype=torch.bfloat16, device=dev) for l in layers]
+        # N > 1: X is replicated on every rank (column-parallel layers).  Each rank uploads 1/N of its rows over its
+        # own PCIe link and the ranks exchange the slices over NVLink (one all-gather per layer), instead of every
+        # rank pulling the whole X out of the same host memory.
+        r0, r1 = shard_bounds(M_TOKENS, world, rank)
+        even_rows = world > 1 and M_TOKENS % world == 0
+        x_slice = [torch.empty(r1 - r0, l["k"], dtype=torch.bfloat16, device=dev) for l in layers] if even_rows else None
         arrived = [torch.cuda.Event() for _ in layers]
         computed = [torch.cuda.Event() for _ in layers]
         freed = [torch.cuda.Event() for _ in layers]
@@ -609,7 +615,11 @@ def main():
             for i, (hx, hy, l, kern) in enumerate(zip(host_x, host_y, layers, kernels)):
                 s_in.wait_event(freed[i])                       # previous step's GEMM has read dev_x[i]
                 with torch.cuda.stream(s_in):
-                    dev_x[i].copy_(hx, non_blocking=True)
+                    if even_rows:
+                        x_slice[i].copy_(hx[r0:r1], non_blocking=True)
+                        dist.all_gather_into_tensor(dev_x[i], x_slice[i])
+                    else:
+                        dev_x[i].copy_(hx, non_blocking=True)
                     arrived[i].record(s_in)
                 stream.wait_event(arrived[i])
                 y = kern.gemm(dev_x[i], l["w"].t())             # quantise X, quantise W, GEMM
@@ -634,10 +644,13 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             dt = float(t.item())
         e2e = {"value": total_flops() / dt / 1e12, "unit": "TFLOP/s",
-               "h2d_bytes_per_step": int(sum(hx.numel() * 2 for hx in host_x)),
-               "d2h_bytes_per_step": int(sum(hy.numel() * 2 for hy in host_y)), "ms_per_step": dt * 1e3,
+               # whole-job bytes per step: every row of every X crosses PCIe once (N > 1: each rank uploads its
+               # slice, NVLink replicates it), every rank downloads its shard of every Y
+               "h2d_bytes_per_step": int(sum(hx.numel() * 2 for hx in host_x)) * (1 if even_rows or world == 1 else world),
+               "d2h_bytes_per_step": int(sum(hy.numel() * 2 for hy in host_y)) * world, "ms_per_step": dt * 1e3,
                "api": "deepwell_b200.cutlass_kernels.BlackwellGemmKernel.gemm, pinned host X in, pinned host Y out, "
-                      "copies on their own streams"}
+                      "copies on their own streams" + ("; X uploaded as 1/N row slices and all-gathered over NVLink"
+                                                       if even_rows else "")}
         nv.check_status(dev)
 
     cpu_baseline = None
