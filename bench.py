@@ -11,25 +11,39 @@ quantisation of layer i+1 runs on a second stream under the GEMM of layer i (--s
 With N GPUs every weight is sharded along its output dimension across the ranks (X is replicated;
 no collective on the data path), so the total work is fixed: strong scaling.
 
-Prints ONE JSON line (rank 0).  `value` is whole-job TFLOP/s with inputs resident in HBM;
-`e2e` is the same through the public API with pinned host buffers, the host->device copy of
-every X and the device->host copy of every Y inside the timed region, on their own streams;
-`roofline` is measured live with CUDA events around every GEMM launch (`achieved_alone`: the same
-launches with nothing else on the GPU); `roofline_quantize` times the row quantiser on the largest
-activation; `cpu_baseline` times the CPU restatement of the same path on the host cores (rank 0, N = 1).
+Prints ONE JSON line (rank 0).  Keys beyond the basic contract:
+  value              whole-job TFLOP/s with inputs resident in HBM (CUDA events, max over ranks)
+  e2e                the same through the public API (cutlass_kernels.BlackwellGemmKernel.gemm) with pinned host
+                     buffers: the host->device copy of every X and the device->host copy of every Y inside the timed
+                     region, on their own streams
+  roofline           the GEMM, measured live with CUDA events around every GEMM launch of the timed region
+                     (`achieved_alone`: the same launches with nothing else on the GPU); both fractions, of 2 x the
+                     measured bf16 burst rate and of 2 x the measured sustained rate; `frac` is the one that fits the run
+  sustained          the same step repeated for >= 2.5 s with the SM clock sampled throughout: the steady state under
+                     the power cap, which the short timed region does not reach
+  roofline_quantize  the row quantiser on the largest activation, against the measured copy bandwidth
+  vendor_gemm        the vendor's block-scaled GEMM (torch._scaled_mm) alternated with ours on the same operands
+  gpt2_mlp, decoder_step   two secondary workloads (GPT-2-small MLP forward+backward; the end-to-end optimize()
+                     training step of a 12-layer decoder), each beside the same layers in bf16 (N = 1 only)
+  with_gather, sharded     N > 1: the step with every layer's output all-gathered over NVLink, and a parity check of
+                     ColumnParallelDWLinear / RowParallelDWLinear under NCCL against the unsharded layer
+  cpu_baseline       the CPU restatement of the same path on the host cores (rank 0, N = 1)
 
---impl reference times only that CPU path (the reference ships no GPU implementation of an
-MXFP8 GEMM and its CPU path is a Python module calling torch.matmul).
+--impl reference times only that CPU path (the reference ships no GPU implementation of an MXFP8 GEMM; its CPU path
+for the GEMM stage is a Python module calling torch.matmul, which is loaded from an install of the reference under
+baseline/_ref when that is present).
 
-Other modes (each prints its own JSON): --workload decoder_step (end-to-end optimize() training step of
-a 12-layer decoder beside the same model with bf16 nn.Linear), --sweep-quantize (quantise-only bandwidth
-sweep), --profile-case (a few launches of one kernel on a small case, for an ncu capture),
+Other modes (each prints its own JSON): --workload decoder_step, --sweep-quantize (quantise-only bandwidth sweep),
+--compare-vendor, --profile-case (a few launches of one kernel on a small case, for an ncu capture),
+--traffic-from-csv (turns an ncu CSV of the GEMM launches into bench_gemm_dram_traffic.json),
 --emulate-world W (tuning aid: rank 0's shard sizes of a W-GPU job on one GPU).
 """
 from __future__ import annotations
 
 import argparse
+import csv
 import json
+import math
 import os
 import sys
 import threading
@@ -47,10 +61,8 @@ METRIC = "mxfp8_quant_gemm_tflops"
 WORKLOAD = "llama3_8b_linears_M16384"
 CPU_SAMPLE_ROWS = 4096
 NOMINAL_MXFP8_TFLOPS = 4500.0
-# dram__bytes_read.sum + dram__bytes_write.sum of the four GEMM launches of one step at N = 1 (ncu capture of
-# this file's own launches, summarised in profiles/mx_gemm_kernel_bench_shapes_dram_traffic.md), bytes
-GEMM_DRAM_TRAFFIC = {"qkv": 278289152, "o": 178107648, "gate_up": 1457078272, "down": 1161285120}
-GEMM_DRAM_TRAFFIC_BYTES = sum(GEMM_DRAM_TRAFFIC.values()) / len(GEMM_DRAM_TRAFFIC)      # mean per launch
+TRAFFIC_JSON = os.path.join(ROOT, "bench_gemm_dram_traffic.json")
+REFERENCE_GEMM_MODULE = os.path.join(ROOT, "baseline", "_ref", "deepwell", "cutlass_kernels.py")
 
 
 def measured_peaks():
@@ -61,6 +73,17 @@ def measured_peaks():
         return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
                 "bf16_tflops_sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"]), "source": "measured"}
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def gemm_dram_traffic():
+    """Mean DRAM bytes (read + write) per GEMM launch of one step at N = 1, from the ncu capture recorded in
+    bench_gemm_dram_traffic.json (written by --traffic-from-csv); None when that file is absent."""
+    if not os.path.exists(TRAFFIC_JSON):
+        return None, None
+    with open(TRAFFIC_JSON) as f:
+        t = json.load(f)
+    per_layer = {k: v["dram_read_bytes"] + v["dram_write_bytes"] for k, v in t["layers"].items()}
+    return sum(per_layer.values()) / max(1, len(per_layer)), t
 
 
 def total_flops(m=M_TOKENS):
@@ -115,18 +138,36 @@ class ClockSampler:
 # ----------------------------------------------------------------------------------------------
 # CPU path (oracle): the reference arm and the cpu_baseline leg
 # ----------------------------------------------------------------------------------------------
+_ref_gemm_kernel = None
+
+
+def reference_gemm_kernel():
+    """BlackwellGemmKernel of the reference's own CPU module (src/deepwell/cutlass_kernels.py:9-55 of the reference,
+    whose gemm is alpha * torch.matmul(a, b) + beta * c), loaded by path from an install of the reference under
+    baseline/_ref; None when no such install travelled with the repository."""
+    global _ref_gemm_kernel
+    if _ref_gemm_kernel is None and os.path.exists(REFERENCE_GEMM_MODULE):
+        import importlib.util
+        spec = importlib.util.spec_from_file_location("_reference_cutlass_kernels", REFERENCE_GEMM_MODULE)
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        _ref_gemm_kernel = mod.BlackwellGemmKernel()
+    return _ref_gemm_kernel
+
+
 def cpu_step(inputs):
-    """One pass of the CPU restatement over the sample: quantise X and W (C, OpenMP), dequantise,
-    fp32 matmul (torch, all host threads; the reference's CPU GEMM is torch.matmul), bf16 output."""
-    from oracle import mx_oracle as o
+    """One pass of the CPU path over the sample: quantise X and W (the C restatement with OpenMP: the reference has no
+    CPU quantiser), dequantise, then the GEMM stage in fp32 on all host threads through the reference's own CPU module
+    when it is installed (torch.matmul either way), bf16 output."""
     from oracle import mx_ref as c
+    kern = reference_gemm_kernel()
     out = []
     for xb, wb in inputs:
         xc, xs = c.quantize_rowwise(xb, 0)
         wc, ws = c.quantize_rowwise(wb, 0)
         a = torch.from_numpy(c.dequantize(xc, xs))
         b = torch.from_numpy(c.dequantize(wc, ws))
-        y = torch.matmul(a, b.t())
+        y = kern.gemm(a, b.t()) if kern is not None else torch.matmul(a, b.t())
         out.append(y.bfloat16())
     return out
 
@@ -153,9 +194,14 @@ def time_cpu(steps, warmup, rows=CPU_SAMPLE_ROWS):
         cpu_step(inputs)
     dt = (time.perf_counter() - t0) / max(1, steps)
     cores = max(torch.get_num_threads(), c.num_threads())
-    return {"value": total_flops(rows) / dt / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
-            "sample": f"first {rows} of {M_TOKENS} token rows of all four layers (full N and K), "
-                      f"{dt:.2f} s per pass: C/OpenMP quantiser + torch.matmul fp32 on dequantised operands"}, dt
+    ref_gemm = reference_gemm_kernel() is not None
+    return {"value": total_flops(rows) / dt / 1e12, "unit": "TFLOP/s", "cores": cores,
+            "kind": "reference" if ref_gemm else "port",
+            "sample": f"first {rows} of {M_TOKENS} token rows of all four layers (full N and K), {dt:.2f} s per pass: "
+                      "C/OpenMP restatement of the quantiser (the reference has no CPU quantiser) + GEMM stage in fp32 "
+                      "on the dequantised operands through "
+                      + ("the reference's own CPU module deepwell/cutlass_kernels.py (BlackwellGemmKernel.gemm = "
+                         "torch.matmul)" if ref_gemm else "torch.matmul (what the reference's CPU module calls)")}, dt
 
 
 def use_all_host_threads():
@@ -232,6 +278,46 @@ def run_profile_case(args):
     print(json.dumps({"profile_case": args.profile_case, "units": units, "ms_per_launch": e0.elapsed_time(e1) / 3}))
 
 
+def traffic_from_csv(path):
+    """Reads an ncu --csv launch log holding dram__bytes_read.sum, dram__bytes_write.sum and gpu__time_duration.sum of
+    the four GEMM launches of one step (in layer order) and writes bench_gemm_dram_traffic.json, the one place the
+    bench line's `roofline.traffic` comes from."""
+    rows = []
+    with open(path, newline="") as f:
+        lines = [l for l in f if l.startswith('"')]
+    for rec in csv.DictReader(lines):
+        rows.append(rec)
+    per_launch = {}
+    for rec in rows:
+        lid = int(rec["ID"])
+        d = per_launch.setdefault(lid, {"kernel": rec["Kernel Name"], "block": rec.get("Block Size", ""), "grid": rec.get("Grid Size", "")})
+        val = float(rec["Metric Value"].replace(",", ""))
+        unit = rec["Metric Unit"]
+        name = rec["Metric Name"]
+        if name.startswith("dram__bytes"):
+            val *= {"byte": 1.0, "Kbyte": 1e3, "Mbyte": 1e6, "Gbyte": 1e9}.get(unit, 1.0)
+            d["dram_read_bytes" if "read" in name else "dram_write_bytes"] = val
+        elif name.startswith("gpu__time_duration"):
+            val *= {"ns": 1e-3, "us": 1.0, "usecond": 1.0, "ms": 1e3, "msecond": 1e3, "nsecond": 1e-3}.get(unit, 1.0)
+            d["duration_us"] = val
+    launches = [per_launch[k] for k in sorted(per_launch)]
+    if len(launches) != len(LAYERS):
+        raise SystemExit(f"expected {len(LAYERS)} GEMM launches in {path}, found {len(launches)}")
+    out = {"source": "ncu --metrics dram__bytes_read.sum,dram__bytes_write.sum,gpu__time_duration.sum --clock-control none "
+                     "-k regex:mx_gemm on `python bench.py --steps 1 --warmup 3 --serial --e2e-steps 0 --sustained-seconds 0 "
+                     "--no-cpu-baseline --no-extra-legs`, the four GEMM launches of the last step",
+           "M": M_TOKENS, "layers": {}}
+    for (name, k, n), l in zip(LAYERS, launches):
+        alg = M_TOKENS * k + n * k + 2 * M_TOKENS * n
+        out["layers"][name] = {"K": k, "N": n, "kernel": l["kernel"], "block": l["block"], "grid": l["grid"],
+                               "duration_us": l.get("duration_us"), "dram_read_bytes": l["dram_read_bytes"],
+                               "dram_write_bytes": l["dram_write_bytes"], "algorithmic_bytes": alg,
+                               "ratio": (l["dram_read_bytes"] + l["dram_write_bytes"]) / alg}
+    with open(TRAFFIC_JSON, "w") as f:
+        json.dump(out, f, indent=1)
+    print(json.dumps(out))
+
+
 # ----------------------------------------------------------------------------------------------
 # quantise-only sweep: Student-t(3) x 0.5 inputs, K in {128, 1024, 4096, 16384}, 2^20 .. 2^32 elements
 # ----------------------------------------------------------------------------------------------
@@ -245,7 +331,8 @@ def run_quantize_sweep(args):
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)           # larger than L2
     g = torch.Generator(device=dev).manual_seed(4567)
     rows_out = []
-    for log2n in range(20, 33, 2):
+    lo, hi = args.sweep_log2_min, args.sweep_log2_max
+    for log2n in range(lo, hi + 1, 2):
         n = 1 << log2n
         # one buffer per size, re-viewed for every K (values are i.i.d., the shape does not matter to them)
         x_flat = torch.empty(n, dtype=torch.bfloat16, device=dev)
@@ -281,18 +368,91 @@ def run_quantize_sweep(args):
                     times.append(e0.elapsed_time(e1))
                 ms = float(np.median(times))
                 gbs = n * 3.03125 / (ms * 1e-3) / 1e9
+                # the same launch back to back (no flush, no host round trip between launches): what a training step sees
+                b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                b0.record()
+                for _ in range(reps):
+                    run()
+                b1.record()
+                torch.cuda.synchronize(dev)
+                ms_b2b = b0.elapsed_time(b1) / reps
+                gbs_b2b = n * 3.03125 / (ms_b2b * 1e-3) / 1e9
                 rows_out.append({"log2_elements": log2n, "K": k, "direction": name, "us": ms * 1e3, "GBps": gbs,
-                                 "frac_of_measured_copy": gbs / peak, "l2_flushed": small})
+                                 "frac_of_measured_copy": gbs / peak, "l2_flushed": small, "us_back_to_back": ms_b2b * 1e3,
+                                 "GBps_back_to_back": gbs_b2b, "frac_back_to_back": gbs_b2b / peak})
                 print(json.dumps(rows_out[-1]), flush=True)
         del x_flat, codes
     print(json.dumps({"sweep": "quantize", "peak_hbm_gbs": peak, "points": len(rows_out)}))
 
 
 # ----------------------------------------------------------------------------------------------
-# GPU arm
+# vendor comparison: cuBLASLt's block-scaled GEMM (through torch._scaled_mm) alternated with ours
 # ----------------------------------------------------------------------------------------------
+def compare_vendor(dev, shapes, rounds=3, reps=10):
+    """Per shape: `rounds` alternations of (vendor x reps, ours x reps) on the same quantised operands, CUDA events.
+    The vendor kernel reads the same codes and the same tiled E8M0 scale buffers (its scale layout is this one)."""
+    from deepwell_b200 import _native as nv
+    out = {}
+    for name, (M, N, K) in shapes.items():
+        g = torch.Generator(device=dev).manual_seed(M + N + K)
+        x = torch.randn(M, K, device=dev, generator=g).bfloat16()
+        w = (torch.randn(N, K, device=dev, generator=g) * 0.02).bfloat16()
+        xc, xs = nv.quantize(x, nv.DIR_ROW, 0, nv.SF_TILED)
+        wc, ws = nv.quantize(w, nv.DIR_ROW, 0, nv.SF_TILED)
+        del x, w
+        sa, sb = xs.view(torch.float8_e8m0fnu), ws.view(torch.float8_e8m0fnu)
+        y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        f_vendor = lambda: torch._scaled_mm(xc, wc.t(), scale_a=sa, scale_b=sb, out_dtype=torch.bfloat16)
+        f_ours = lambda: nv.gemm(xc, xs, wc, ws, out=y)
+        try:
+            yv = f_vendor()
+        except Exception as e:        # a torch build without the block-scaled path
+            out[name] = {"error": f"vendor kernel unavailable: {type(e).__name__}: {str(e)[:120]}"}
+            continue
+        f_ours()
+        identical = bool(torch.equal(yv, y))
+        del yv
+
+        def timed(fn):
+            for _ in range(2):
+                fn()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize(dev)
+            return e0.elapsed_time(e1) / reps
+
+        flops = 2.0 * M * N * K
+        v, u = [], []
+        for _ in range(rounds):
+            v.append(flops / (timed(f_vendor) * 1e-3) / 1e12)
+            u.append(flops / (timed(f_ours) * 1e-3) / 1e12)
+        out[name] = {"shape": [M, N, K], "vendor_tflops": [round(t, 1) for t in v], "ours_tflops": [round(t, 1) for t in u],
+                     "ours_over_vendor": float(np.median(u) / np.median(v)), "outputs_identical": identical}
+        del xc, xs, wc, ws, y
+    return out
+
+
+def run_compare_vendor(args):
+    from deepwell_b200 import _native as nv
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    nv.load()
+    nv.set_gemm_variant(args.variant)
+    shapes = {name: (M_TOKENS, n, k) for name, k, n in LAYERS}
+    shapes.update({"gpt2_fc": (8192, 3072, 768), "gpt2_proj": (8192, 768, 3072), "square_8192x4096": (8192, 8192, 4096)})
+    sampler = ClockSampler(0)
+    sampler.start()
+    res = compare_vendor(dev, shapes, rounds=5, reps=20)
+    print(json.dumps({"compare": "vendor block-scaled GEMM (torch._scaled_mm) vs dw_mxfp8_gemm, alternated, TFLOP/s",
+                      "shapes": res, "clocks": sampler.stop()}))
+
+
 # ----------------------------------------------------------------------------------------------
-# Secondary workload: the end-to-end deepwell.optimize() training step of a pre-LN decoder
+# Secondary workloads
+# ----------------------------------------------------------------------------------------------
 def build_decoder(vocab, hidden, heads, ffn, layers):
     import torch.nn as nn
     import torch.nn.functional as F
@@ -328,19 +488,16 @@ def build_decoder(vocab, hidden, heads, ffn, layers):
     return Decoder()
 
 
-def run_decoder_step(args):
-    """BASELINE config 5: random-init 12-layer pre-LN decoder (hidden 1024, 16 heads, FFN 4096, vocab 32000), batch 8 x
-    sequence 2048 uniform token ids; every nn.Linear replaced by deepwell.optimize(precision='mxfp8').  One step = ids
-    host->device, forward, cross-entropy, backward, fused AdamW step, loss device->host.  The same model with its
-    bf16 nn.Linear layers is timed beside it.  Prints one JSON line; attention (torch SDPA), LayerNorm, GELU, the loss
-    and the optimizer are PyTorch's own in both arms: only the linear layers differ."""
+def decoder_step_numbers(steps, warmup):
+    """End-to-end optimize() training step: random-init 12-layer pre-LN decoder (hidden 1024, 16 heads, FFN 4096, vocab
+    32000), batch 8 x sequence 2048 uniform token ids; every nn.Linear replaced by deepwell.optimize(precision='mxfp8').
+    One step = ids host->device, forward, cross-entropy, backward, fused AdamW step, loss device->host.  The same
+    model with its bf16 nn.Linear layers is timed beside it.  Attention (torch SDPA), LayerNorm, GELU, the loss and the
+    optimizer are PyTorch's own in both arms: only the linear layers differ."""
     import copy
     import torch.nn.functional as F
     import deepwell_b200 as dw
 
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device (B200); there is no CPU fallback for the product path")
-    torch.cuda.set_device(0)
     vocab, hidden, heads, ffn, layers, batch, seq = 32000, 1024, 16, 4096, 12, 8, 2048
     torch.manual_seed(1234)
     base = build_decoder(vocab, hidden, heads, ffn, layers).cuda().bfloat16()
@@ -348,16 +505,14 @@ def run_decoder_step(args):
     del base
     n_dw = sum(isinstance(m, dw.DWLinear) for m in arms["mxfp8_dwlinear"].modules())
     lin_params = sum(m.weight.numel() for m in arms["mxfp8_dwlinear"].modules() if isinstance(m, dw.DWLinear))
-    ids_host = torch.randint(0, vocab, (args.steps + args.warmup, batch, seq), generator=torch.Generator().manual_seed(7)).pin_memory()
+    ids_host = torch.randint(0, vocab, (steps + warmup, batch, seq), generator=torch.Generator().manual_seed(7)).pin_memory()
     out, losses = {}, {}
-    sampler = ClockSampler(0)
-    sampler.start()
     for name, net in arms.items():
         opt = torch.optim.AdamW(net.parameters(), lr=1e-4, fused=True)
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         cur = []
-        for i in range(args.steps + args.warmup):
-            if i == args.warmup:
+        for i in range(steps + warmup):
+            if i == warmup:
                 torch.cuda.synchronize()
                 ev0.record()
             ids = ids_host[i].cuda(non_blocking=True)
@@ -369,43 +524,231 @@ def run_decoder_step(args):
             cur.append(loss.item())
         ev1.record()
         torch.cuda.synchronize()
-        out[name] = ev0.elapsed_time(ev1) / args.steps
+        out[name] = ev0.elapsed_time(ev1) / steps
         losses[name] = cur
-        del opt
+        del opt, logits, loss
         arms[name] = None
         torch.cuda.empty_cache()
-    clocks = sampler.stop()
     tokens = batch * seq
     ms = out["mxfp8_dwlinear"]
+    return {"workload": "preln_decoder_12x1024_ffn4096_vocab32000_b8_s2048_train_step", "steps": steps, "warmup": warmup,
+            "tokens_per_s": tokens / ms * 1e3, "ms_per_step": ms, "dwlinear_modules": n_dw,
+            "linear_tflop_per_step": 6.0 * lin_params * tokens / 1e12, "optimizer": "AdamW(fused)",
+            "bf16_nn_linear": {"ms_per_step": out["bf16_nn_linear"], "tokens_per_s": tokens / out["bf16_nn_linear"] * 1e3},
+            "speedup_vs_bf16_nn_linear": out["bf16_nn_linear"] / ms,
+            "loss_first_last": {k: [v[0], v[-1]] for k, v in losses.items()},
+            "h2d_bytes_per_step": tokens * 8, "d2h_bytes_per_step": 4}
+
+
+def run_decoder_step(args):
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (B200); there is no CPU fallback for the product path")
+    torch.cuda.set_device(0)
+    sampler = ClockSampler(0)
+    sampler.start()
+    r = decoder_step_numbers(args.steps, args.warmup)
+    clocks = sampler.stop()
     print(json.dumps({
-        "metric": "decoder_train_tokens_per_s", "value": tokens / ms * 1e3, "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "metric": "decoder_train_tokens_per_s", "value": r["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "mxfp8 linears (e4m3+e8m0, fp32 accumulate), bf16 elsewhere", "data": "synthetic",
-        "config": {"workload": "preln_decoder_12x1024_ffn4096_vocab32000_b8_s2048_train_step", "dwlinear_modules": n_dw,
-                   "linear_tflop_per_step": 6.0 * lin_params * tokens / 1e12, "optimizer": "AdamW(fused)",
+        "config": {"workload": r["workload"], "dwlinear_modules": r["dwlinear_modules"],
+                   "linear_tflop_per_step": r["linear_tflop_per_step"], "optimizer": r["optimizer"],
                    "l2": "activations and weights far larger than L2"},
-        "bf16_nn_linear": {"ms_per_step": out["bf16_nn_linear"], "tokens_per_s": tokens / out["bf16_nn_linear"] * 1e3},
-        "speedup_vs_bf16_nn_linear": out["bf16_nn_linear"] / ms,
-        "loss_first_last": {k: [v[0], v[-1]] for k, v in losses.items()},
-        "e2e": {"value": tokens / ms * 1e3, "unit": "tokens/s", "h2d_bytes_per_step": tokens * 8, "d2h_bytes_per_step": 4,
+        "bf16_nn_linear": r["bf16_nn_linear"], "speedup_vs_bf16_nn_linear": r["speedup_vs_bf16_nn_linear"],
+        "loss_first_last": r["loss_first_last"],
+        "e2e": {"value": r["tokens_per_s"], "unit": "tokens/s", "h2d_bytes_per_step": r["h2d_bytes_per_step"],
+                "d2h_bytes_per_step": r["d2h_bytes_per_step"],
                 "api": "deepwell_b200.optimize(model, precision='mxfp8'); ids host->device and loss.item() every step"},
         "clocks": clocks}))
 
 
+def gpt2_mlp_numbers(reps=30):
+    """GPT-2-small MLP linears, forward + backward, 8 x 1024 = 8192 tokens: 768 -> 3072 and 3072 -> 768, bf16 weights
+    N(0,0.02), activations and output gradients N(0,1).  DWLinear (three MXFP8 GEMMs + the quantisers per layer)
+    beside bf16 nn.Linear, microseconds per forward+backward, CUDA events over `reps` iterations after warm-up."""
+    import torch.nn as nn
+    import deepwell_b200 as dw
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator(device=dev).manual_seed(2345)
+    res = {}
+    for name, k, n in (("fc_768_3072", 768, 3072), ("proj_3072_768", 3072, 768)):
+        lin = nn.Linear(k, n, bias=True).to(dev).bfloat16()
+        with torch.no_grad():
+            lin.weight.copy_((torch.randn(n, k, device=dev, generator=g) * 0.02).bfloat16())
+        mx = dw.DWLinear.from_linear(lin)
+        x = torch.randn(8192, k, device=dev, generator=g).bfloat16().requires_grad_(True)
+        gy = torch.randn(8192, n, device=dev, generator=g).bfloat16()
+
+        def fb(layer):
+            x.grad = None
+            layer.weight.grad = None
+            layer.bias.grad = None
+            layer(x).backward(gy)
+
+        times = {}
+        for arm, layer in (("bf16_nn_linear_us", lin), ("mxfp8_dwlinear_us", mx)):
+            for _ in range(5):
+                fb(layer)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                fb(layer)
+            e1.record()
+            torch.cuda.synchronize(dev)
+            times[arm] = e0.elapsed_time(e1) / reps * 1e3
+        times["speedup_vs_bf16"] = times["bf16_nn_linear_us"] / times["mxfp8_dwlinear_us"]
+        times["gflop_fwd_bwd"] = 6.0 * 8192 * k * n / 1e9
+        res[name] = times
+    res["tokens"] = 8192
+    res["note"] = "forward + backward of one layer, eager (one Python->C++ call per direction), inputs resident in HBM"
+    return res
+
+
+# ----------------------------------------------------------------------------------------------
+# N > 1: the sharded modules under NCCL, checked against the unsharded layer
+# ----------------------------------------------------------------------------------------------
+def sharded_leg(dev, rank, world):
+    """ColumnParallelDWLinear (QKV 4096 -> 6144, gather_output) and RowParallelDWLinear (down 14336 -> 4096, all-reduce and
+    reduce-scatter) forward + backward on `world` GPUs under NCCL against the unsharded DWLinear computed on every rank
+    from the same seeded tensors.  Y of the column-parallel layer must be bit-equal (same kernel, same order over K);
+    gradients and the row-parallel output are sums of per-rank bf16 partials and are held to the GEMM tolerance
+    |got - ref| <= 1e-2 * max(|ref|, mean|ref|) on 99.9 % of the elements and 4e-2 everywhere.  Also times the
+    column-parallel forward with and without the gather, and the row-parallel forward with its reduction."""
+    import torch.distributed as dist
+    import deepwell_b200 as dw
+    from deepwell_b200.sharded import ColumnParallelDWLinear, RowParallelDWLinear
+
+    m = 8192
+    res = {"tokens": m, "world": world}
+
+    def close(got, ref, what):
+        got, ref = got.float(), ref.float()
+        floor = ref.abs().mean()
+        err = (got - ref).abs() / torch.maximum(ref.abs(), floor)
+        frac_ok = float((err <= 1e-2).float().mean())
+        worst = float(err.max())
+        res[what + "_max_rel_err"] = worst
+        return frac_ok >= 0.999 and worst <= 4e-2 and not bool(torch.isnan(got).any())
+
+    def timed(fn, reps=10):
+        for _ in range(3):
+            fn()
+        dist.barrier()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        t = torch.tensor([e0.elapsed_time(e1) / reps * 1e3], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    g = torch.Generator(device=dev).manual_seed(777)          # same seed on every rank: replicated tensors
+    ok = True
+    # ---- column-parallel: QKV ----
+    k, n = 4096, 6144
+    x = torch.randn(m, k, device=dev, generator=g).bfloat16()
+    w = (torch.randn(n, k, device=dev, generator=g) * 0.02).bfloat16()
+    b = torch.randn(n, device=dev, generator=g).bfloat16()
+    gy = torch.randn(m, n, device=dev, generator=g).bfloat16()
+    full = dw.DWLinear(k, n, bias=True, device=dev, dtype=torch.bfloat16)
+    with torch.no_grad():
+        full.weight.copy_(w)
+        full.bias.copy_(b)
+    xr = x.clone().requires_grad_(True)
+    y_ref = full(xr)
+    y_ref.backward(gy)
+    col = ColumnParallelDWLinear(k, n, bias=True, gather_output=True, device=dev, dtype=torch.bfloat16)
+    col.load_full_weight(w, b)
+    xs = x.clone().requires_grad_(True)
+    y = col(xs)
+    y.backward(gy)
+    torch.cuda.synchronize(dev)
+    bit_equal = bool(torch.equal(y.view(torch.int16), y_ref.view(torch.int16)))
+    res["column_parallel_y_bit_equal"] = bit_equal
+    ok &= bit_equal
+    ok &= close(xs.grad, xr.grad, "column_parallel_dx")
+    dw_equal = bool(torch.equal(col.local.weight.grad.view(torch.int16), full.weight.grad[col.n0:col.n1].view(torch.int16)))
+    res["column_parallel_dw_bit_equal"] = dw_equal
+    ok &= dw_equal
+    ok &= close(col.local.bias.grad, full.bias.grad[col.n0:col.n1], "column_parallel_db")
+    nogather = ColumnParallelDWLinear(k, n, bias=True, gather_output=False, device=dev, dtype=torch.bfloat16)
+    nogather.load_full_weight(w, b)
+    blocked = ColumnParallelDWLinear(k, n, bias=True, gather_output=True, blocked_output=True, device=dev, dtype=torch.bfloat16)
+    blocked.load_full_weight(w, b)
+    with torch.no_grad():
+        res["qkv_fwd_us_unsharded"] = timed(lambda: full(x))
+        res["qkv_fwd_us_no_gather"] = timed(lambda: nogather(x))
+        res["qkv_fwd_us_with_gather"] = timed(lambda: col(x))
+        res["qkv_fwd_us_with_gather_blocked_layout"] = timed(lambda: blocked(x))
+    res["gather_bytes_per_rank"] = m * (n // world) * 2 * (world - 1)
+    del full, col, nogather, blocked, x, w, b, gy, xr, xs, y, y_ref
+    # ---- row-parallel: down projection, fed by this rank's slice of the features ----
+    k, n = 14336, 4096
+    x = torch.randn(m, k, device=dev, generator=g).bfloat16()
+    w = (torch.randn(n, k, device=dev, generator=g) * 0.02).bfloat16()
+    gy = torch.randn(m, n, device=dev, generator=g).bfloat16()
+    full = dw.DWLinear(k, n, bias=False, device=dev, dtype=torch.bfloat16)
+    with torch.no_grad():
+        full.weight.copy_(w)
+    xr = x.clone().requires_grad_(True)
+    y_ref = full(xr)
+    y_ref.backward(gy)
+    row = RowParallelDWLinear(k, n, bias=False, input_is_parallel=True, device=dev, dtype=torch.bfloat16)
+    row.load_full_weight(w)
+    xl = x[:, row.k0:row.k1].clone().requires_grad_(True)
+    y = row(xl)
+    y.backward(gy)
+    torch.cuda.synchronize(dev)
+    ok &= close(y, y_ref, "row_parallel_y")
+    ok &= close(xl.grad, xr.grad[:, row.k0:row.k1], "row_parallel_dx")
+    ok &= close(row.local.weight.grad, full.weight.grad[:, row.k0:row.k1], "row_parallel_dw")
+    rs = RowParallelDWLinear(k, n, bias=False, input_is_parallel=True, scatter_output=True, device=dev, dtype=torch.bfloat16)
+    rs.load_full_weight(w)
+    with torch.no_grad():
+        y_rs = rs(xl.detach())
+        ok &= close(y_rs, y_ref[rank * (m // world):(rank + 1) * (m // world)], "row_parallel_reduce_scatter_y")
+        xd = xl.detach()
+        res["down_fwd_us_unsharded"] = timed(lambda: full(x))
+        res["down_fwd_us_all_reduce"] = timed(lambda: row(xd))
+        res["down_fwd_us_reduce_scatter"] = timed(lambda: rs(xd))
+    flag = torch.tensor([1 if ok else 0], device=dev, dtype=torch.int32)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    res["parity"] = "ok" if int(flag.item()) == 1 else "MISMATCH"
+    return res
+
+
+# ----------------------------------------------------------------------------------------------
+# GPU arm
+# ----------------------------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="deepwell_b200", choices=["deepwell_b200", "reference"])
-    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--e2e-steps", type=int, default=10)
+    ap.add_argument("--sustained-seconds", type=float, default=2.5,
+                    help="length of the sustained leg (the same step repeated; 0 switches it off)")
     ap.add_argument("--variant", type=int, default=0, help="GEMM kernel variant (0 = automatic)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra-legs", action="store_true",
+                    help="skip the secondary legs (vendor comparison, GPT-2 MLP, decoder step, sharded parity, gather)")
     ap.add_argument("--sweep-quantize", action="store_true",
                     help="quantise-only bandwidth sweep (K in {128,1024,4096,16384}, 2^20..2^32 elements, both directions)")
+    ap.add_argument("--sweep-log2-min", type=int, default=20)
+    ap.add_argument("--sweep-log2-max", type=int, default=32)
+    ap.add_argument("--compare-vendor", action="store_true",
+                    help="alternate the vendor block-scaled GEMM (torch._scaled_mm) with dw_mxfp8_gemm on the workload's shapes")
+    ap.add_argument("--traffic-from-csv", default=None, help="ncu CSV of the GEMM launches -> bench_gemm_dram_traffic.json")
     ap.add_argument("--emulate-world", type=int, default=0,
                     help="tuning aid: on one GPU, run the shard sizes rank 0 would get in a job of this many GPUs")
     ap.add_argument("--serial", action="store_true", help="quantise and GEMM on one stream (no overlap between layers)")
+    ap.add_argument("--quant-persistent", action="store_true",
+                    help="second-stream quantiser launches as persistent grids (default: DW_QUANT_BACKGROUND, short-lived blocks)")
     ap.add_argument("--profile-case", default=None, choices=["gemm", "quant_row", "quant_both", "quant_col"],
                     help="run a few launches of one kernel on a small case (for an ncu capture) and exit")
     ap.add_argument("--workload", default="linears", choices=["linears", "decoder_step"],
@@ -419,11 +762,18 @@ def main():
     if args.impl == "reference":
         run_reference_arm(args, rank)
         return
+    if args.traffic_from_csv:
+        traffic_from_csv(args.traffic_from_csv)
+        return
     if args.profile_case:
         run_profile_case(args)
         return
     if args.sweep_quantize:
         run_quantize_sweep(args)
+        return
+    if args.compare_vendor:
+        if rank == 0:
+            run_compare_vendor(args)
         return
     if args.workload == "decoder_step":
         if rank == 0:
@@ -464,29 +814,36 @@ def main():
                        "ws": u8(nv.scale_bytes(nl, k, nv.SF_TILED)),
                        "y": torch.empty(M_TOKENS, nl, dtype=torch.bfloat16, device=dev)})
     status = nv.status_word(dev)
-    stream = torch.cuda.current_stream(dev)          # GEMMs (and the step timer) run here
+    # GEMMs (and the step timer) run on `stream`.  The four layers are independent problems, so the (HBM-bound)
+    # quantisation of layer i+1 runs on a second, lower-priority stream underneath the (tensor-bound) GEMM of layer i.
+    # --serial keeps everything on one stream.
+    lo_pri, hi_pri = torch.cuda.Stream.priority_range()
+    stream = torch.cuda.Stream(dev, priority=hi_pri)
+    torch.cuda.set_stream(stream)
     st = stream.cuda_stream
-    # The four layers are independent problems, so the (HBM-bound) quantisation of layer i+1 runs on a
-    # second stream underneath the (tensor-bound) GEMM of layer i.  --serial keeps everything on one stream.
-    qstream = stream if args.serial else torch.cuda.Stream(dev)
+    qstream = stream if args.serial else torch.cuda.Stream(dev, priority=lo_pri)
     sq = qstream.cuda_stream
     for l in layers:
         l["quantised"] = torch.cuda.Event()            # operands of this layer are ready
         l["consumed"] = torch.cuda.Event()             # the GEMM that read them has finished
     gemm_events = []
 
-    def step(record: bool):
+    qflags = nv.QUANT_BACKGROUND if (qstream is not stream and not args.quant_persistent) else 0
+
+    def step(record: bool, after_gemm=None):
         launches = 0
         for l in layers:
             if qstream is not stream:
                 qstream.wait_event(l["consumed"])      # do not overwrite operands a GEMM may still read
-            nv.check(L.dw_mxfp8_quantize(l["x"].data_ptr(), l["xc"].data_ptr(), l["xs"].data_ptr(), M_TOKENS, l["k"],
-                                         nv.DIR_ROW, nv.RULE_OCP_FLOOR, nv.SF_TILED, sq), "quantize X")
-            nv.check(L.dw_mxfp8_quantize(l["w"].data_ptr(), l["wc"].data_ptr(), l["ws"].data_ptr(), l["n"], l["k"],
-                                         nv.DIR_ROW, nv.RULE_OCP_FLOOR, nv.SF_TILED, sq), "quantize W")
+            nv.check(L.dw_mxfp8_quantize_ex(l["x"].data_ptr(), l["xc"].data_ptr(), l["xs"].data_ptr(), M_TOKENS, l["k"],
+                                            nv.DIR_ROW, nv.RULE_OCP_FLOOR, nv.SF_TILED, qflags, sq), "quantize X")
+            nv.check(L.dw_mxfp8_quantize_ex(l["w"].data_ptr(), l["wc"].data_ptr(), l["ws"].data_ptr(), l["n"], l["k"],
+                                            nv.DIR_ROW, nv.RULE_OCP_FLOOR, nv.SF_TILED, qflags, sq), "quantize W")
             if qstream is not stream:
                 l["quantised"].record(qstream)
                 stream.wait_event(l["quantised"])
+            if after_gemm is not None and "gather_done" in l:
+                stream.wait_event(l["gather_done"])    # the previous step's all-gather has read this layer's Y
             if record:
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record(stream)
@@ -498,6 +855,8 @@ def main():
                 gemm_events.append((e0, e1))
             if qstream is not stream:
                 l["consumed"].record(stream)
+            if after_gemm is not None:
+                after_gemm(l)
             launches += 3
         return launches
 
@@ -506,51 +865,69 @@ def main():
             dist.barrier()
         torch.cuda.synchronize(dev)
 
+    def max_over_ranks(v):
+        if world > 1:
+            t = torch.tensor([v], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+        return v
+
+    def timed_steps(n_steps, record, after_gemm=None, finish=None):
+        """n_steps steps bracketed by barrier + synchronize, CUDA events on the GEMM stream, max over ranks (ms)."""
+        barrier()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record(stream)
+        qstream.wait_event(t0)                        # nothing of the timed steps starts before the timer
+        n_launch = 0
+        for _ in range(n_steps):
+            n_launch += step(record, after_gemm)
+        if finish is not None:
+            finish()
+        t1.record(stream)                             # the last GEMM depends on every quantisation before it
+        barrier()
+        return max_over_ranks(t0.elapsed_time(t1)), n_launch
+
     for _ in range(warmup):
         step(False)
     nv.check_status(dev)
 
     sampler = ClockSampler(local_rank)
-    barrier()
     sampler.start()
-    t_start, t_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t_start.record(stream)
-    qstream.wait_event(t_start)                       # nothing of the timed steps starts before the timer
-    launches = 0
-    for _ in range(args.steps):
-        launches += step(True)
-    t_stop.record(stream)                             # the last GEMM depends on every quantisation before it
-    barrier()
+    elapsed_ms, launches = timed_steps(args.steps, True)
     clocks = sampler.stop()
     nv.check_status(dev)
-    elapsed_ms = t_start.elapsed_time(t_stop)
-    if world > 1:
-        t = torch.tensor([elapsed_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms = float(t.item())
     ms_per_step = elapsed_ms / args.steps
     value = total_flops() / (ms_per_step * 1e-3) / 1e12
 
     # ---- roofline of the dominant kernel (GEMM), live CUDA-event durations of this rank ----
     gemm_ms = sum(a.elapsed_time(b) for a, b in gemm_events)
-    gemm_flops = args.steps * sum(2.0 * M_TOKENS * l["n"] * l["k"] for l in layers)
-    achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12
+    gemm_flops_step = sum(2.0 * M_TOKENS * l["n"] * l["k"] for l in layers)
+    achieved = args.steps * gemm_flops_step / (gemm_ms * 1e-3) / 1e12
     peaks = measured_peaks()
-    peak = 2.0 * peaks["bf16_tflops_sustained"]
+    peak_burst, peak_sustained = 2.0 * peaks["bf16_tflops"], 2.0 * peaks["bf16_tflops_sustained"]
+    # The denominator that fits the run: a timed region shorter than a second with the SM clock at its maximum is a
+    # burst measurement (the power cap has not bitten yet), anything else is held to the sustained figure.
+    at_max_clock = clocks["sm_mhz"] is None or clocks["sm_max_mhz"] is None or clocks["sm_mhz"] >= 0.95 * clocks["sm_max_mhz"]
+    burst_run = elapsed_ms < 1000.0 and at_max_clock
+    peak = peak_burst if burst_run else peak_sustained
+    traffic, traffic_info = gemm_dram_traffic()
     roofline = {"bound": "tensor", "kernel": "mx_gemm_kernel", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                "frac": achieved / peak, "traffic": GEMM_DRAM_TRAFFIC_BYTES if world == 1 else None,
-                "traffic_note": "mean DRAM bytes per GEMM launch (ncu, N = 1); algorithmic mean A + B + D = 5.16e8",
-                "peak_basis": f"2 x bf16_tflops_sustained of {peaks['source']} MEASURED_PEAKS (MXFP8 issues at twice the "
-                              "bf16 tensor rate); nominal dense MXFP8 is 4500",
+                "frac": achieved / peak, "frac_of_burst": achieved / peak_burst, "frac_of_sustained": achieved / peak_sustained,
+                "peak_burst": peak_burst, "peak_sustained": peak_sustained,
+                "peak_choice": ("burst" if burst_run else "sustained") + f": timed region {elapsed_ms:.0f} ms, median SM clock "
+                               f"{clocks['sm_mhz']} of {clocks['sm_max_mhz']} MHz",
+                "peak_basis": f"2 x the bf16 dense rate of {peaks['source']} MEASURED_PEAKS (MXFP8 issues at twice the bf16 "
+                              "tensor rate): burst for a sub-second region at full clock, else sustained; nominal dense "
+                              "MXFP8 is 4500",
                 "frac_of_nominal_4500": achieved / NOMINAL_MXFP8_TFLOPS,
+                "traffic": traffic if world == 1 else None,
+                "traffic_note": "mean DRAM bytes per GEMM launch (ncu, N = 1, bench_gemm_dram_traffic.json); algorithmic mean "
+                                "A + B + D = 5.16e8",
                 "gemm_ms_per_step": gemm_ms / args.steps, "launches_timed": len(gemm_events)}
 
-    # the same GEMM launches with nothing else on the GPU (in the timed region the next layer's
-    # quantisation runs underneath them and takes its share of power and issue slots)
-    if not args.serial:
-        torch.cuda.synchronize(dev)
-        alone = []
-        for _ in range(3):
+    def gemm_only(reps):
+        ev = []
+        for _ in range(reps):
             for l in layers:
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record(stream)
@@ -558,14 +935,37 @@ def main():
                                          l["y"].data_ptr(), None, M_TOKENS, l["n"], l["k"], 1.0, 0.0, None, 0,
                                          status.data_ptr(), st), "gemm")
                 e1.record(stream)
-                alone.append((e0, e1))
+                ev.append((e0, e1))
         torch.cuda.synchronize(dev)
-        alone_ms = sum(a.elapsed_time(b) for a, b in alone) / 3
-        alone_tf = sum(2.0 * M_TOKENS * l["n"] * l["k"] for l in layers) / (alone_ms * 1e-3) / 1e12
+        return sum(a.elapsed_time(b) for a, b in ev) / reps
+
+    # the same GEMM launches with nothing else on the GPU (in the timed region the next layer's
+    # quantisation runs underneath them and takes its share of power and issue slots)
+    if not args.serial:
+        torch.cuda.synchronize(dev)
+        alone_ms = gemm_only(3)
+        alone_tf = gemm_flops_step / (alone_ms * 1e-3) / 1e12
         roofline["achieved_alone"] = alone_tf
-        roofline["frac_alone"] = alone_tf / peak
+        roofline["frac_alone_of_burst"] = alone_tf / peak_burst
         roofline["note"] = ("achieved/frac: live in the timed region, where the next layer's quantiser shares the GPU; "
                             "achieved_alone: the same four launches back to back with nothing else running")
+
+    # ---- sustained leg: the same step for >= args.sustained_seconds, clocks sampled throughout ----
+    sustained = None
+    if args.sustained_seconds > 0:
+        n_sus = max(args.steps, int(math.ceil(args.sustained_seconds * 1e3 / ms_per_step)))
+        sus_sampler = ClockSampler(local_rank)
+        sus_sampler.start()
+        sus_ms, _ = timed_steps(n_sus, False)
+        sus_clocks = sus_sampler.stop()
+        sus_step = sus_ms / n_sus
+        sus_value = total_flops() / (sus_step * 1e-3) / 1e12
+        sustained = {"value": sus_value, "unit": "TFLOP/s", "ms_per_step": sus_step, "steps": n_sus, "seconds": sus_ms / 1e3,
+                     "sm_mhz_median": sus_clocks["sm_mhz"], "sm_max_mhz": sus_clocks["sm_max_mhz"],
+                     "reasons": sus_clocks["reasons"], "clock_samples": sus_clocks["samples"],
+                     "frac_of_sustained_peak": sus_value / peak_sustained, "frac_of_burst_peak": sus_value / peak_burst,
+                     "note": "whole step (quantisers + GEMMs) over 2 x measured sustained / burst bf16 rate"}
+        nv.check_status(dev)
 
     # ---- quantiser bandwidth (second kernel of the path), timed alone on the largest activation ----
     big = max(layers, key=lambda l: l["k"])
@@ -582,6 +982,40 @@ def main():
     roofline_q = {"bound": "hbm", "kernel": "mx_quant_row_kernel", "achieved": q_gbs, "peak": peaks["hbm_gbs"],
                   "unit": "GB/s", "frac": q_gbs / peaks["hbm_gbs"], "frac_of_nominal_8000": q_gbs / 8000.0,
                   "shape": [M_TOKENS, big["k"]], "bytes_per_element": 3.03125}
+
+    # ---- N > 1: the same step with every layer's output all-gathered along N over NVLink (NCCL, its own stream) ----
+    with_gather = None
+    if world > 1 and not args.no_extra_legs:
+        try:
+            cstream = torch.cuda.Stream(dev)
+            for l in layers:
+                l["gathered"] = torch.empty(world, M_TOKENS, l["n"], dtype=torch.bfloat16, device=dev)   # rank-major blocks
+                l["gemm_done"] = torch.cuda.Event()
+
+            def gather_after(l):
+                l["gemm_done"].record(stream)
+                cstream.wait_event(l["gemm_done"])
+                with torch.cuda.stream(cstream):
+                    dist.all_gather_into_tensor(l["gathered"].view(world * M_TOKENS, l["n"]), l["y"])
+                    l["gather_done"] = torch.cuda.Event()
+                    l["gather_done"].record(cstream)
+
+            even = all(n % (32 * world) == 0 for _, _, n in LAYERS)
+            if even:
+                for _ in range(2):
+                    step(False, gather_after)
+                stream.wait_stream(cstream)
+                g_ms, _ = timed_steps(args.steps, False, gather_after, finish=lambda: stream.wait_stream(cstream))
+                g_step = g_ms / args.steps
+                with_gather = {"value": total_flops() / (g_step * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": g_step,
+                               "gather_bytes_per_rank_per_step": int(sum(M_TOKENS * l["n"] * 2 * (world - 1) for l in layers)),
+                               "note": "each GEMM's output shard all-gathered (NCCL all_gather_into_tensor on its own stream, "
+                                       "overlapping the next layer's GEMM); without the gather: `value`"}
+            for l in layers:
+                del l["gathered"]
+            nv.check_status(dev)
+        except Exception as e:
+            with_gather = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
 
     # ---- end to end through the public API with host buffers ----
     e2e = None
@@ -632,26 +1066,47 @@ def main():
                 outs.append(y)
             torch.cuda.synchronize(dev)
 
-        e2e_step()
+        for _ in range(2):
+            e2e_step()
         barrier()
         t0 = time.perf_counter()
         for _ in range(args.e2e_steps):
             e2e_step()
         barrier()
-        dt = (time.perf_counter() - t0) / args.e2e_steps
-        if world > 1:
-            t = torch.tensor([dt], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            dt = float(t.item())
+        dt = max_over_ranks((time.perf_counter() - t0) / args.e2e_steps)
         e2e = {"value": total_flops() / dt / 1e12, "unit": "TFLOP/s",
                # whole-job bytes per step: every row of every X crosses PCIe once (N > 1: each rank uploads its
                # slice, NVLink replicates it), every rank downloads its shard of every Y
                "h2d_bytes_per_step": int(sum(hx.numel() * 2 for hx in host_x)) * (1 if even_rows or world == 1 else world),
                "d2h_bytes_per_step": int(sum(hy.numel() * 2 for hy in host_y)) * world, "ms_per_step": dt * 1e3,
+               "steps": args.e2e_steps, "warmup": 2,
                "api": "deepwell_b200.cutlass_kernels.BlackwellGemmKernel.gemm, pinned host X in, pinned host Y out, "
                       "copies on their own streams" + ("; X uploaded as 1/N row slices and all-gathered over NVLink"
                                                        if even_rows else "")}
         nv.check_status(dev)
+        del host_x, host_y, dev_x, kernels
+
+    # ---- secondary legs ----
+    extra = {}
+    if not args.no_extra_legs and not args.emulate_world:
+        if world > 1:
+            try:
+                extra["sharded"] = sharded_leg(dev, rank, world)
+            except Exception as e:
+                extra["sharded"] = {"parity": "not run", "error": f"{type(e).__name__}: {str(e)[:300]}"}
+            extra["sharded_parity"] = extra["sharded"].get("parity")
+        elif rank == 0:
+            for key, fn in (("vendor_gemm", lambda: compare_vendor(dev, {n: (M_TOKENS, nn, k) for n, k, nn in LAYERS})),
+                            ("gpt2_mlp", gpt2_mlp_numbers),
+                            ("decoder_step", lambda: decoder_step_numbers(steps=5, warmup=3))):
+                try:
+                    for l in layers:                      # the headline tensors are no longer needed
+                        l.pop("y", None)
+                    extra[key] = fn()
+                    nv.check_status(dev)
+                except Exception as e:
+                    extra[key] = {"error": f"{type(e).__name__}: {str(e)[:300]}"}
+                torch.cuda.empty_cache()
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -659,21 +1114,22 @@ def main():
         cpu_baseline, _ = time_cpu(steps=2, warmup=1)
 
     if rank == 0:
-        bytes_step = sum(l["x"].numel() * 2 + l["w"].numel() * 2 + l["y"].numel() * 2 for l in layers)
+        bytes_step = sum(l["x"].numel() * 2 + l["w"].numel() * 2 + M_TOKENS * l["n"] * 2 for l in layers)
         line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
                 "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "mxfp8(e4m3+e8m0), fp32 accumulate, bf16 out", "data": "synthetic",
                 "config": {"workload": WORKLOAD, "M": M_TOKENS, "layers": {n: [k, nn] for n, k, nn in LAYERS},
                            "parallelism": f"N-sharded x{world}, X replicated, no data-path collective",
                            "step": "per layer: quantise X, quantise W shard, block-scaled GEMM"
-                                   + ("" if args.serial else "; quantisation of the next layer on a second stream"),
+                                   + ("" if args.serial else "; quantisation of the next layer on a second, lower-priority stream"
+                                      + ("" if args.quant_persistent else " as short-lived thread blocks (DW_QUANT_BACKGROUND)")),
                            "l2": f"inputs larger than L2: {bytes_step / 1e9:.2f} GB touched per step per GPU",
                            "gemm_variant": args.variant,
                            **({"emulated_world": args.emulate_world,
                                "note": "TUNING RUN: one rank's shard on one GPU; value is not a job throughput"}
                               if args.emulate_world else {})},
-                "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roofline,
-                "roofline_quantize": roofline_q, "cpu_baseline": cpu_baseline}
+                "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roofline, "sustained": sustained,
+                "roofline_quantize": roofline_q, "with_gather": with_gather, **extra, "cpu_baseline": cpu_baseline}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -27,6 +27,7 @@ DW_OK = 0
 DIR_ROW, DIR_COL_T, DIR_COL = 0, 1, 2
 RULE_OCP_FLOOR, RULE_REF_CEIL = 0, 1
 SF_FLAT, SF_TILED = 0, 1
+QUANT_BACKGROUND = 1
 
 DIRECTIONS = {"row": DIR_ROW, "col": DIR_COL_T, "col_t": DIR_COL_T, "col_inplace": DIR_COL}
 RULES = {"ocp_floor": RULE_OCP_FLOOR, "ref_ceil": RULE_REF_CEIL}
@@ -38,7 +39,8 @@ ABI_SYMBOLS = (
     "dw_mxfp8_gemm_workspace", "dw_mxfp8_check_status", "dw_mxfp8_gemm_set_variant",
     "dw_mxfp8_gemm_set_timing_buffer", "dw_mxfp8_gemm_splitk_static", "dw_mxfp8_gemm_fused",
     "dw_mxfp8_colsum_workspace", "dw_mxfp8_quantize_both_colsum", "dw_mxfp8_gemm_grouped",
-    "dw_mxfp8_update_amax_history",
+    "dw_mxfp8_update_amax_history", "dw_mxfp8_gemm_planned", "dw_mxfp8_gemm_workspace_planned",
+    "dw_mxfp8_selftest_bounded_wait", "dw_mxfp8_debug_fake_device", "dw_mxfp8_debug_counter", "dw_mxfp8_quantize_ex",
 )
 
 _lib = None
@@ -70,6 +72,7 @@ def load() -> ctypes.CDLL:
     L.dw_mxfp8_scale_bytes.argtypes = [i64, i64, i32]
     L.dw_mxfp8_scale_bytes.restype = sz
     L.dw_mxfp8_quantize.argtypes = [p, p, p, i64, i64, i32, i32, i32, p]
+    L.dw_mxfp8_quantize_ex.argtypes = [p, p, p, i64, i64, i32, i32, i32, i32, p]
     L.dw_mxfp8_quantize_both.argtypes = [p, p, p, p, p, i64, i64, i32, i32, p]
     L.dw_mxfp8_dequantize.argtypes = [p, p, p, i64, i64, i32, p]
     L.dw_mxfp8_update_amax_history.argtypes = [p, p, i32, i64, p]
@@ -85,6 +88,13 @@ def load() -> ctypes.CDLL:
     L.dw_mxfp8_gemm_fused.argtypes = [p, p, p, p, p, p, i64, i64, i64, f32, f32, i32, p, p, i32, p, p]
     L.dw_mxfp8_gemm_grouped.argtypes = [p, p, p, p, p, p, i64, i64, i64, i32, i32, f32, p, p]
     L.dw_mxfp8_gemm_splitk_static.argtypes = [p, p, p, p, p, p, i64, i64, i64, f32, f32, i32, p, p]
+    L.dw_mxfp8_gemm_planned.argtypes = [p, p, p, p, p, p, i64, i64, i64, f32, f32, p, sz, i32, p, p]
+    L.dw_mxfp8_gemm_workspace_planned.argtypes = [i64, i64, i64, i32]
+    L.dw_mxfp8_gemm_workspace_planned.restype = sz
+    L.dw_mxfp8_selftest_bounded_wait.argtypes = [ctypes.c_longlong, p, p]
+    L.dw_mxfp8_debug_fake_device.argtypes = [i32, i32]
+    L.dw_mxfp8_debug_counter.argtypes = [i32]
+    L.dw_mxfp8_debug_counter.restype = ctypes.c_longlong
     _lib = L
     return L
 
@@ -206,11 +216,19 @@ def status_word(device) -> torch.Tensor:
     return w
 
 
+def plan_word(variant: int = 0, group_m: int = 0, splits: int = 0, direct_stores: bool = False) -> int:
+    """The plan word of dw_mxfp8_gemm_planned / dw_mxfp8_gemm_set_variant: kernel variant (0 = chosen per problem),
+    row tiles per raster band, split-K count, per-thread instead of TMA stores."""
+    return int(variant) | (int(group_m) << 8) | (int(splits) << 16) | (int(bool(direct_stores)) << 24)
+
+
 def gemm(a_codes: torch.Tensor, a_sf: torch.Tensor, b_codes: torch.Tensor, b_sf: torch.Tensor,
          out: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None, alpha: float = 1.0,
-         beta: float = 0.0) -> torch.Tensor:
-    """D[M,N] = alpha * A[M,K] . B[N,K]^T + beta * D + bias; operands as produced by quantize(..., SF_TILED)."""
-    return ext().gemm(a_codes, a_sf, b_codes, b_sf, out, bias, float(alpha), float(beta), status_word(a_codes.device))
+         beta: float = 0.0, plan: Optional[int] = None) -> torch.Tensor:
+    """D[M,N] = alpha * A[M,K] . B[N,K]^T + beta * D + bias; operands as produced by quantize(..., SF_TILED).
+    plan: this call's own plan word (plan_word(...)); None = the process default."""
+    return ext().gemm(a_codes, a_sf, b_codes, b_sf, out, bias, float(alpha), float(beta), status_word(a_codes.device),
+                      -1 if plan is None else int(plan))
 
 
 def gemm_grouped(a_codes: torch.Tensor, a_sf: torch.Tensor, b_codes: torch.Tensor, b_sf: torch.Tensor,
@@ -276,6 +294,6 @@ def check_status(device=None) -> None:
 
 
 def set_gemm_variant(v: int, group_m: int = 0, splits: int = 0, direct_stores: bool = False) -> None:
-    """Kernel variant (0 = automatic), raster band height, split-K count and output store path for later GEMMs."""
-    check(load().dw_mxfp8_gemm_set_variant(int(v) | (int(group_m) << 8) | (int(splits) << 16) | (int(bool(direct_stores)) << 24)),
-          "dw_mxfp8_gemm_set_variant")
+    """PROCESS default of the plan word, for calls that pass none (a switch for benchmarks and tests; library code
+    passes `plan=` per call instead)."""
+    check(load().dw_mxfp8_gemm_set_variant(plan_word(v, group_m, splits, direct_stores)), "dw_mxfp8_gemm_set_variant")

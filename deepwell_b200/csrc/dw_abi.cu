@@ -1,9 +1,49 @@
-// Library-level entry points of the C ABI (probes and error strings).
+// Library-level entry points of the C ABI (probes and error strings) and the per-device property cache.
 #include <cuda_runtime.h>
 
-#include "../../include/dw_mxfp8.h"
+#include <atomic>
+#include <mutex>
 
-extern "C" DW_API int dw_mxfp8_abi_version(void) { return 1; }
+#include "dw_common.cuh"
+
+namespace dw {
+
+// dw_mxfp8_debug_fake_device: what current_device() reports instead of asking the runtime (cc_major < 0: off).
+static std::atomic<int> g_fake_cc{-1}, g_fake_sms{0};
+
+int current_device(DeviceInfo* out) {
+    const int fake = g_fake_cc.load(std::memory_order_relaxed);
+    if (fake >= 0) {
+        const int sms = g_fake_sms.load(std::memory_order_relaxed);
+        *out = DeviceInfo{0, sms > 0 ? sms : 148, fake};
+        return fake == 10 ? DW_OK : DW_ERR_ARCH;
+    }
+    static std::mutex mu;
+    static DeviceInfo cache[kMaxDevices];
+    static bool have[kMaxDevices] = {};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        cudaGetLastError();
+        return DW_ERR_LAUNCH;
+    }
+    std::lock_guard<std::mutex> lock(mu);
+    if (!have[dev]) {
+        DeviceInfo di{dev, 0, 0};
+        if (cudaDeviceGetAttribute(&di.sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&di.cc_major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess || di.sms <= 0) {
+            cudaGetLastError();
+            return DW_ERR_LAUNCH;
+        }
+        cache[dev] = di;
+        have[dev] = true;
+    }
+    *out = cache[dev];
+    return out->cc_major == 10 ? DW_OK : DW_ERR_ARCH;
+}
+
+}  // namespace dw
+
+extern "C" DW_API int dw_mxfp8_abi_version(void) { return 2; }
 
 extern "C" DW_API int dw_mxfp8_device_supported(int device) {
     int major = 0;
@@ -12,6 +52,12 @@ extern "C" DW_API int dw_mxfp8_device_supported(int device) {
         return 0;
     }
     return major == 10 ? 1 : 0;
+}
+
+extern "C" DW_API int dw_mxfp8_debug_fake_device(int cc_major, int sms) {
+    dw::g_fake_sms.store(sms, std::memory_order_relaxed);
+    dw::g_fake_cc.store(cc_major, std::memory_order_relaxed);
+    return DW_OK;
 }
 
 extern "C" DW_API const char* dw_mxfp8_error_string(int code) {

@@ -13,6 +13,15 @@ namespace dw {
 constexpr int kBlock = 32;  // elements per scaling block
 
 // ------------------------------------------------------------------------------------------
+// host side: the current device
+// ------------------------------------------------------------------------------------------
+constexpr int kMaxDevices = 64;
+struct DeviceInfo { int device; int sms; int cc_major; };
+// Properties of the CURRENT device (cached per device index, so one process may drive several GPUs).
+// DW_OK; DW_ERR_ARCH if it is not compute capability 10.x (*out is still filled); DW_ERR_LAUNCH if no device answers.
+int current_device(DeviceInfo* out);
+
+// ------------------------------------------------------------------------------------------
 // MX arithmetic
 // ------------------------------------------------------------------------------------------
 

@@ -59,11 +59,12 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
     return ok != 0;
 }
 
-// Bounded wait.  Gives up after ~kWaitCycles SM cycles (or as soon as another thread of the
+// Bounded wait.  Gives up after ~limit_cycles SM cycles (or as soon as another thread of the
 // CTA has raised *abort_flag) and returns false; the caller records the failure and unwinds.
 constexpr long long kWaitCycles = 2000000000ll;  // about one second
 template <bool kCluster = false>
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          long long limit_cycles = kWaitCycles) {
     if (kCluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     uint32_t spins = 0;
@@ -71,7 +72,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if (kCluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
         if ((++spins & 63u) == 0u) {
             if (*abort_flag != 0) return false;
-            if (clock64() - t0 > kWaitCycles) return false;
+            if (clock64() - t0 > limit_cycles) return false;
         }
     }
 }

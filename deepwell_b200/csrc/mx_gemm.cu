@@ -24,6 +24,7 @@
 // and unwinds through the common exit (TMEM is always freed).
 
 #include <algorithm>
+#include <atomic>
 #include <mutex>
 
 #include "dw_common.cuh"
@@ -121,7 +122,7 @@ __device__ __forceinline__ float apply_activation(float x, int act) {
     return x;
 }
 
-enum : int { kErrProducer = 1, kErrMmaFull = 2, kErrMmaAcc = 3, kErrEpilogue = 4 };
+enum : int { kErrProducer = 1, kErrMmaFull = 2, kErrMmaAcc = 3, kErrEpilogue = 4, kErrSelfTest = 5 };
 
 template <int BN, int kCtas, int kGroup>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -604,6 +605,21 @@ mx_splitk_reduce_kernel(const float* __restrict__ partial, uint16_t* __restrict_
     }
 }
 
+// Test aid for the bounded waits: one thread waits, with a caller-chosen cycle limit, on a barrier that nothing
+// arrives at.  No copy and no tensor-core operation is in flight, so when the limit runs out the kernel simply
+// records kErrSelfTest in the status word and returns, as the GEMM's roles do.
+__global__ void mx_wait_selftest_kernel(int* status, long long limit_cycles) {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        ptx::mbar_init(smem_u32(&bar), 1);
+        ptx::fence_barrier_init();
+        if (!ptx::mbar_wait<false>(smem_u32(&bar), 0, &abort_flag, limit_cycles) && status != nullptr)
+            atomicCAS(status, 0, kErrSelfTest | (static_cast<int>(blockIdx.x) << 8));
+    }
+}
+
 // ------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------
@@ -614,7 +630,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 static EncodeTiledFn encode_fn() {
     static EncodeTiledFn fn = nullptr;
     static std::once_flag once;
-    std::call_once(once, [] {
+    std::call_once(once, [] {       // a property of the driver, not of a device
         void* f = nullptr;
         cudaDriverEntryPointQueryResult qres;
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &qres) == cudaSuccess &&
@@ -624,69 +640,96 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// uint8 [rows, k] row-major, box = box_rows x 128 bytes, 128-byte swizzle, zero fill out of bounds
-static bool make_operand_map(CUtensorMap* m, const void* base, int64_t rows, int64_t k, int box_rows) {
-    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
-    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k)};
-    const cuuint32_t box[2] = {128u, static_cast<cuuint32_t>(box_rows)};
-    const cuuint32_t estr[2] = {1u, 1u};
-    return encode_fn()(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
-                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
-// tiled scale buffer seen as uint32 [tiles, 128]; one box = one 512-byte tile
-static bool make_sf_map(CUtensorMap* m, const void* base, int64_t tiles) {
-    const cuuint64_t dims[2] = {128u, static_cast<cuuint64_t>(tiles)};
-    const cuuint64_t strides[1] = {512u};
-    const cuuint32_t box[2] = {128u, 1u};
-    const cuuint32_t estr[2] = {1u, 1u};
-    return encode_fn()(m, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, estr,
-                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
-// bf16 D [M, N] row-major for the epilogue's stores: box = 32 rows x 32 columns (64 bytes), 64-byte swizzle
-static bool make_output_map(CUtensorMap* m, const void* base, int64_t M, int64_t N) {
-    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(M)};
-    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(N) * 2u};
-    const cuuint32_t box[2] = {32u, 32u};
-    const cuuint32_t estr[2] = {1u, 1u};
-    return encode_fn()(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
-static int g_tma_store = 1;
-static int g_group_m = 0;  // row tiles per raster band (0 = default)
-// 0 auto; 1: 1 CTA, BN 128; 2: 1 CTA, BN 256; 3: CTA pair (256-row tile), BN 256; 4: CTA pair, BN 128;
-// 5: CTA pair, BN 192 (two whole accumulators in tensor memory, unlike 3)
-static int g_variant = 0;
-
-static int sm_count() {
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+// The three kinds of tensor map the GEMM uses.  A map is a pure function of (kind, base, rows, row length, box rows),
+// so encoded maps are kept in a small per-thread table and a layer that calls with the same buffers again (cached
+// weight operands, a captured graph's fixed buffers, the bench loop) pays for no encode.
+enum MapKind : int { kMapOperand = 0, kMapScales = 1, kMapOutput = 2 };
+struct MapKey {
+    const void* base; int64_t rows, inner; int box_rows, kind;
+    bool operator==(const MapKey& o) const {
+        return base == o.base && rows == o.rows && inner == o.inner && box_rows == o.box_rows && kind == o.kind;
     }
-    return sms;
+};
+
+static bool encode_map(CUtensorMap* m, const MapKey& k) {
+    const cuuint32_t estr[2] = {1u, 1u};
+    void* base = const_cast<void*>(k.base);
+    if (k.kind == kMapOperand) {
+        // uint8 [rows, inner] row-major, box = box_rows x 128 bytes, 128-byte swizzle, zero fill out of bounds
+        const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k.inner), static_cast<cuuint64_t>(k.rows)};
+        const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k.inner)};
+        const cuuint32_t box[2] = {128u, static_cast<cuuint32_t>(k.box_rows)};
+        return encode_fn()(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    }
+    if (k.kind == kMapScales) {
+        // tiled scale buffer seen as uint32 [tiles, 128]; one box = one 512-byte tile
+        const cuuint64_t dims[2] = {128u, static_cast<cuuint64_t>(k.rows)};
+        const cuuint64_t strides[1] = {512u};
+        const cuuint32_t box[2] = {128u, 1u};
+        return encode_fn()(m, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    }
+    // bf16 D [rows, inner] row-major for the epilogue's stores: box = 32 rows x 32 columns (64 bytes), 64-byte swizzle
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k.inner), static_cast<cuuint64_t>(k.rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k.inner) * 2u};
+    const cuuint32_t box[2] = {32u, 32u};
+    return encode_fn()(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                       CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
+
+static std::atomic<long long> g_map_encodes{0};     // encodes actually performed (dw_mxfp8_debug_counter(0))
+
+static bool get_map(CUtensorMap* out, const void* base, int64_t rows, int64_t inner, int box_rows, int kind) {
+    constexpr int kSlots = 64;
+    struct Slot { MapKey key; CUtensorMap map; bool valid; };
+    static thread_local Slot table[kSlots] = {};
+    const MapKey key = {base, rows, inner, box_rows, kind};
+    uint64_t h = reinterpret_cast<uintptr_t>(base) >> 4;
+    h ^= static_cast<uint64_t>(rows) * 0x9E3779B97F4A7C15ull + static_cast<uint64_t>(inner) * 0xC2B2AE3D27D4EB4Full +
+         static_cast<uint64_t>(box_rows * 4 + kind);
+    Slot& s = table[(h ^ (h >> 29)) % kSlots];
+    if (!(s.valid && s.key == key)) {
+        if (!encode_map(&s.map, key)) { s.valid = false; return false; }
+        s.key = key; s.valid = true;
+        g_map_encodes.fetch_add(1, std::memory_order_relaxed);
+    }
+    *out = s.map;
+    return true;
+}
+
+// What a caller may fix about a launch; everything 0 = decided per problem by plan_gemm.
+//   bits [0,8)   kernel variant: 1: 1 CTA, BN 128; 2: 1 CTA, BN 256; 3: CTA pair (256-row tile), BN 256;
+//                4: CTA pair, BN 128; 5: CTA pair, BN 192 (two whole accumulators in tensor memory, unlike 3)
+//   bits [8,16)  row tiles per raster band        bits [16,24)  split-K count
+//   bit 24       D written with per-thread stores instead of TMA stores
+struct PlanWord {
+    int variant, group_m, splits; bool direct_stores;
+    static bool valid(int w) { return w >= 0 && (w & 0xFF) <= 5 && (w >> 25) == 0; }
+    explicit PlanWord(int w) : variant(w & 0xFF), group_m((w >> 8) & 0xFF), splits((w >> 16) & 0xFF), direct_stores((w >> 24) & 1) {}
+};
+static std::atomic<int> g_default_plan{0};          // dw_mxfp8_gemm_set_variant: the plan word of calls that pass none
+static std::atomic<long long*> g_timing{nullptr};   // optional per-CTA wait counters (dw_mxfp8_gemm_set_timing_buffer)
 
 template <int BN, int kCtas, int kGroup>
-static int launch_gemm(const void* a, const void* a_sf, const void* b, const void* b_sf, GemmParams p, cudaStream_t st) {
+static int launch_gemm(const void* a, const void* a_sf, const void* b, const void* b_sf, GemmParams p, const PlanWord& pw,
+                       const DeviceInfo& di, cudaStream_t st) {
     using Cfg = GemmCfg<BN, kCtas, kGroup>;
     CUtensorMap tm_a, tm_b, tm_sfa, tm_sfb, tm_d;
     const int64_t kt = (p.K / 32 + 3) / 4;
     const int64_t b_rows = p.tile_group != nullptr ? p.N * p.num_groups : p.N;
-    if (!make_operand_map(&tm_a, a, p.M, p.K, 128) || !make_operand_map(&tm_b, b, b_rows, p.K, Cfg::kBRows) ||
-        !make_sf_map(&tm_sfa, a_sf, ((p.M + 127) / 128) * kt) || !make_sf_map(&tm_sfb, b_sf, ((b_rows + 127) / 128) * kt))
+    if (!get_map(&tm_a, a, p.M, p.K, 128, kMapOperand) || !get_map(&tm_b, b, b_rows, p.K, Cfg::kBRows, kMapOperand) ||
+        !get_map(&tm_sfa, a_sf, ((p.M + 127) / 128) * kt, 128, 1, kMapScales) ||
+        !get_map(&tm_sfb, b_sf, ((b_rows + 127) / 128) * kt, 128, 1, kMapScales))
         return DW_ERR_LAUNCH;
     // D goes out by TMA when its rows are 16-byte multiples (the tensor map's stride rule) and it is
     // written by the GEMM kernel itself (not by the split-K reduction)
-    p.tma_store = (p.d != nullptr && p.splits <= 1 && p.N % 8 == 0 && g_tma_store) ? 1 : 0;
+    p.tma_store = (p.d != nullptr && p.splits <= 1 && p.N % 8 == 0 && !pw.direct_stores) ? 1 : 0;
     if (p.tma_store) {
-        if (!make_output_map(&tm_d, p.d, p.M, p.N)) return DW_ERR_LAUNCH;
+        if (!get_map(&tm_d, p.d, p.M, p.N, 32, kMapOutput)) return DW_ERR_LAUNCH;
     } else {
         tm_d = tm_a;                                        // unused by the kernel
     }
@@ -702,20 +745,27 @@ static int launch_gemm(const void* a, const void* a_sf, const void* b, const voi
         const int64_t tile_bytes = static_cast<int64_t>(128 * kCtas) * p.K, b_bytes = p.N * p.K;
         int64_t g = 16 / kCtas;
         if (b_bytes > (32ll << 20)) g = std::max<int64_t>(16 / kCtas, std::min<int64_t>((32ll << 20) / tile_bytes, 64 / kCtas));
-        p.group_m = static_cast<uint32_t>(g_group_m > 0 ? g_group_m : g);
+        p.group_m = static_cast<uint32_t>(pw.group_m > 0 ? pw.group_m : g);
     }
 
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute(mx_gemm_kernel<BN, kCtas, kGroup>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        Cfg::kSmemBytes);
-    });
-    if (attr_err != cudaSuccess) return DW_ERR_LAUNCH;
+    // the opt-in to more than 48 KB of dynamic shared memory is a per-device attribute of the kernel
+    {
+        static std::mutex mu;
+        static bool done[kMaxDevices] = {};
+        std::lock_guard<std::mutex> lock(mu);
+        if (!done[di.device]) {
+            if (cudaFuncSetAttribute(mx_gemm_kernel<BN, kCtas, kGroup>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     Cfg::kSmemBytes) != cudaSuccess) {
+                cudaGetLastError();
+                return DW_ERR_LAUNCH;
+            }
+            done[di.device] = true;
+        }
+    }
 
     p.kb_per_split = (p.num_kblocks + p.splits - 1) / p.splits;
     p.splits = (p.num_kblocks + p.kb_per_split - 1) / p.kb_per_split;      // every split owns at least one k-block
-    const int workers = std::min<int64_t>(static_cast<int64_t>(p.num_tiles) * p.splits, sm_count() / kCtas);
+    const int workers = std::min<int64_t>(static_cast<int64_t>(p.num_tiles) * p.splits, di.sms / kCtas);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(workers * kCtas));
     cfg.blockDim = dim3(kGemmThreads);
@@ -732,7 +782,7 @@ static int launch_gemm(const void* a, const void* a_sf, const void* b, const voi
     }
     if (p.splits > 1) {
         const int64_t quads = (p.M * p.N + 3) / 4;
-        const int grid = static_cast<int>(std::min<int64_t>((quads + 255) / 256, static_cast<int64_t>(sm_count()) * 8));
+        const int grid = static_cast<int>(std::min<int64_t>((quads + 255) / 256, static_cast<int64_t>(di.sms) * 8));
         mx_splitk_reduce_kernel<<<grid, 256, 0, st>>>(p.partial, p.d, p.bias, p.M, p.N, p.splits, p.alpha, p.beta);
         if (cudaGetLastError() != cudaSuccess) return DW_ERR_LAUNCH;
     }
@@ -743,13 +793,12 @@ static int launch_gemm(const void* a, const void* a_sf, const void* b, const voi
 // tiles to occupy the GPU and K is long (weight-gradient GEMMs: small N x K output, contraction over
 // all tokens).
 struct GemmPlan { int variant; uint32_t splits; size_t ws_bytes; };
-static int g_splits = 0;   // forced split count (0 = automatic)
 
-static GemmPlan plan_gemm(int64_t M, int64_t N, int64_t K) {
+static GemmPlan plan_gemm(int64_t M, int64_t N, int64_t K, const PlanWord& pw, int sms) {
     GemmPlan pl;
     const int64_t nkb = (K + 127) / 128;
-    pl.variant = g_variant != 0 ? g_variant : ((N <= 128) ? 1 : (M <= 128 ? 2 : 3));
-    if (g_variant == 0 && pl.variant == 3) {
+    pl.variant = pw.variant != 0 ? pw.variant : ((N <= 128) ? 1 : (M <= 128 ? 2 : 3));
+    if (pw.variant == 0 && pl.variant == 3) {
         // 256 x 256 tiles on CTA pairs (3), 256 x 192 tiles on CTA pairs (5) or 128 x 256 tiles on single CTAs (2).
         // Cost of the slowest worker in units of (256 columns x one k-block) of one SM's tensor time:
         // rounds of tiles x (k-blocks x efficiency + per-tile overhead), fitted to measurements on B200.  Variant 3's
@@ -759,7 +808,7 @@ static GemmPlan plan_gemm(int64_t M, int64_t N, int64_t K) {
         // 74 CTA pairs (8192 x 768 x 3072: 96 tiles of 256 x 256 = 2 rounds at 65 %; 128 tiles of 256 x 192 = 2
         // rounds at 86 %: 20.7 us against 24.5).
         // Problems small enough for split-K keep variant 3, which the split heuristic below was measured with.
-        const int64_t sms = sm_count(), pairs = sms / 2, tm = (M + 255) / 256;
+        const int64_t pairs = sms / 2, tm = (M + 255) / 256;
         const bool would_split = tm * ((N + 255) / 256) * 4 <= pairs && nkb >= 32;
         auto rounds = [](int64_t tiles, int64_t workers) { return static_cast<double>((tiles + workers - 1) / workers); };
         const double cost3 = rounds(tm * ((N + 255) / 256), pairs) * (nkb + 2.0);
@@ -772,17 +821,15 @@ static GemmPlan plan_gemm(int64_t M, int64_t N, int64_t K) {
     }
     const int ctas = (pl.variant >= 3) ? 2 : 1, bn = (pl.variant == 1 || pl.variant == 4) ? 128 : (pl.variant == 5 ? 192 : 256);
     const int64_t tiles = ((M + 128 * ctas - 1) / (128 * ctas)) * ((N + bn - 1) / bn);
-    const int64_t workers = sm_count() / ctas;
+    const int64_t workers = sms / ctas;
     int64_t splits = 1;
-    if (g_splits > 0) splits = std::min<int64_t>(g_splits, nkb);
+    if (pw.splits > 0) splits = std::min<int64_t>(pw.splits, nkb);
     // measured on B200: worth it only below a quarter of the GPU (the reduction pass costs ~10 us)
     else if (tiles * 4 <= workers && nkb >= 32) splits = std::max<int64_t>(1, std::min<int64_t>({workers / tiles, nkb / 16, 4}));
     pl.splits = static_cast<uint32_t>(splits);
     pl.ws_bytes = splits > 1 ? static_cast<size_t>(splits) * M * N * sizeof(float) : 0;
     return pl;
 }
-
-static long long* g_timing = nullptr;   // optional per-CTA wait counters (dw_mxfp8_gemm_set_timing_buffer)
 
 struct FusedOut {
     int act = DW_ACT_NONE; int rule = DW_RULE_OCP_FLOOR; void* codes = nullptr; void* scales = nullptr;
@@ -791,7 +838,8 @@ struct FusedOut {
 
 static int run_gemm(const void* a_codes, const void* a_sf, const void* b_codes, const void* b_sf, void* d_bf16,
                     const void* bias_bf16, int64_t M, int64_t N, int64_t K, float alpha, float beta, int variant,
-                    uint32_t splits, float* partial, void* status_word, cudaStream_t st, const FusedOut& fo = FusedOut()) {
+                    uint32_t splits, float* partial, void* status_word, const PlanWord& pw, const DeviceInfo& di, cudaStream_t st,
+                    const FusedOut& fo = FusedOut()) {
     GemmParams p = {};
     p.act = fo.act; p.q_rule = fo.rule;
     p.q_codes = static_cast<uint8_t*>(fo.codes); p.q_scales = static_cast<uint8_t*>(fo.scales);
@@ -801,25 +849,28 @@ static int run_gemm(const void* a_codes, const void* a_sf, const void* b_codes, 
     p.status = static_cast<int*>(status_word);
     p.M = M; p.N = N; p.K = K; p.alpha = alpha; p.beta = beta;
     p.splits = splits; p.partial = partial;
-    p.wait_cycles = g_timing;
+    p.wait_cycles = g_timing.load(std::memory_order_relaxed);
     p.tile_group = fo.tile_group; p.num_groups = fo.num_groups;
     switch (variant) {
-        case 1: return launch_gemm<128, 1, 1>(a_codes, a_sf, b_codes, b_sf, p, st);
-        case 2: return launch_gemm<256, 1, 1>(a_codes, a_sf, b_codes, b_sf, p, st);
-        case 3: return launch_gemm<256, 2, 1>(a_codes, a_sf, b_codes, b_sf, p, st);
-        case 4: return launch_gemm<128, 2, 1>(a_codes, a_sf, b_codes, b_sf, p, st);
-        default: return launch_gemm<192, 2, 1>(a_codes, a_sf, b_codes, b_sf, p, st);
+        case 1: return launch_gemm<128, 1, 1>(a_codes, a_sf, b_codes, b_sf, p, pw, di, st);
+        case 2: return launch_gemm<256, 1, 1>(a_codes, a_sf, b_codes, b_sf, p, pw, di, st);
+        case 3: return launch_gemm<256, 2, 1>(a_codes, a_sf, b_codes, b_sf, p, pw, di, st);
+        case 4: return launch_gemm<128, 2, 1>(a_codes, a_sf, b_codes, b_sf, p, pw, di, st);
+        default: return launch_gemm<192, 2, 1>(a_codes, a_sf, b_codes, b_sf, p, pw, di, st);
     }
 }
 
+// Argument checks that need no device, then the device: DW_ERR_ARCH unless the current device is compute capability 10.x.
 static int check_gemm_args(const void* a_codes, const void* a_sf, const void* b_codes, const void* b_sf, const void* d_bf16,
-                           const void* bias_bf16, int64_t M, int64_t N, int64_t K, bool d_optional = false) {
+                           const void* bias_bf16, int64_t M, int64_t N, int64_t K, DeviceInfo* di, bool d_optional = false) {
     if (!a_codes || !a_sf || !b_codes || !b_sf || (!d_bf16 && !d_optional)) return DW_ERR_BAD_ARG;
     if (K == 0 || K % 32 != 0) return DW_ERR_BAD_ARG;
     auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
     if (!al16(a_codes) || !al16(b_codes) || !al16(a_sf) || !al16(b_sf) || !al16(d_bf16)) return DW_ERR_BAD_ARG;
     if (bias_bf16 && !al16(bias_bf16)) return DW_ERR_BAD_ARG;
     if (M >= (1ll << 31) || N >= (1ll << 31) || K >= (1ll << 31)) return DW_ERR_TOO_LARGE;
+    const int rc = current_device(di);
+    if (rc != DW_OK) return rc;
     if (encode_fn() == nullptr) return DW_ERR_LAUNCH;
     return DW_OK;
 }
@@ -829,43 +880,58 @@ static int check_gemm_args(const void* a_codes, const void* a_sf, const void* b_
 using namespace dw;
 
 extern "C" DW_API int dw_mxfp8_gemm_set_variant(int variant) {
-    // bits [0,8): kernel variant; bits [8,16): row tiles per raster band; bits [16,24): split-K count (0 = automatic);
-    // bit 24: write D with per-thread stores instead of TMA stores
-    const int v = variant & 0xFF, gm = (variant >> 8) & 0xFF, sp = (variant >> 16) & 0xFF;
-    if (variant < 0 || v > 5) return DW_ERR_BAD_ARG;
-    g_tma_store = ((variant >> 24) & 1) ? 0 : 1;
-    g_variant = v;
-    g_group_m = gm;
-    g_splits = sp;
+    if (!PlanWord::valid(variant)) return DW_ERR_BAD_ARG;
+    g_default_plan.store(variant, std::memory_order_relaxed);
     return DW_OK;
 }
 
 extern "C" DW_API int dw_mxfp8_gemm_set_timing_buffer(void* device_buffer, size_t bytes) {
     if (device_buffer != nullptr && (bytes < DW_GEMM_TIMING_BYTES || (reinterpret_cast<uintptr_t>(device_buffer) & 7) != 0))
         return DW_ERR_BAD_ARG;
-    g_timing = static_cast<long long*>(device_buffer);
+    g_timing.store(static_cast<long long*>(device_buffer), std::memory_order_relaxed);
     return DW_OK;
 }
 
-extern "C" DW_API size_t dw_mxfp8_gemm_workspace(int64_t M, int64_t N, int64_t K) {
-    if (M <= 0 || N <= 0 || K <= 0) return 0;
-    return plan_gemm(M, N, K).ws_bytes;
+// SM count for planning when no device can be asked (a build machine sizing buffers): B200's
+static int planning_sms() {
+    DeviceInfo di;
+    const int rc = current_device(&di);
+    return (rc == DW_OK || rc == DW_ERR_ARCH) && di.sms > 0 ? di.sms : 148;
 }
 
-extern "C" DW_API int dw_mxfp8_gemm(const void* a_codes, const void* a_sf, const void* b_codes, const void* b_sf, void* d_bf16,
-                             const void* bias_bf16, int64_t M, int64_t N, int64_t K, float alpha, float beta, void* workspace,
-                             size_t workspace_bytes, void* status_word, void* stream) {
-    if (M < 0 || N < 0 || K < 0) return DW_ERR_BAD_ARG;
+extern "C" DW_API size_t dw_mxfp8_gemm_workspace_planned(int64_t M, int64_t N, int64_t K, int plan) {
+    if (M <= 0 || N <= 0 || K <= 0 || !PlanWord::valid(plan)) return 0;
+    return plan_gemm(M, N, K, PlanWord(plan), planning_sms()).ws_bytes;
+}
+
+extern "C" DW_API size_t dw_mxfp8_gemm_workspace(int64_t M, int64_t N, int64_t K) {
+    return dw_mxfp8_gemm_workspace_planned(M, N, K, g_default_plan.load(std::memory_order_relaxed));
+}
+
+extern "C" DW_API int dw_mxfp8_gemm_planned(const void* a_codes, const void* a_sf, const void* b_codes, const void* b_sf,
+                                            void* d_bf16, const void* bias_bf16, int64_t M, int64_t N, int64_t K, float alpha,
+                                            float beta, void* workspace, size_t workspace_bytes, int plan, void* status_word,
+                                            void* stream) {
+    if (M < 0 || N < 0 || K < 0 || !PlanWord::valid(plan)) return DW_ERR_BAD_ARG;
     if (M == 0 || N == 0) return DW_OK;
-    const int rc = check_gemm_args(a_codes, a_sf, b_codes, b_sf, d_bf16, bias_bf16, M, N, K);
+    DeviceInfo di;
+    const int rc = check_gemm_args(a_codes, a_sf, b_codes, b_sf, d_bf16, bias_bf16, M, N, K, &di);
     if (rc != DW_OK) return rc;
-    GemmPlan pl = plan_gemm(M, N, K);
+    const PlanWord pw(plan);
+    GemmPlan pl = plan_gemm(M, N, K, pw, di.sms);
     // without a large enough, 16-byte aligned workspace the GEMM runs unsplit
     if (pl.splits > 1 && (workspace == nullptr || workspace_bytes < pl.ws_bytes ||
                           (reinterpret_cast<uintptr_t>(workspace) & 15) != 0))
         pl.splits = 1;
     return run_gemm(a_codes, a_sf, b_codes, b_sf, d_bf16, bias_bf16, M, N, K, alpha, beta, pl.variant, pl.splits,
-                    static_cast<float*>(workspace), status_word, static_cast<cudaStream_t>(stream));
+                    static_cast<float*>(workspace), status_word, pw, di, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" DW_API int dw_mxfp8_gemm(const void* a_codes, const void* a_sf, const void* b_codes, const void* b_sf, void* d_bf16,
+                             const void* bias_bf16, int64_t M, int64_t N, int64_t K, float alpha, float beta, void* workspace,
+                             size_t workspace_bytes, void* status_word, void* stream) {
+    return dw_mxfp8_gemm_planned(a_codes, a_sf, b_codes, b_sf, d_bf16, bias_bf16, M, N, K, alpha, beta, workspace,
+                                 workspace_bytes, g_default_plan.load(std::memory_order_relaxed), status_word, stream);
 }
 
 extern "C" DW_API int dw_mxfp8_gemm_fused(const void* a_codes, const void* a_sf, const void* b_codes, const void* b_sf,
@@ -879,17 +945,19 @@ extern "C" DW_API int dw_mxfp8_gemm_fused(const void* a_codes, const void* a_sf,
     if (d_bf16 == nullptr && out_codes == nullptr) return DW_ERR_BAD_ARG;          // nothing to write
     if (d_bf16 == nullptr && beta != 0.0f) return DW_ERR_BAD_ARG;                  // beta reads D
     if (M == 0 || N == 0) return DW_OK;
-    const int rc = check_gemm_args(a_codes, a_sf, b_codes, b_sf, d_bf16, bias_bf16, M, N, K, true);
-    if (rc != DW_OK) return rc;
     if (out_codes != nullptr && (N % 32 != 0 || (reinterpret_cast<uintptr_t>(out_codes) & 15) != 0)) return DW_ERR_BAD_ARG;
     if (out_codes == nullptr && N % 8 != 0 && activation != DW_ACT_NONE && d_bf16 == nullptr) return DW_ERR_BAD_ARG;
+    DeviceInfo di;
+    const int rc = check_gemm_args(a_codes, a_sf, b_codes, b_sf, d_bf16, bias_bf16, M, N, K, &di, true);
+    if (rc != DW_OK) return rc;
     FusedOut fo;
     fo.act = activation; fo.rule = scale_rule; fo.codes = out_codes; fo.scales = out_scales;
-    GemmPlan pl = plan_gemm(M, N, K);
+    const PlanWord pw(g_default_plan.load(std::memory_order_relaxed));
+    GemmPlan pl = plan_gemm(M, N, K, pw, di.sms);
     // the scale padding of the quantised output is written per 128-column group: keep column tiles that are multiples of 128
     if (out_codes != nullptr && pl.variant > 4) pl.variant = 3;
     return run_gemm(a_codes, a_sf, b_codes, b_sf, d_bf16, bias_bf16, M, N, K, alpha, beta, pl.variant, 1, nullptr, status_word,
-                    static_cast<cudaStream_t>(stream), fo);
+                    pw, di, static_cast<cudaStream_t>(stream), fo);
 }
 
 extern "C" DW_API int dw_mxfp8_gemm_grouped(const void* a_codes, const void* a_sf, const void* b_codes, const void* b_sf,
@@ -899,15 +967,17 @@ extern "C" DW_API int dw_mxfp8_gemm_grouped(const void* a_codes, const void* a_s
     if (rows_per_tile != 128 && rows_per_tile != 256) return DW_ERR_BAD_ARG;
     if (M_total % rows_per_tile != 0 || N % 128 != 0) return DW_ERR_BAD_ARG;   // whole row tiles per group; whole scale tiles per weight
     if (M_total == 0) return DW_OK;
-    const int rc = check_gemm_args(a_codes, a_sf, b_codes, b_sf, d_bf16, nullptr, M_total, N, K);
-    if (rc != DW_OK) return rc;
     if (static_cast<int64_t>(num_groups) * N >= (1ll << 31)) return DW_ERR_TOO_LARGE;
+    DeviceInfo di;
+    const int rc = check_gemm_args(a_codes, a_sf, b_codes, b_sf, d_bf16, nullptr, M_total, N, K, &di);
+    if (rc != DW_OK) return rc;
     FusedOut fo;
     fo.tile_group = tile_group; fo.num_groups = static_cast<uint32_t>(num_groups);
     // the row tile of the kernel must be the granularity of tile_group: 1 CTA x 128 rows or a CTA pair x 256 rows
     const int variant = rows_per_tile == 128 ? 2 : 3;
+    const PlanWord pw(g_default_plan.load(std::memory_order_relaxed) & (1 << 24));     // the store mode only
     return run_gemm(a_codes, a_sf, b_codes, b_sf, d_bf16, nullptr, M_total, N, K, alpha, 0.0f, variant, 1, nullptr, status_word,
-                    static_cast<cudaStream_t>(stream), fo);
+                    pw, di, static_cast<cudaStream_t>(stream), fo);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -921,7 +991,6 @@ static __device__ __align__(256) float g_splitk_scratch[kStaticScratchFloats];
 // In host code `g_splitk_scratch` is only a handle for the runtime, not an address a kernel can use.
 // The device address is looked up once per device, with that device current.
 static int static_scratch_address(float** out) {
-    constexpr int kMaxDevices = 64;
     static std::mutex mu;
     static float* cached[kMaxDevices] = {};
     int dev = -1;
@@ -945,18 +1014,20 @@ extern "C" DW_API int dw_mxfp8_gemm_splitk_static(const void* a_codes, const voi
                                                   float alpha, float beta, int splits, void* status_word, void* stream) {
     if (M < 0 || N < 0 || K < 0 || splits < 2 || splits > 255) return DW_ERR_BAD_ARG;
     if (M == 0 || N == 0) return DW_OK;
-    const int rc = check_gemm_args(a_codes, a_sf, b_codes, b_sf, d_bf16, bias_bf16, M, N, K);
-    if (rc != DW_OK) return rc;
     const int64_t nkb = (K + 127) / 128;
     const int64_t eff = std::min<int64_t>(splits, nkb);                        // the kernel never uses more
-    if (static_cast<uint64_t>(eff) * static_cast<uint64_t>(M) * static_cast<uint64_t>(N) > kStaticScratchFloats)
+    if (K > 0 && static_cast<uint64_t>(eff) * static_cast<uint64_t>(M) * static_cast<uint64_t>(N) > kStaticScratchFloats)
         return DW_ERR_TOO_LARGE;
+    DeviceInfo di;
+    const int rc = check_gemm_args(a_codes, a_sf, b_codes, b_sf, d_bf16, bias_bf16, M, N, K, &di);
+    if (rc != DW_OK) return rc;
     float* scratch = nullptr;
     const int arc = static_scratch_address(&scratch);
     if (arc != DW_OK) return arc;
-    const int variant = plan_gemm(M, N, K).variant;
+    const PlanWord pw(g_default_plan.load(std::memory_order_relaxed) & 0xFF);        // the variant only
+    const int variant = plan_gemm(M, N, K, pw, di.sms).variant;
     return run_gemm(a_codes, a_sf, b_codes, b_sf, d_bf16, bias_bf16, M, N, K, alpha, beta, variant,
-                    static_cast<uint32_t>(eff), scratch, status_word, static_cast<cudaStream_t>(stream));
+                    static_cast<uint32_t>(eff), scratch, status_word, pw, di, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" DW_API int dw_mxfp8_check_status(const void* status_word, void* stream) {
@@ -966,4 +1037,18 @@ extern "C" DW_API int dw_mxfp8_check_status(const void* status_word, void* strea
     if (cudaMemcpyAsync(&host, status_word, sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess) return DW_ERR_LAUNCH;
     if (cudaStreamSynchronize(st) != cudaSuccess) return DW_ERR_LAUNCH;
     return host == 0 ? DW_OK : DW_ERR_DEVICE_STATUS;
+}
+
+extern "C" DW_API int dw_mxfp8_selftest_bounded_wait(long long limit_cycles, void* status_word, void* stream) {
+    if (status_word == nullptr || limit_cycles < 0) return DW_ERR_BAD_ARG;
+    if (limit_cycles > DW_SELFTEST_MAX_WAIT_CYCLES) return DW_ERR_TOO_LARGE;       // a test never keeps an SM longer than ~1 ms
+    DeviceInfo di;
+    const int rc = current_device(&di);
+    if (rc != DW_OK) return rc;
+    mx_wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<int*>(status_word), limit_cycles);
+    return cudaGetLastError() == cudaSuccess ? DW_OK : DW_ERR_LAUNCH;
+}
+
+extern "C" DW_API long long dw_mxfp8_debug_counter(int which) {
+    return which == 0 ? g_map_encodes.load(std::memory_order_relaxed) : -1;
 }

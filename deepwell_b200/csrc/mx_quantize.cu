@@ -431,20 +431,10 @@ mx_dequant_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__
 // ------------------------------------------------------------------------------------------
 static inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
-static int num_sms() {
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess) return 148;
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-    }
-    return sms;
-}
-
 static int launch_status() { return cudaGetLastError() == cudaSuccess ? DW_OK : DW_ERR_LAUNCH; }
 
 static int quantize_generic(const uint16_t* x, uint8_t* codes, uint8_t* scales, int64_t rows, int64_t cols, int direction,
-                            int rule, int layout, cudaStream_t st) {
+                            int rule, int layout, const DeviceInfo& di, cudaStream_t st) {
     // operand rows/cols = (rows, cols) for ROW, (cols, rows) for the column directions
     int64_t orow, ocol, xsr, xsc, csr, csc;
     int block_major;
@@ -455,7 +445,7 @@ static int quantize_generic(const uint16_t* x, uint8_t* codes, uint8_t* scales, 
         if (direction == DW_DIR_COL_T) { csr = rows; csc = 1; } else { csr = 1; csc = cols; }
     }
     const int64_t nb = (ocol + 31) / 32, total = orow * nb;
-    const int grid = static_cast<int>(std::min<int64_t>((total + 255) / 256, static_cast<int64_t>(num_sms()) * 16));
+    const int grid = static_cast<int>(std::min<int64_t>((total + 255) / 256, static_cast<int64_t>(di.sms) * 16));
     if (layout == DW_SF_TILED) {
         const int64_t rt = (orow + 127) / 128, kt = (nb + 3) / 4;
         mx_sf_pad_kernel<<<static_cast<int>(std::min<int64_t>((rt * kt * 512 + 255) / 256, 4096)), 256, 0, st>>>(
@@ -467,12 +457,16 @@ static int quantize_generic(const uint16_t* x, uint8_t* codes, uint8_t* scales, 
 }
 
 static int quantize_row_fast(const uint16_t* x, uint8_t* codes, uint8_t* scales, int64_t rows, int64_t cols, int rule,
-                             int layout, cudaStream_t st) {
+                             int layout, int flags, const DeviceInfo& di, cudaStream_t st) {
     const int64_t total_chunks = rows * cols / 16;
     const FastDiv cpr = FastDiv::make(static_cast<uint32_t>(cols / 16));
     const int packed = (cols % 128 == 0) && aligned(scales, 4);
     const int64_t want = (total_chunks + 511) / 512;
-    const int grid = static_cast<int>(std::min<int64_t>(want, static_cast<int64_t>(num_sms()) * 8));
+    // Default: a persistent grid that fills every SM (8 CTAs each) and strides over the matrix.  DW_QUANT_BACKGROUND: one
+    // short-lived CTA per 16 KB slab instead, so that a kernel of another stream that needs whole SMs (the GEMM: one
+    // 213 KB CTA per SM) is not kept waiting until a persistent grid retires, and this launch runs in what is left over.
+    const bool background = (flags & DW_QUANT_BACKGROUND) != 0 && total_chunks <= (1ll << 30);
+    const int grid = static_cast<int>(background ? want : std::min<int64_t>(want, static_cast<int64_t>(di.sms) * 8));
     if (layout == DW_SF_TILED && (rows % 128 != 0 || (cols / 32) % 4 != 0)) {
         const int64_t nb = cols / 32, rt = (rows + 127) / 128, kt = (nb + 3) / 4;
         mx_sf_pad_kernel<<<static_cast<int>(std::min<int64_t>((rt * kt * 512 + 255) / 256, 4096)), 256, 0, st>>>(
@@ -489,16 +483,22 @@ static int quantize_row_fast(const uint16_t* x, uint8_t* codes, uint8_t* scales,
 
 template <bool kDoRow, bool kDoCol, bool kColSum = false>
 static int launch_tile_kernel(const uint16_t* x, uint8_t* cr, uint8_t* sr, uint8_t* ct, uint8_t* sc, int64_t rows, int64_t cols,
-                              uint32_t tiles_c, uint32_t tiles, int rule, int layout, cudaStream_t st,
+                              uint32_t tiles_c, uint32_t tiles, int rule, int layout, const DeviceInfo& di, cudaStream_t st,
                               float* colsum_partial = nullptr) {
-    static std::once_flag once;
-    static cudaError_t attr_err = cudaSuccess;
-    std::call_once(once, [] {
-        attr_err = cudaFuncSetAttribute(mx_quant_tile_kernel<kDoRow, kDoCol, kColSum>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        kTileSmemBytes);
-    });
-    if (attr_err != cudaSuccess) return DW_ERR_LAUNCH;
-    const uint32_t grid = std::min<uint32_t>(tiles, static_cast<uint32_t>(num_sms()) * 3u);   // 3 CTAs of 65 KB per SM
+    {   // the opt-in to more than 48 KB of dynamic shared memory is a per-device attribute of the kernel
+        static std::mutex mu;
+        static bool done[kMaxDevices] = {};
+        std::lock_guard<std::mutex> lock(mu);
+        if (!done[di.device]) {
+            if (cudaFuncSetAttribute(mx_quant_tile_kernel<kDoRow, kDoCol, kColSum>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     kTileSmemBytes) != cudaSuccess) {
+                cudaGetLastError();
+                return DW_ERR_LAUNCH;
+            }
+            done[di.device] = true;
+        }
+    }
+    const uint32_t grid = std::min<uint32_t>(tiles, static_cast<uint32_t>(di.sms) * 3u);   // 3 CTAs of 65 KB per SM
     mx_quant_tile_kernel<kDoRow, kDoCol, kColSum><<<grid, 256, kTileSmemBytes, st>>>(x, cr, sr, ct, sc, rows, cols, tiles_c, tiles,
                                                                                     rule, layout, colsum_partial);
     return launch_status();
@@ -555,7 +555,12 @@ extern "C" DW_API size_t dw_mxfp8_scale_bytes(int64_t rows, int64_t k, int scale
 
 extern "C" DW_API int dw_mxfp8_quantize(const void* x_bf16, void* codes, void* scales, int64_t rows, int64_t cols, int direction,
                                  int scale_rule, int scale_layout, void* stream) {
-    if (rows < 0 || cols < 0) return DW_ERR_BAD_ARG;
+    return dw_mxfp8_quantize_ex(x_bf16, codes, scales, rows, cols, direction, scale_rule, scale_layout, 0, stream);
+}
+
+extern "C" DW_API int dw_mxfp8_quantize_ex(const void* x_bf16, void* codes, void* scales, int64_t rows, int64_t cols, int direction,
+                                    int scale_rule, int scale_layout, int flags, void* stream) {
+    if (rows < 0 || cols < 0 || (flags & ~DW_QUANT_BACKGROUND) != 0) return DW_ERR_BAD_ARG;
     if (direction < DW_DIR_ROW || direction > DW_DIR_COL) return DW_ERR_BAD_ARG;
     if (scale_rule != DW_RULE_OCP_FLOOR && scale_rule != DW_RULE_REF_CEIL) return DW_ERR_BAD_ARG;
     if (scale_layout != DW_SF_FLAT && scale_layout != DW_SF_TILED) return DW_ERR_BAD_ARG;
@@ -563,20 +568,23 @@ extern "C" DW_API int dw_mxfp8_quantize(const void* x_bf16, void* codes, void* s
     if (!x_bf16 || !codes || !scales) return DW_ERR_BAD_ARG;
     if (!aligned(x_bf16, 2)) return DW_ERR_BAD_ARG;
     if (rows * cols >= (1ll << 35)) return DW_ERR_TOO_LARGE;
+    DeviceInfo di;
+    const int drc = current_device(&di);
+    if (drc != DW_OK) return drc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const uint16_t* x = static_cast<const uint16_t*>(x_bf16);
     uint8_t* c = static_cast<uint8_t*>(codes);
     uint8_t* s = static_cast<uint8_t*>(scales);
 
     if (direction == DW_DIR_ROW && cols % 32 == 0 && aligned(x, 16) && aligned(c, 16))
-        return quantize_row_fast(x, c, s, rows, cols, scale_rule, scale_layout, st);
+        return quantize_row_fast(x, c, s, rows, cols, scale_rule, scale_layout, flags, di, st);
     if (direction == DW_DIR_COL_T && tile_path_ok(x, rows, cols) && aligned(c, 16) &&
         (scale_layout == DW_SF_FLAT || aligned(s, 16))) {
         const uint32_t tiles_c = static_cast<uint32_t>((cols + 127) / 128);
         const uint32_t tiles = static_cast<uint32_t>((rows + 127) / 128) * tiles_c;
-        return launch_tile_kernel<false, true>(x, nullptr, nullptr, c, s, rows, cols, tiles_c, tiles, scale_rule, scale_layout, st);
+        return launch_tile_kernel<false, true>(x, nullptr, nullptr, c, s, rows, cols, tiles_c, tiles, scale_rule, scale_layout, di, st);
     }
-    return quantize_generic(x, c, s, rows, cols, direction, scale_rule, scale_layout, st);
+    return quantize_generic(x, c, s, rows, cols, direction, scale_rule, scale_layout, di, st);
 }
 
 extern "C" DW_API int dw_mxfp8_quantize_both(const void* x_bf16, void* codes_row, void* scales_row, void* codes_col_t,
@@ -596,6 +604,9 @@ extern "C" DW_API int dw_mxfp8_quantize_both(const void* x_bf16, void* codes_row
     if (rows == 0 || cols == 0) return DW_OK;
     if (!x_bf16) return DW_ERR_BAD_ARG;
     if (rows * cols >= (1ll << 35)) return DW_ERR_TOO_LARGE;
+    DeviceInfo di;
+    const int drc = current_device(&di);
+    if (drc != DW_OK) return drc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (tile_path_ok(x_bf16, rows, cols) && aligned(codes_row, 8) && aligned(codes_col_t, 16) &&
         (scale_layout == DW_SF_FLAT || (aligned(scales_row, 16) && aligned(scales_col, 16)))) {
@@ -604,7 +615,7 @@ extern "C" DW_API int dw_mxfp8_quantize_both(const void* x_bf16, void* codes_row
         return launch_tile_kernel<true, true>(static_cast<const uint16_t*>(x_bf16), static_cast<uint8_t*>(codes_row),
                                               static_cast<uint8_t*>(scales_row), static_cast<uint8_t*>(codes_col_t),
                                               static_cast<uint8_t*>(scales_col), rows, cols, tiles_c, tiles, scale_rule,
-                                              scale_layout, st);
+                                              scale_layout, di, st);
     }
     int rc = dw_mxfp8_quantize(x_bf16, codes_row, scales_row, rows, cols, DW_DIR_ROW, scale_rule, scale_layout, stream);
     if (rc != DW_OK) return rc;
@@ -655,13 +666,16 @@ extern "C" DW_API int dw_mxfp8_quantize_both_colsum(const void* x_bf16, void* co
     if (!(tile_path_ok(x_bf16, rows, cols) && aligned(codes_row, 8) && aligned(codes_col_t, 16) &&
           (scale_layout == DW_SF_FLAT || (aligned(scales_row, 16) && aligned(scales_col, 16)))))
         return DW_ERR_BAD_ARG;
+    DeviceInfo di;
+    const int drc = current_device(&di);
+    if (drc != DW_OK) return drc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const uint32_t tiles_c = static_cast<uint32_t>((cols + 127) / 128);
     const int64_t tiles_r = (rows + 127) / 128;
     const int rc = launch_tile_kernel<true, true, true>(static_cast<const uint16_t*>(x_bf16), static_cast<uint8_t*>(codes_row),
                                                         static_cast<uint8_t*>(scales_row), static_cast<uint8_t*>(codes_col_t),
                                                         static_cast<uint8_t*>(scales_col), rows, cols, tiles_c,
-                                                        static_cast<uint32_t>(tiles_r) * tiles_c, scale_rule, scale_layout, st,
+                                                        static_cast<uint32_t>(tiles_r) * tiles_c, scale_rule, scale_layout, di, st,
                                                         static_cast<float*>(workspace));
     if (rc != DW_OK) return rc;
     mx_colsum_reduce_kernel<<<static_cast<unsigned>((cols + 31) / 32), 256, 0, st>>>(static_cast<const float*>(workspace), tiles_r,
@@ -673,12 +687,15 @@ extern "C" DW_API int dw_mxfp8_update_amax_history(const void* x_bf16, float* am
                                                    void* stream) {
     if (!amax_history || history_len <= 0 || num_elements < 0 || (num_elements > 0 && !x_bf16)) return DW_ERR_BAD_ARG;
     if ((reinterpret_cast<uintptr_t>(amax_history) & 3) != 0 || (reinterpret_cast<uintptr_t>(x_bf16) & 1) != 0) return DW_ERR_BAD_ARG;
+    DeviceInfo di;
+    const int drc = current_device(&di);
+    if (drc != DW_OK) return drc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     mx_amax_shift_kernel<<<1, 1, 0, st>>>(amax_history, history_len);
     if (launch_status() != DW_OK) return DW_ERR_LAUNCH;
     if (num_elements == 0) return DW_OK;
     const int64_t want = (num_elements / 16 + 255) / 256 + 1;
-    const int grid = static_cast<int>(std::min<int64_t>(want, static_cast<int64_t>(num_sms()) * 8));
+    const int grid = static_cast<int>(std::min<int64_t>(want, static_cast<int64_t>(di.sms) * 8));
     mx_amax_kernel<<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(x_bf16), num_elements, amax_history);
     return launch_status();
 }
@@ -690,8 +707,11 @@ extern "C" DW_API int dw_mxfp8_dequantize(const void* codes, const void* scales,
     if (rows == 0 || cols == 0) return DW_OK;
     if (!codes || !scales || !out_bf16) return DW_ERR_BAD_ARG;
     if (cols % 16 == 0 && (!aligned(codes, 16) || !aligned(out_bf16, 16))) return DW_ERR_BAD_ARG;
+    DeviceInfo di;
+    const int drc = current_device(&di);
+    if (drc != DW_OK) return drc;
     const int64_t total = rows * ((cols + 15) / 16);
-    const int grid = static_cast<int>(std::min<int64_t>((total + 255) / 256, static_cast<int64_t>(num_sms()) * 16));
+    const int grid = static_cast<int>(std::min<int64_t>((total + 255) / 256, static_cast<int64_t>(di.sms) * 16));
     mx_dequant_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint8_t*>(codes), static_cast<const uint8_t*>(scales), static_cast<uint16_t*>(out_bf16), rows,
         cols, scale_layout);

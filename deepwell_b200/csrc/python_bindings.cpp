@@ -70,6 +70,31 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> quantize_both(const Tensor& x_in, int
   return {cr.view(torch::kFloat8_e4m3fn), sr, ct.view(torch::kFloat8_e4m3fn), sc};
 }
 
+// dw_mxfp8_quantize_both into buffers the caller keeps (a module's persistent weight operands, so that a captured
+// CUDA graph re-quantises into the addresses it recorded).  The column-wise pair may be absent.
+void quantize_both_into(const Tensor& x_in, const Tensor& cr, const Tensor& sr, const c10::optional<Tensor>& ct,
+                        const c10::optional<Tensor>& sc, int64_t rule) {
+  require_bf16_2d(x_in, "input");
+  TORCH_CHECK(x_in.is_contiguous(), "input must be contiguous");
+  const c10::cuda::CUDAGuard guard(x_in.device());
+  const int64_t rows = x_in.size(0), cols = x_in.size(1);
+  auto check_buf = [&](const Tensor& t, int64_t bytes, const char* name) {
+    TORCH_CHECK(t.is_cuda() && t.get_device() == x_in.get_device() && t.is_contiguous() && t.element_size() == 1 &&
+                    t.numel() >= bytes, name, " must be a contiguous one-byte CUDA tensor of at least ", bytes, " bytes");
+  };
+  check_buf(cr, rows * cols, "row codes");
+  check_buf(sr, static_cast<int64_t>(dw_mxfp8_scale_bytes(rows, cols, DW_SF_TILED)), "row scales");
+  TORCH_CHECK(ct.has_value() == sc.has_value(), "column codes and scales come together");
+  if (ct.has_value()) {
+    check_buf(*ct, rows * cols, "column codes");
+    check_buf(*sc, static_cast<int64_t>(dw_mxfp8_scale_bytes(cols, rows, DW_SF_TILED)), "column scales");
+  }
+  check_rc(dw_mxfp8_quantize_both(x_in.data_ptr(), cr.data_ptr(), sr.data_ptr(), ct.has_value() ? ct->data_ptr() : nullptr,
+                                  sc.has_value() ? sc->data_ptr() : nullptr, rows, cols, static_cast<int>(rule), DW_SF_TILED,
+                                  stream_of(x_in)),
+           "dw_mxfp8_quantize_both");
+}
+
 // quantize_both plus the column sums of x ([cols], fp32 or bf16); see dw_mxfp8_quantize_both_colsum
 std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> quantize_both_colsum(const Tensor& x_in, int64_t rule, int64_t layout,
                                                                         bool sum_bf16) {
@@ -95,9 +120,10 @@ std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor> quantize_both_colsum(const Te
   return {cr.view(torch::kFloat8_e4m3fn), sr, ct.view(torch::kFloat8_e4m3fn), sc, sum};
 }
 
-// D[M,N] = alpha * A[M,K] . B[N,K]^T + beta * D + bias; operands with DW_SF_TILED scales; see dw_mxfp8_gemm
+// D[M,N] = alpha * A[M,K] . B[N,K]^T + beta * D + bias; operands with DW_SF_TILED scales; see dw_mxfp8_gemm.
+// plan < 0: the process default (dw_mxfp8_gemm); otherwise this call's own plan word (dw_mxfp8_gemm_planned).
 Tensor gemm(const Tensor& a, const Tensor& a_sf, const Tensor& b, const Tensor& b_sf, const c10::optional<Tensor>& out_in,
-            const c10::optional<Tensor>& bias, double alpha, double beta, const Tensor& status) {
+            const c10::optional<Tensor>& bias, double alpha, double beta, const Tensor& status, int64_t plan = -1) {
   TORCH_CHECK(a.is_cuda() && b.is_cuda() && a_sf.is_cuda() && b_sf.is_cuda(), "operands must be on CUDA");
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.element_size() == 1 && b.element_size() == 1, "operands must be 2-D one-byte tensors");
   const int64_t M = a.size(0), K = a.size(1), N = b.size(0);
@@ -122,13 +148,21 @@ Tensor gemm(const Tensor& a, const Tensor& a_sf, const Tensor& b, const Tensor& 
                 "bias must be a contiguous bfloat16 [N] tensor");
     bias_ptr = bias->data_ptr();
   }
-  const size_t ws_bytes = dw_mxfp8_gemm_workspace(M, N, K);       // non-zero when the GEMM will split K
+  // non-zero when the GEMM will split K
+  const size_t ws_bytes = plan < 0 ? dw_mxfp8_gemm_workspace(M, N, K)
+                                   : dw_mxfp8_gemm_workspace_planned(M, N, K, static_cast<int>(plan));
   Tensor ws;
   if (ws_bytes) ws = bytes_like(a, {static_cast<int64_t>(ws_bytes)});
-  check_rc(dw_mxfp8_gemm(a.data_ptr(), a_sf.data_ptr(), b.data_ptr(), b_sf.data_ptr(), out.data_ptr(), bias_ptr, M, N, K,
-                         static_cast<float>(alpha), static_cast<float>(beta), ws_bytes ? ws.data_ptr() : nullptr, ws_bytes,
-                         status.data_ptr(), stream_of(a)),
-           "dw_mxfp8_gemm");
+  void* ws_ptr = ws_bytes ? ws.data_ptr() : nullptr;
+  const float al = static_cast<float>(alpha), be = static_cast<float>(beta);
+  if (plan < 0)
+    check_rc(dw_mxfp8_gemm(a.data_ptr(), a_sf.data_ptr(), b.data_ptr(), b_sf.data_ptr(), out.data_ptr(), bias_ptr, M, N, K, al,
+                           be, ws_ptr, ws_bytes, status.data_ptr(), stream_of(a)),
+             "dw_mxfp8_gemm");
+  else
+    check_rc(dw_mxfp8_gemm_planned(a.data_ptr(), a_sf.data_ptr(), b.data_ptr(), b_sf.data_ptr(), out.data_ptr(), bias_ptr, M, N,
+                                   K, al, be, ws_ptr, ws_bytes, static_cast<int>(plan), status.data_ptr(), stream_of(a)),
+             "dw_mxfp8_gemm_planned");
   return out;
 }
 
@@ -185,9 +219,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "torch-tensor layer over libdw_mxfp8.so (MX quantisation + block-scaled GEMM for sm_100a)";
   m.def("quantize", &quantize, py::arg("x"), py::arg("direction"), py::arg("rule"), py::arg("layout"));
   m.def("quantize_both", &quantize_both, py::arg("x"), py::arg("rule"), py::arg("layout"));
+  m.def("quantize_both_into", &quantize_both_into, py::arg("x"), py::arg("codes_row"), py::arg("scales_row"),
+        py::arg("codes_col_t") = py::none(), py::arg("scales_col") = py::none(), py::arg("rule") = 0);
   m.def("quantize_both_colsum", &quantize_both_colsum, py::arg("x"), py::arg("rule"), py::arg("layout"), py::arg("sum_bf16"));
   m.def("gemm", &gemm, py::arg("a"), py::arg("a_sf"), py::arg("b"), py::arg("b_sf"), py::arg("out") = py::none(),
-        py::arg("bias") = py::none(), py::arg("alpha") = 1.0, py::arg("beta") = 0.0, py::arg("status"));
+        py::arg("bias") = py::none(), py::arg("alpha") = 1.0, py::arg("beta") = 0.0, py::arg("status"), py::arg("plan") = -1);
   m.def("linear_forward", &linear_forward);
   m.def("linear_backward", &linear_backward);
 }

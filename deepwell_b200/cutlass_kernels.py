@@ -58,8 +58,10 @@ def _check_2d_cuda(t: torch.Tensor, name: str) -> None:
 
 
 def mxfp8_gemm_bf16(a: torch.Tensor, b_kn: torch.Tensor, c: Optional[torch.Tensor] = None, alpha: float = 1.0,
-                    beta: float = 0.0, bias: Optional[torch.Tensor] = None, scale_rule: int = nv.RULE_OCP_FLOOR) -> torch.Tensor:
-    """alpha * A[M,K] @ B[K,N] + beta * C (+ bias) with both operands quantised to MXFP8 along K."""
+                    beta: float = 0.0, bias: Optional[torch.Tensor] = None, scale_rule: int = nv.RULE_OCP_FLOOR,
+                    plan: Optional[int] = None) -> torch.Tensor:
+    """alpha * A[M,K] @ B[K,N] + beta * C (+ bias) with both operands quantised to MXFP8 along K.
+    plan: the caller's own GEMM plan word (nv.plan_word); None = the process default."""
     a = a.to(torch.bfloat16)
     b_kn = b_kn.to(torch.bfloat16)
     a_codes, a_sf = nv.quantize(a, nv.DIR_ROW, scale_rule, nv.SF_TILED)
@@ -73,7 +75,7 @@ def mxfp8_gemm_bf16(a: torch.Tensor, b_kn: torch.Tensor, c: Optional[torch.Tenso
         if c is None:
             raise RuntimeError("beta != 0 needs the C operand")
         out = c.to(torch.bfloat16).contiguous().clone()
-    return nv.gemm(a_codes, a_sf, b_codes, b_sf, out=out, bias=bias, alpha=alpha, beta=beta)
+    return nv.gemm(a_codes, a_sf, b_codes, b_sf, out=out, bias=bias, alpha=alpha, beta=beta, plan=plan)
 
 
 _STACK_LIMIT = 20 << 20     # elements per expert weight above which the experts are quantised one launch each
@@ -86,7 +88,11 @@ def mxfp8_grouped_gemm_bf16(a_list: Sequence[torch.Tensor], b_list: Sequence[tor
     whole row tile) and quantised once, the weights are quantised into one stacked operand, and
     dw_mxfp8_gemm_grouped lets each row tile multiply its own group's weight.  Groups of different widths
     fall back to one launch per group.  Returns views into one output buffer.  `weight_cache` (a dict the caller
-    keeps) lets repeated calls with unchanged weight tensors reuse the stacked quantised operand."""
+    keeps) lets repeated calls with unchanged weights reuse the stacked quantised operand: an entry is reused only
+    when every weight is the same storage region (same storage object, offset, shape, strides, dtype, device) at the
+    same version as when it was built.  The entry keeps the source tensors alive, so an address cannot be handed to
+    a new tensor while the entry exists; weight lists rebuilt from temporaries on every call therefore never match
+    a stale entry (they miss, and are quantised again)."""
     G = len(a_list)
     if G == 0:
         return []
@@ -111,9 +117,16 @@ def mxfp8_grouped_gemm_bf16(a_list: Sequence[torch.Tensor], b_list: Sequence[tor
     a_codes, a_sf = nv.quantize(torch.cat(pieces, dim=0), nv.DIR_ROW, scale_rule, nv.SF_TILED)
     # weights: one stacked K-major operand [G * N, K] from one quantiser launch (N % 128 == 0, so every group owns
     # whole scale tiles and the stacked scale buffer is the concatenation of the groups' buffers)
-    key = tuple((b.data_ptr(), b._version, tuple(b.stride())) for b in b_list) + (scale_rule,)
-    cached = None if weight_cache is None else weight_cache.get("key")
-    if cached is not None and cached == key:
+    key = (G, K, N, scale_rule, str(dev)) + tuple(
+        (b.untyped_storage().data_ptr(), b.storage_offset(), tuple(b.shape), tuple(b.stride()), b.dtype, b._version)
+        for b in b_list)
+    hit = False
+    if weight_cache is not None and weight_cache.get("key") == key:
+        held = weight_cache["sources"]
+        # same storage OBJECTS as when the entry was built (they have been kept alive since, so equal addresses
+        # cannot belong to recycled memory)
+        hit = len(held) == G and all(h.untyped_storage()._cdata == b.untyped_storage()._cdata for h, b in zip(held, b_list))
+    if hit:
         b_codes, b_sf = weight_cache["operand"]
     else:
         k_major = [b.stride(0) == 1 and b.stride(1) == K for b in b_list]     # transposed views of [N, K] weights
@@ -135,7 +148,7 @@ def mxfp8_grouped_gemm_bf16(a_list: Sequence[torch.Tensor], b_list: Sequence[tor
             stacked = torch.cat([b.to(torch.bfloat16) for b in b_list], dim=1)           # [K, G * N]
             b_codes, b_sf = nv.quantize(stacked, nv.DIR_COL_T, scale_rule, nv.SF_TILED)
         if weight_cache is not None:
-            weight_cache["key"], weight_cache["operand"] = key, (b_codes, b_sf)
+            weight_cache["key"], weight_cache["operand"], weight_cache["sources"] = key, (b_codes, b_sf), list(b_list)
     groups = torch.tensor(tile_group, dtype=torch.int32).to(dev, non_blocking=True)
     d = nv.gemm_grouped(a_codes, a_sf, b_codes, b_sf, groups, G, rows_per_tile=rpt, alpha=alpha)
     return [d[o:o + m] for o, m in zip(offsets, sizes)]
@@ -151,7 +164,8 @@ class BlackwellGemmKernel:
         self.use_microscaling = False
         self.block_size = 32
         self.tmem_residency = True
-        self.cluster_shape = (2, 1)
+        self.cluster_shape: Optional[Tuple[int, int]] = None     # None: the kernel variant is chosen per problem
+        self.plan = nv.plan_word(0)                               # this object's own launch choices (all automatic)
         self.initialized = False
 
     def initialize(self, m: int, n: int, k: int, dtype: str = "bf16", use_microscaling: bool = False,
@@ -176,7 +190,7 @@ class BlackwellGemmKernel:
             raise RuntimeError(f"operand shapes {tuple(a.shape)} x {tuple(b.shape)} do not match the initialised "
                                f"problem {self.m}x{self.n}x{self.k}")
         if self.dtype == "mxfp8":
-            out = mxfp8_gemm_bf16(a, b, c, alpha, beta)
+            out = mxfp8_gemm_bf16(a, b, c, alpha, beta, plan=self.plan)
             return out if a.dtype == torch.bfloat16 else out.to(a.dtype)
         # plain library GEMM for the unquantised dtypes (the reference calls cuBLAS here, :143-172)
         td = _TORCH_DTYPES[self.dtype]
@@ -192,11 +206,14 @@ class BlackwellGemmKernel:
         self.tmem_residency = bool(enable)
 
     def set_cluster_shape(self, m: int, n: int) -> None:
-        """(2, 1) selects the CTA-pair kernel (cta_group::2), (1, 1) the single-CTA kernel."""
+        """(2, 1) pins THIS object's GEMMs to the CTA-pair kernel (cta_group::2, 256 x 256 tiles), (1, 1) to the
+        single-CTA kernel (128 x 256 tiles).  The choice travels with every gemm() call of this object as its plan
+        word; other kernel objects, DWLinear and other host threads are not affected.  Without a call the variant
+        is chosen per problem."""
         if (m, n) not in ((1, 1), (2, 1)):
             raise RuntimeError("supported cluster shapes: (1, 1) and (2, 1)")
         self.cluster_shape = (int(m), int(n))
-        nv.set_gemm_variant(3 if m == 2 else 2)
+        self.plan = nv.plan_word(3 if m == 2 else 2)
 
     def get_expected_tflops(self) -> float:
         """Nominal dense peak of the selected precision (csrc/cutlass_kernels.cpp:233-263 kept hard-coded

@@ -6,7 +6,9 @@
  * consumes those operands.  Plain pointers and sizes only; every pointer is a
  * DEVICE pointer unless stated; `stream` is a cudaStream_t passed as void*.
  * All calls are asynchronous on `stream`, allocate nothing, and borrow the caller's
- * buffers.  Return value: DW_OK or a negative DW_ERR_* code (the convention of the
+ * buffers.  State is kept per device (one process may drive several GPUs; the device that is
+ * current at the call is the one used) and every launching call returns DW_ERR_ARCH on a
+ * device that is not compute capability 10.x.  Return value: DW_OK or a negative DW_ERR_* code (the convention of the
  * reference's only C ABI, dw_fmha_bf16_forward, csrc/fmha_bridge_min/fmha_bridge_min.cu:39-46).
  *
  * Each entry point names the reference interface it replaces (path:line inside the
@@ -68,6 +70,16 @@ size_t dw_mxfp8_scale_bytes(int64_t rows, int64_t k, int scale_layout);
  * codes: uint8 E4M3 (fn); scales: uint8 E8M0.  x and codes 16-byte aligned. */
 int dw_mxfp8_quantize(const void *x_bf16, void *codes, void *scales, int64_t rows, int64_t cols,
                       int direction, int scale_rule, int scale_layout, void *stream);
+
+/* dw_mxfp8_quantize with launch flags.  DW_QUANT_BACKGROUND: the launch is meant to run underneath a GEMM that
+ * another stream issues (the next layer's operands while this layer multiplies).  The row-wise kernel then uses one
+ * short-lived thread block per 16 KB of input instead of a persistent grid that fills every SM, so the GEMM's
+ * thread blocks (one per SM, nearly all of its shared memory) get their SMs as soon as they are ready and the
+ * quantiser takes what is left.  Same bytes out; the other directions ignore the flag.
+ * The reference has one launch shape (one block per 32 elements, csrc/mxfp8_quantization.cu:232-240). */
+#define DW_QUANT_BACKGROUND 1
+int dw_mxfp8_quantize_ex(const void *x_bf16, void *codes, void *scales, int64_t rows, int64_t cols,
+                         int direction, int scale_rule, int scale_layout, int flags, void *stream);
 
 /* One read of x, both operand forms: row-wise (codes_row [rows, cols]) and column-wise
  * transposed (codes_col_t [cols, rows]).  Either output pair may be NULL.
@@ -158,6 +170,21 @@ int dw_mxfp8_gemm_grouped(const void *a_codes, const void *a_sf, const void *b_c
 /* Replaces BlackwellGemmKernel::get_workspace_size, csrc/cutlass_kernels.cpp:229-231. */
 size_t dw_mxfp8_gemm_workspace(int64_t M, int64_t N, int64_t K);
 
+/* dw_mxfp8_gemm with the launch choices of THIS call in `plan` instead of the process default
+ * (dw_mxfp8_gemm_set_variant): bits [0,8) kernel variant (0 = chosen per problem; 1: one CTA, 128-wide
+ * column tiles; 2: one CTA, 256-wide; 3: CTA pair on a 256 x 256 tile; 4: CTA pair, 128-wide; 5: CTA pair,
+ * 192-wide), bits [8,16) row tiles per raster band, bits [16,24) split-K count, bit 24 per-thread stores
+ * instead of TMA stores; 0 = everything automatic.  Two host threads (or two kernel objects) can thus run
+ * different variants at the same time; nothing the call reads is process state.
+ * This is where BlackwellGemmKernel::set_cluster_shape / enable_tmem_residency (csrc/cutlass_kernels.cpp:265-272,
+ * per-object flags the reference stores and ignores) take effect: the Python class keeps its own plan word.
+ * dw_mxfp8_gemm_workspace_planned is the matching workspace query. */
+int dw_mxfp8_gemm_planned(const void *a_codes, const void *a_sf, const void *b_codes, const void *b_sf,
+                          void *d_bf16, const void *bias_bf16, int64_t M, int64_t N, int64_t K, float alpha,
+                          float beta, void *workspace, size_t workspace_bytes, int plan, void *status_word,
+                          void *stream);
+size_t dw_mxfp8_gemm_workspace_planned(int64_t M, int64_t N, int64_t K, int plan);
+
 /* Split-K GEMM that allocates nothing and needs no workspace from the caller.  No counterpart in
  * the reference.
  *
@@ -186,8 +213,28 @@ int dw_mxfp8_gemm_splitk_static(const void *a_codes, const void *a_sf, const voi
                                 void *d_bf16, const void *bias_bf16, int64_t M, int64_t N, int64_t K, float alpha,
                                 float beta, int splits, void *status_word, void *stream);
 
-/* Synchronises `stream`, reads the status word; DW_OK or DW_ERR_DEVICE_STATUS. */
+/* Synchronises `stream`, reads the status word; DW_OK or DW_ERR_DEVICE_STATUS.
+ * The kernels only SET the word (once, first failure wins: low byte = which wait gave up, upper bits = CTA);
+ * nothing in the library reads it back on its own, so a caller that passes a status word polls it here at a
+ * point where it synchronises anyway (once per optimizer step, say) and clears it after a failure.
+ * The reference reports kernel trouble with printf only (csrc/blackwell_gemm_kernel.cu:76-98). */
 int dw_mxfp8_check_status(const void *status_word, void *stream);
+
+/* Test aid for that error path: launches one tiny kernel whose single thread waits, for at most
+ * `limit_cycles` SM cycles (<= DW_SELFTEST_MAX_WAIT_CYCLES, about a millisecond), on a barrier nothing
+ * arrives at, with no copy and no tensor-core operation in flight.  The wait runs out, the kernel records
+ * code 5 in the status word exactly as the GEMM's roles do, and returns; the context stays usable.
+ * No counterpart in the reference. */
+#define DW_SELFTEST_MAX_WAIT_CYCLES 2000000ll
+int dw_mxfp8_selftest_bounded_wait(long long limit_cycles, void *status_word, void *stream);
+
+/* Test aids.  dw_mxfp8_debug_fake_device: every later call of this process takes the current device to have
+ * compute capability `cc_major`.x and `sms` SMs instead of asking the runtime (cc_major < 0 switches it off);
+ * with cc_major != 10 every launching entry point returns DW_ERR_ARCH before it touches the device, which is
+ * how that path is tested on machines without a GPU.  dw_mxfp8_debug_counter(0): tensor maps encoded so far
+ * (the rest were served from the per-thread table).  No counterpart in the reference. */
+int dw_mxfp8_debug_fake_device(int cc_major, int sms);
+long long dw_mxfp8_debug_counter(int which);
 
 /* Tuning aid: per-CTA counters of the SM cycles the GEMM's producer, MMA-issuer and epilogue
  * roles spent waiting, written by every later dw_mxfp8_gemm launch of this process into
@@ -198,10 +245,10 @@ int dw_mxfp8_check_status(const void *status_word, void *stream);
 #define DW_GEMM_TIMING_BYTES (296 * 8 * 8)
 int dw_mxfp8_gemm_set_timing_buffer(void *device_buffer, size_t bytes);
 
-/* Selects the GEMM kernel variant (bits 0-7), raster band height (bits 8-15) and split-K count
- * (bits 16-23) for later dw_mxfp8_gemm calls in this process (0 = automatic); bit 24 set: the output
- * is written with per-thread stores instead of TMA stores (for comparison and for debugging).  Counterpart of BlackwellGemmKernel::set_cluster_shape /
- * enable_tmem_residency, csrc/cutlass_kernels.cpp:265-272 (flags the reference stores and ignores). */
+/* Process default of the plan word (see dw_mxfp8_gemm_planned) for the entry points that take none:
+ * dw_mxfp8_gemm, dw_mxfp8_gemm_fused, dw_mxfp8_gemm_grouped (store mode only) and
+ * dw_mxfp8_gemm_splitk_static (variant only).  A tuning and test switch; library users pass the plan per call.
+ * Counterpart of the process-wide defaults in KernelSelector (csrc/cutlass_kernels.h:227-241). */
 int dw_mxfp8_gemm_set_variant(int variant);
 
 #ifdef __cplusplus

@@ -35,7 +35,12 @@ def assert_close(got, ref):
 
 
 def oracle_gemm(nv, x, w, alpha=1.0, beta=0.0, d0=None, bias=None, rows=None, cols=None):
-    """fp32-accumulated product of the dequantised operands (optionally a row/column sample)."""
+    """fp32-accumulated product of the dequantised operands (optionally a row/column sample).
+
+    The codes and scales that are dequantised here come from the GPU quantiser.  That is sound because the
+    quantiser is pinned bit for bit against the oracle on its own (tests/test_gpu_quantize.py), so these are the
+    bytes the oracle's quantiser would give; test_smoke_matrix_end_to_end_through_the_oracle below keeps one case
+    that goes bf16 -> oracle quantiser -> oracle GEMM with nothing from the GPU on the reference side."""
     xc, xs = nv.quantize(x, nv.DIR_ROW, 0, nv.SF_FLAT)
     wc, ws = nv.quantize(w, nv.DIR_ROW, 0, nv.SF_FLAT)
     xc, xs, wc, ws = host(xc), host(xs), host(wc), host(ws)
@@ -107,9 +112,29 @@ def test_tma_store_and_direct_store_epilogues_agree(nv, variant):
         assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16)), (M, N, K)
 
 
+def test_smoke_matrix_end_to_end_through_the_oracle(nv):
+    """X [2048,4096] N(0,1) with 1 % outliers x50, W [4096,4096] N(0,0.02): the reference side is computed entirely on
+    the CPU (oracle quantiser on the bf16 bits, oracle dequantised fp32 GEMM) on a band of rows and columns that
+    crosses tile edges; the GPU side is quantise + GEMM through the C ABI."""
+    nv.set_gemm_variant(0)
+    X, W = config1_inputs()
+    rows = np.r_[0:40, 120:136, 250:262, 2040:2048]
+    cols = np.r_[0:24, 248:264, 1016:1032, 4088:4096]
+    bits = lambda t: t.contiguous().view(torch.int16).numpy().view(np.uint16)
+    xq, xs = o.quantize_rowwise(bits(X[rows]))
+    wq, ws = o.quantize_rowwise(bits(W[cols]))
+    ref = torch.from_numpy(o.dequantize_rowwise(xq, xs)) @ torch.from_numpy(o.dequantize_rowwise(wq, ws)).t()
+    x, w = X.cuda(), W.cuda()
+    xc, xsf = nv.quantize(x, nv.DIR_ROW, 0, nv.SF_TILED)
+    wc, wsf = nv.quantize(w, nv.DIR_ROW, 0, nv.SF_TILED)
+    y = nv.gemm(xc, xsf, wc, wsf)
+    nv.check_status()
+    assert_close(y.cpu()[rows][:, cols], ref)
+
+
 @pytest.mark.parametrize("variant", [0, 3])
 def test_config1_full(nv, golden, variant):
-    """BASELINE config 1 in full: X [2048,4096] . W [4096,4096]^T, and the golden 64x64 corner."""
+    """The 2048 x 4096 x 4096 outlier matrix in full: X [2048,4096] . W [4096,4096]^T, and the golden 64x64 corner."""
     nv.set_gemm_variant(variant)
     X, W = config1_inputs()
     x, w = X.cuda(), W.cuda()
@@ -122,11 +147,26 @@ def test_config1_full(nv, golden, variant):
     assert_close(y[:64, :64].cpu(), corner)
 
 
+def band_edge_samples(extent, tile_sizes, extra, gen):
+    """Indices that include the first and the last element of every tile of every size in `tile_sizes` along an axis
+    of length `extent` (so every tile band edge of the kernels' 128/192/256-wide tiles is hit), plus `extra` random ones."""
+    idx = {0, extent - 1}
+    for t in tile_sizes:
+        for start in range(0, extent, t):
+            idx.add(start)
+            idx.add(min(start + t, extent) - 1)
+    idx.update(int(v) for v in torch.randint(0, extent, (extra,), generator=gen))
+    return torch.tensor(sorted(idx))
+
+
 @pytest.mark.parametrize("variant", [0, 3])
-@pytest.mark.parametrize("M,N,K", [(8192, 3072, 768), (8192, 768, 3072), (16384, 6144, 4096), (16384, 4096, 14336)])
+@pytest.mark.parametrize("M,N,K", [(8192, 3072, 768), (8192, 768, 3072), (16384, 6144, 4096), (16384, 4096, 4096),
+                                   (16384, 28672, 4096), (16384, 4096, 14336)])
 def test_model_shapes_sampled(nv, variant, M, N, K):
-    """GPT-2-small and Llama-3-8B linear shapes at full size: 96 sampled rows x 160 sampled
-    columns against the oracle, plus linearity in alpha (a size-independent property)."""
+    """GPT-2-small MLP and all four Llama-3-8B linear shapes at full size against the oracle on a sample that holds
+    the first and last row of every 128- and 256-row tile and the first and last column of every 128-, 192- and
+    256-column tile (every tile band edge of every kernel variant) plus random interior points, and linearity in
+    alpha (a size-independent property)."""
     nv.set_gemm_variant(variant)
     g = torch.Generator("cuda").manual_seed(3456)
     x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
@@ -136,8 +176,8 @@ def test_model_shapes_sampled(nv, variant, M, N, K):
     y = nv.gemm(xc, xs, wc, ws)
     nv.check_status()
     gi = torch.Generator().manual_seed(7)
-    rows = torch.cat([torch.tensor([0, M - 1]), torch.randint(0, M, (94,), generator=gi)])
-    cols = torch.cat([torch.tensor([0, N - 1]), torch.randint(0, N, (158,), generator=gi)])
+    rows = band_edge_samples(M, (128, 256), 32, gi)
+    cols = band_edge_samples(N, (128, 192, 256), 32, gi)
     ref = oracle_gemm(nv, x, w, rows=rows.numpy(), cols=cols.numpy())
     assert_close(y[rows.cuda()][:, cols.cuda()].cpu(), ref)
     y2 = nv.gemm(xc, xs, wc, ws, alpha=2.0)
@@ -339,3 +379,131 @@ def test_grouped_gemm_weight_cache_and_quantize_into(nv):
     nv.quantize_into(x, big_c[N:2 * N], big_s[scales.numel():2 * scales.numel()], nv.DIR_ROW, 0, nv.SF_TILED)
     assert torch.equal(big_c[N:2 * N], codes.view(torch.uint8)) and torch.equal(big_s[scales.numel():2 * scales.numel()], scales)
     assert int(big_c[:N].sum()) == 0 and int(big_c[2 * N:].sum()) == 0
+
+
+# ----------------------------------------------------------------------------------------------
+# the boundary: plan per call, host threads, tensor-map table, error paths
+# ----------------------------------------------------------------------------------------------
+def test_two_host_threads_two_streams_two_variants(nv, native_lib):
+    """Two host threads, each on its own stream, run the block-scaled GEMM with DIFFERENT kernel variants (passed per
+    call as the plan word) and the tile quantiser at the same time; both get oracle-correct results, repeatedly.
+    Nothing a call reads is process state, so neither thread can change what the other runs."""
+    import threading
+    nv.set_gemm_variant(0)
+    L = native_lib
+    M, N, K = 640, 768, 1024
+    g = torch.Generator("cpu").manual_seed(21)
+    x = torch.randn(M, K, generator=g).bfloat16().cuda()
+    w = (torch.randn(N, K, generator=g) * 0.03).bfloat16().cuda()
+    ref = oracle_gemm(nv, x, w)
+    e_r, e_rs = o.quantize_rowwise(x.cpu().view(torch.int16).numpy().view(np.uint16))
+    e_c, e_cs = o.quantize_colwise(x.cpu().view(torch.int16).numpy().view(np.uint16))
+    status = nv.status_word("cuda:0")
+    torch.cuda.synchronize()
+    errors, results = [], {}
+
+    def worker(name, variant):
+        try:
+            torch.cuda.set_device(0)
+            stream = torch.cuda.Stream()
+            with torch.cuda.stream(stream):
+                u8 = lambda *shape: torch.empty(*shape, dtype=torch.uint8, device="cuda")
+                for it in range(6):
+                    cr, ct = u8(M, K), u8(K, M)
+                    sr, sc = u8(nv.scale_bytes(M, K, nv.SF_TILED)), u8(nv.scale_bytes(K, M, nv.SF_TILED))
+                    rc = L.dw_mxfp8_quantize_both(x.data_ptr(), cr.data_ptr(), sr.data_ptr(), ct.data_ptr(), sc.data_ptr(), M, K,
+                                                  0, nv.SF_TILED, stream.cuda_stream)
+                    assert rc == 0
+                    wc, ws = u8(N, K), u8(nv.scale_bytes(N, K, nv.SF_TILED))
+                    assert L.dw_mxfp8_quantize(w.data_ptr(), wc.data_ptr(), ws.data_ptr(), N, K, 0, 0, nv.SF_TILED, stream.cuda_stream) == 0
+                    y = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+                    rc = L.dw_mxfp8_gemm_planned(cr.data_ptr(), sr.data_ptr(), wc.data_ptr(), ws.data_ptr(), y.data_ptr(), None,
+                                                 M, N, K, 1.0, 0.0, None, 0, nv.plan_word(variant), status.data_ptr(),
+                                                 stream.cuda_stream)
+                    assert rc == 0
+                    stream.synchronize()
+                    results[(name, it)] = (y.cpu(), cr.cpu().numpy(), sr.cpu().numpy(), ct.cpu().numpy(), sc.cpu().numpy())
+        except Exception as e:          # surfaced in the main thread
+            errors.append((name, repr(e)))
+
+    threads = [threading.Thread(target=worker, args=("pair", 3)), threading.Thread(target=worker, args=("single", 2))]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    nv.check_status()
+    for (name, it), (y, cr, sr, ct, sc) in results.items():
+        assert_close(y, ref)
+        assert np.array_equal(cr, e_r) and np.array_equal(sr, o.sf_flat_to_tiled(e_rs)), (name, it)
+        assert np.array_equal(ct, e_c) and np.array_equal(sc, o.sf_flat_to_tiled(e_cs)), (name, it)
+    # the two variants really are different kernels with the same result up to accumulation order: compare one pair
+    assert_close(results[("pair", 0)][0], results[("single", 0)][0].float())
+
+
+def test_kernel_objects_keep_their_own_cluster_shape(nv):
+    """set_cluster_shape on one BlackwellGemmKernel pins that object only; another object and the process default are
+    untouched (the choice travels with each call as its plan word)."""
+    from deepwell_b200 import cutlass_kernels as ck
+    nv.set_gemm_variant(0)
+    a = torch.randn(512, 256, device="cuda").bfloat16()
+    b = (torch.randn(256, 384, device="cuda") * 0.05).bfloat16()
+    k1, k2 = ck.BlackwellGemmKernel(), ck.BlackwellGemmKernel()
+    for k in (k1, k2):
+        k.initialize(512, 384, 256, "mxfp8", True, 32)
+    k1.set_cluster_shape(1, 1)
+    assert k1.plan == nv.plan_word(2) and k2.plan == nv.plan_word(0) and k2.cluster_shape is None
+    y1, y2 = k1.gemm(a, b), k2.gemm(a, b)
+    nv.check_status()
+    ref = oracle_gemm(nv, a, b.t().contiguous())
+    assert_close(y1.cpu(), ref)
+    assert_close(y2.cpu(), ref)
+
+
+def test_tensor_maps_are_encoded_once_per_buffer(nv, native_lib):
+    """A second GEMM on the same buffers encodes no tensor map (they come from the per-thread table); new buffers do."""
+    nv.set_gemm_variant(0)
+    x = torch.randn(384, 256, device="cuda").bfloat16()
+    w = torch.randn(512, 256, device="cuda").bfloat16()
+    xc, xs = nv.quantize(x, nv.DIR_ROW, 0, nv.SF_TILED)
+    wc, ws = nv.quantize(w, nv.DIR_ROW, 0, nv.SF_TILED)
+    out = torch.empty(384, 512, dtype=torch.bfloat16, device="cuda")
+    first = nv.gemm(xc, xs, wc, ws, out=out).clone()
+    n0 = native_lib.dw_mxfp8_debug_counter(0)
+    again = nv.gemm(xc, xs, wc, ws, out=out)
+    assert native_lib.dw_mxfp8_debug_counter(0) == n0
+    assert torch.equal(first, again)
+    out2 = torch.empty(384, 512, dtype=torch.bfloat16, device="cuda")
+    nv.gemm(xc, xs, wc, ws, out=out2)
+    assert native_lib.dw_mxfp8_debug_counter(0) == n0 + 1          # only the output map is new
+    assert torch.equal(first, out2)
+    nv.check_status()
+
+
+def test_status_word_set_from_the_host_raises(nv):
+    """The error path above the kernels, without a device fault: a non-zero status word (here written by the host,
+    as a kernel whose wait expired would) makes check_status raise a RuntimeError that names the wait and the CTA,
+    and clears the word."""
+    sw = nv.status_word("cuda:0")
+    sw.fill_(3 | (17 << 8))                      # code 3 (accumulator wait) recorded by CTA 17
+    with pytest.raises(RuntimeError, match=r"status word 3, CTA 17"):
+        nv.check_status("cuda:0")
+    assert int(sw.item()) == 0
+    nv.check_status("cuda:0")                    # clean again
+
+
+def test_bounded_wait_runs_out_and_is_reported(nv, native_lib):
+    """A wait that nothing satisfies gives up after its limit (100 000 cycles here, ~50 us), the kernel returns, the
+    status word carries its code and the C ABI reports DW_ERR_DEVICE_STATUS; the context stays usable.  The kernel
+    is the library's self-test: one thread on an mbarrier nobody arrives at, no copy or tensor-core work in flight."""
+    L = native_lib
+    sw = nv.status_word("cuda:0")
+    sw.zero_()
+    st = torch.cuda.current_stream().cuda_stream
+    assert L.dw_mxfp8_selftest_bounded_wait(100000, sw.data_ptr(), st) == 0
+    assert L.dw_mxfp8_check_status(sw.data_ptr(), st) == -4
+    assert int(sw.item()) == 5                   # self-test code, CTA 0
+    with pytest.raises(RuntimeError, match=r"status word 5, CTA 0"):
+        nv.check_status("cuda:0")
+    # the context is intact: a GEMM right after gives the right answer
+    run(nv, 256, 256, 256)

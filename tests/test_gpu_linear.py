@@ -237,6 +237,105 @@ def test_dwlinear_training_step_captured_in_a_cuda_graph(dw):
     _native.check_status()
 
 
+def test_captured_graph_sees_weight_updates(dw):
+    """A forward + backward captured in a CUDA graph re-quantises the weight on every replay, into the module's own
+    persistent buffers: after the weight is changed through ``p.data.copy_`` (which moves no version counter), after a
+    real optimizer step, and after eager forwards in between, a replay equals the eager run on the current weight."""
+    torch.manual_seed(33)
+    m = dw.DWLinear.from_linear(nn.Linear(256, 384, bias=True).cuda().bfloat16())
+    opt = torch.optim.SGD(m.parameters(), lr=0.5)
+    x = torch.randn(512, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    gy = torch.randn(512, 384, device="cuda", dtype=torch.bfloat16)
+
+    def step():
+        x.grad = None
+        m.weight.grad = None
+        m.bias.grad = None
+        y = m(x)
+        y.backward(gy)
+        return y
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            step()
+    torch.cuda.current_stream().wait_stream(side)
+    x.grad = None
+    m.weight.grad = None
+    m.bias.grad = None
+    buffers = [t.data_ptr() for pair in (m._wq_row, m._wq_col) for t in pair]
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        y_static = step()
+    assert [t.data_ptr() for pair in (m._wq_row, m._wq_col) for t in pair] == buffers      # never replaced
+
+    def replay_equals_eager():
+        graph.replay()
+        torch.cuda.synchronize()
+        got = [y_static.clone(), x.grad.clone(), m.weight.grad.clone(), m.bias.grad.clone()]
+        y = step()
+        torch.cuda.synchronize()
+        for a, b in zip(got, [y, x.grad, m.weight.grad, m.bias.grad]):
+            assert torch.equal(a, b)
+        return got[0]
+
+    y0 = replay_equals_eager()
+    new_w = (torch.randn(384, 256, device="cuda") * 0.1).bfloat16()
+    version = m.weight._version
+    m.weight.data.copy_(new_w)                               # master-weight style write: no version bump
+    assert m.weight._version == version
+    y1 = replay_equals_eager()                               # eager run inside also refreshes: see invalidate below
+    assert not torch.equal(y0, y1)
+    step()
+    opt.step()                                               # in-place update under no_grad: version moves
+    y2 = replay_equals_eager()
+    assert not torch.equal(y1, y2)
+    assert [t.data_ptr() for pair in (m._wq_row, m._wq_col) for t in pair] == buffers
+    from deepwell_b200 import _native
+    _native.check_status()
+
+
+def test_data_writes_need_invalidate_or_cache_off(dw):
+    """Outside graph capture the weight operands are refreshed when the parameter's version moves.  A write through
+    ``weight.data`` moves no version: ``invalidate_weight_cache()`` (or ``weight_cache="off"``) makes it visible."""
+    m = dw.DWLinear(64, 96, bias=False).cuda().bfloat16()
+    x = torch.randn(32, 64, device="cuda", dtype=torch.bfloat16)
+    y1 = m(x)
+    m.weight.data.mul_(2.0)
+    m.invalidate_weight_cache()
+    assert torch.equal(m(x).float(), 2 * y1.float())
+    off = dw.DWLinear(64, 96, bias=False, weight_cache="off").cuda().bfloat16()
+    z1 = off(x)
+    off.weight.data.mul_(2.0)                                # no invalidate needed
+    assert torch.equal(off(x).float(), 2 * z1.float())
+
+
+def test_grouped_weight_cache_never_matches_recycled_temporaries(dw):
+    """Weight lists rebuilt from temporaries on every call (fresh tensors, version 0, addresses the allocator may
+    hand out again) must not hit an entry built from other values: the entry keeps its sources alive and is matched by
+    storage identity, not by address."""
+    from deepwell_b200 import cutlass_kernels as ck
+    K, N, G = 256, 256, 2
+    g = torch.Generator("cpu").manual_seed(5)
+    a_list = [torch.randn(256, K, generator=g).bfloat16().cuda() for _ in range(G)]
+    masters = [(torch.randn(N, K, generator=g) * 0.05).cuda() for _ in range(G)]           # fp32 master weights
+    cache = {}
+    outs = []
+    for scale in (1.0, 2.0, 4.0):
+        w_list = [(w * scale).to(torch.bfloat16).t() for w in masters]                      # temporaries, rebuilt each call
+        outs.append([o_.clone() for o_ in ck.mxfp8_grouped_gemm_bf16(a_list, w_list, weight_cache=cache)])
+        del w_list
+    for o1, o2, o4 in zip(*outs):
+        assert torch.equal(o2.float(), 2 * o1.float()) and torch.equal(o4.float(), 4 * o1.float())   # exact in MX
+    # unchanged persistent weights do hit
+    w_keep = [(w).to(torch.bfloat16).t() for w in masters]
+    ck.mxfp8_grouped_gemm_bf16(a_list, w_keep, weight_cache=cache)
+    operand = cache["operand"][0]
+    ck.mxfp8_grouped_gemm_bf16(a_list, [w for w in w_keep], weight_cache=cache)
+    assert cache["operand"][0] is operand
+
+
 def test_blackwell_production_gemm_and_fused_linear_gelu(dw):
     """deepwell.kernels.blackwell_production: BlackwellGEMM.gemm with bias + activation fused in the epilogue equals the
     oracle's activation of the fp32 result (tolerance 1e-2 of the value scale, bf16 output); FusedLinearGELU without

@@ -5,7 +5,9 @@ a binding that has no allocator to ask, cannot give dw_mxfp8_gemm the workspace 
 splits K.  This entry point keeps the partial sums in a fixed array inside the library instead.
 The test calls it straight through the C ABI (ctypes, raw pointers), twice in a row on different
 problems so that the second call finds the first call's leftovers in the shared array, and compares
-each result with dw_mxfp8_gemm run with a caller-provided workspace and the same split count.
+each result with dw_mxfp8_gemm run with a caller-provided workspace and the same split count (the same
+kernel and the same order of additions, so the outputs must be identical bit for bit) and with the CPU
+oracle (within the GEMM tolerance).
 
 The file name sorts last on purpose: a run that stops at the first failure has then already run
 every other test.
@@ -28,6 +30,19 @@ def _operands(nv, M, N, K, seed):
     bias = torch.randn(N, generator=g).bfloat16().cuda()
     d0 = torch.randn(M, N, generator=g).bfloat16().cuda()
     return ac, asf, bc, bsf, bias, d0
+
+
+def _oracle(ops, alpha, beta):
+    """alpha * dq(A) . dq(B)^T + beta * D0 + bias in fp32 on the CPU (the oracle's dequantiser on the operands' bytes)."""
+    import numpy as np
+    from oracle import mx_oracle as o
+    ac, asf, bc, bsf, bias, d0 = ops
+    host = lambda t: t.view(torch.uint8).cpu().numpy()
+    M, K = ac.shape
+    N = bc.shape[0]
+    a = torch.from_numpy(o.dequantize_rowwise(host(ac), o.sf_tiled_to_flat(host(asf), M, K // 32)))
+    b = torch.from_numpy(o.dequantize_rowwise(host(bc), o.sf_tiled_to_flat(host(bsf), N, K // 32)))
+    return (alpha * (a @ b.t()) + beta * d0.float().cpu() + bias.float().cpu()[None, :]).double()
 
 
 def _close(got, ref):
@@ -75,7 +90,8 @@ def test_static_scratch_entry_point_matches_workspace_entry_point(native_lib):
         ref = run_workspace(ops, M, N, K, splits, alpha, beta)
         nv.check_status("cuda:0")
         assert not torch.isnan(got.float()).any()
-        assert _close(got.cpu(), ref.float().cpu()), (M, N, K)
+        assert torch.equal(got.view(torch.int16), ref.view(torch.int16)), (M, N, K)
+        assert _close(got.cpu(), _oracle(ops, alpha, beta)), (M, N, K)
 
     # sizes beyond the fixed array are refused, nothing is launched
     big_m, big_n = 4096, 4096                       # 2 splits x 64 MiB of partial sums > 32 MiB
