@@ -5,7 +5,8 @@ Public surface (names of the reference package ``deepwell``):
     DWLinear                           the module the reference's optimizer leaves as a TODO
     cutlass_kernels                    the extension-module API (csrc/python_bindings.cpp)
     kernels.cutlass_bindings, kernels.registry
-    sharded                            N-sharded (column-parallel) linear over torch.distributed
+    engine.ExecutableModel             its MLP executor (_mlp_with_cutlass, src/deepwell/engine.py:132-209)
+    sharded                            N-sharded (column-parallel) and K-sharded (row-parallel) linear over torch.distributed
 """
 __version__ = "0.1.0"
 

@@ -253,23 +253,27 @@ def gemm_grouped(a_codes: torch.Tensor, a_sf: torch.Tensor, b_codes: torch.Tenso
     return out
 
 
-ACTIVATIONS = {"none": 0, "relu": 1, "gelu": 2, "silu": 3}
+ACTIVATIONS = {"none": 0, "relu": 1, "gelu": 2, "silu": 3, "swiglu": 4}
 
 
 def gemm_fused(a_codes: torch.Tensor, a_sf: torch.Tensor, b_codes: torch.Tensor, b_sf: torch.Tensor,
                bias: Optional[torch.Tensor] = None, activation: str = "none", quantize_out: bool = True,
                write_d: bool = True, alpha: float = 1.0, rule: int = RULE_OCP_FLOOR):
-    """act(alpha * A . B^T + bias) -> (D bf16 or None, codes or None, tiled scales or None).  See dw_mxfp8_gemm_fused."""
+    """act(alpha * A . B^T + bias) -> (D bf16 or None, codes or None, tiled scales or None).  See dw_mxfp8_gemm_fused.
+    activation="swiglu": B is the gate and up weight interleaved by interleave_gate_up(); the outputs have N / 2 columns."""
     for t, n in ((a_codes, "A"), (b_codes, "B"), (a_sf, "A scales"), (b_sf, "B scales")):
         _require_cuda(t, n)
     M, K = a_codes.shape
     N, Kb = b_codes.shape
     if K != Kb:
         raise RuntimeError(f"contraction mismatch: A is [{M},{K}], B is [{N},{Kb}]")
+    if activation == "swiglu" and N % 64:
+        raise RuntimeError("swiglu needs a fused gate+up width that is a multiple of 64")
     dev = a_codes.device
-    d = torch.empty((M, N), dtype=torch.bfloat16, device=dev) if write_d else None
-    codes = torch.empty((M, N), dtype=torch.uint8, device=dev) if quantize_out else None
-    scales = torch.empty(scale_bytes(M, N, SF_TILED), dtype=torch.uint8, device=dev) if quantize_out else None
+    n_out = N // 2 if activation == "swiglu" else N
+    d = torch.empty((M, n_out), dtype=torch.bfloat16, device=dev) if write_d else None
+    codes = torch.empty((M, n_out), dtype=torch.uint8, device=dev) if quantize_out else None
+    scales = torch.empty(scale_bytes(M, n_out, SF_TILED), dtype=torch.uint8, device=dev) if quantize_out else None
     if bias is not None and (bias.dtype != torch.bfloat16 or bias.numel() != N or not bias.is_contiguous()):
         raise RuntimeError("bias must be a contiguous bfloat16 [N] tensor")
     sw = status_word(dev)
@@ -279,6 +283,16 @@ def gemm_fused(a_codes: torch.Tensor, a_sf: torch.Tensor, b_codes: torch.Tensor,
                                          ptr(bias), M, N, K, float(alpha), 0.0, ACTIVATIONS[activation], ptr(codes),
                                          ptr(scales), rule, sw.data_ptr(), _stream(dev)), "dw_mxfp8_gemm_fused")
     return d, (None if codes is None else codes.view(torch.float8_e4m3fn)), scales
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """[F, ...] gate and up weights (or [F] biases) -> the [2 F, ...] operand of the SwiGLU epilogue: groups of 32 gate
+    rows followed by the 32 up rows of the same outputs (DW_ACT_SWIGLU of dw_mxfp8_gemm_fused).  F % 32 == 0."""
+    if gate.shape != up.shape or gate.shape[0] % 32:
+        raise RuntimeError("gate and up must have the same shape, with a multiple of 32 rows")
+    f = gate.shape[0]
+    rest = gate.shape[1:]
+    return torch.stack((gate.reshape(f // 32, 32, *rest), up.reshape(f // 32, 32, *rest)), dim=1).reshape(2 * f, *rest)
 
 
 def check_status(device=None) -> None:

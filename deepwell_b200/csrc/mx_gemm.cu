@@ -46,10 +46,13 @@ struct GemmParams {
     float* partial;
     // Fused epilogue: activation after alpha/beta/bias, and optionally the output quantised row-wise
     // (blocks of 32 along N) as the next GEMM's A operand: codes [M, N] + tiled scales.  d may be null then.
+    // act == DW_ACT_SWIGLU: the N columns are gate/up pairs interleaved in groups of 32 (columns [64 j, 64 j + 32) gate,
+    // [64 j + 32, 64 j + 64) up of output columns [32 j, 32 j + 32)); the outputs (d, q_codes, q_scales) have out_n = N / 2
+    // columns.  Otherwise out_n == N.
     int act, q_rule;
     uint8_t* q_codes;
     uint8_t* q_scales;
-    int64_t q_kt;
+    int64_t q_kt, out_n;
     // Optional tuning counters (the caller's workspace): per CTA, SM cycles each role spent waiting
     //   [0] producer: free stage       [1] MMA issuer: accumulator drained (two tiles back)
     //   [2] MMA issuer: shared accumulator columns drained (previous tile)
@@ -387,6 +390,85 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     for (int v = 0; v < 4; ++v) b[v] = *reinterpret_cast<const uint4*>(bias + bcol + 8 * v);
                 }
             };
+            if (act == DW_ACT_SWIGLU) {
+                // Gate and up columns of the same 32 outputs sit in neighbouring chunks (2 j, 2 j + 1), both in this warp's
+                // half: h = silu(gate) * up in fp32, rounded to bf16 once, then quantised as one MX block of the next
+                // GEMM's A operand.  The pair that holds the shared accumulator columns goes first.
+                const int npairs = ch_count / 2;
+                const int64_t F_ = p.out_n;
+#pragma unroll 1
+                for (int ip = 0; ip < npairs; ++ip) {
+                    const int pr = shared_last ? npairs - 1 - ip : ip;
+                    const int cg = (ch_begin + 2 * pr) * 32;                       // gate chunk; the up chunk follows it
+                    uint32_t rg[32], ru[32];
+                    ptx::tc_ld_32x32b_x32(t_row + cg, rg);
+                    ptx::tc_ld_32x32b_x32(t_row + cg + 32, ru);
+                    ptx::tc_wait_ld();
+                    if (owns_shared && ip == 0) {
+                        ptx::tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) {
+                            if (kCtas == 2) ptx::mbar_arrive_cluster(ovl_bar, 0); else ptx::mbar_arrive(ovl_bar);
+                        }
+                    }
+                    const int64_t ocol = (col0 + cg) >> 1;                         // first of the 32 output columns
+                    const bool in_rows = row < M_;
+                    if (ocol + 32 <= F_) {
+                        uint32_t o[16];
+                        if (in_rows) {
+                            float h[32];
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) {
+                                float gv = __uint_as_float(rg[i]) * p.alpha, uv = __uint_as_float(ru[i]) * p.alpha;
+                                if (bias != nullptr) {
+                                    gv += __uint_as_float(static_cast<uint32_t>(bias[col0 + cg + i]) << 16);
+                                    uv += __uint_as_float(static_cast<uint32_t>(bias[col0 + cg + 32 + i]) << 16);
+                                }
+                                h[i] = apply_activation(gv, DW_ACT_SILU) * uv;
+                            }
+#pragma unroll
+                            for (int i = 0; i < 16; ++i)
+                                asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(o[i]) : "f"(h[2 * i + 1]), "f"(h[2 * i]));
+                            if (p.d != nullptr && !p.tma_store) {
+                                uint16_t* dst = p.d + row * F_ + ocol;
+#pragma unroll
+                                for (int v = 0; v < 4; ++v)
+                                    *reinterpret_cast<uint4*>(dst + 8 * v) = make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
+                            }
+                        }
+                        if (p.tma_store && row - lane < M_) stage_and_store(o, in_rows, ocol, row - lane);
+                        if (p.q_codes != nullptr) {
+                            if (in_rows) {
+                                const uint32_t sb = e8m0_from_amax(fold_amax(amax_words(o)), p.q_rule);
+                                const uint32_t inv = e8m0_inverse_bf16x2(sb);
+                                uint32_t q[8];
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) q[i] = quant_word(o[2 * i], inv) | (quant_word(o[2 * i + 1], inv) << 16);
+                                uint8_t* qd = p.q_codes + row * F_ + ocol;
+                                if ((reinterpret_cast<uintptr_t>(qd) & 31) == 0) {
+                                    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(qd), "r"(q[0]), "r"(q[1]),
+                                                 "r"(q[2]), "r"(q[3]), "r"(q[4]), "r"(q[5]), "r"(q[6]), "r"(q[7]) : "memory");
+                                } else {
+                                    stg_v4(qd, make_uint4(q[0], q[1], q[2], q[3]));
+                                    stg_v4(qd + 16, make_uint4(q[4], q[5], q[6], q[7]));
+                                }
+                                p.q_scales[sf_tiled_offset(row, ocol >> 5, p.q_kt)] = static_cast<uint8_t>(sb);
+                            } else if (row < ((M_ + 127) & ~int64_t(127))) {
+                                p.q_scales[sf_tiled_offset(row, ocol >> 5, p.q_kt)] = 127;         // padding rows of the last tile
+                            }
+                        }
+                    } else if (p.q_codes != nullptr && ocol < ((F_ + 127) & ~int64_t(127)) && row < ((M_ + 127) & ~int64_t(127))) {
+                        p.q_scales[sf_tiled_offset(row, ocol >> 5, p.q_kt)] = 127;                 // padding k-blocks of the scale tile
+                    }
+                }
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    if (kCtas == 2) ptx::mbar_arrive_cluster(acce_bar(acc), 0); else ptx::mbar_arrive(acce_bar(acc));
+                }
+                if (++acc == kAcc) { acc = 0; acc_phase ^= 1u; }
+                continue;
+            }
             uint4 bias_next[4] = {};
             load_bias(0, bias_next);
 #pragma unroll 1
@@ -727,9 +809,9 @@ static int launch_gemm(const void* a, const void* a_sf, const void* b, const voi
         return DW_ERR_LAUNCH;
     // D goes out by TMA when its rows are 16-byte multiples (the tensor map's stride rule) and it is
     // written by the GEMM kernel itself (not by the split-K reduction)
-    p.tma_store = (p.d != nullptr && p.splits <= 1 && p.N % 8 == 0 && !pw.direct_stores) ? 1 : 0;
+    p.tma_store = (p.d != nullptr && p.splits <= 1 && p.N % 8 == 0 && p.out_n % 8 == 0 && !pw.direct_stores) ? 1 : 0;
     if (p.tma_store) {
-        if (!get_map(&tm_d, p.d, p.M, p.N, 32, kMapOutput)) return DW_ERR_LAUNCH;
+        if (!get_map(&tm_d, p.d, p.M, p.out_n, 32, kMapOutput)) return DW_ERR_LAUNCH;
     } else {
         tm_d = tm_a;                                        // unused by the kernel
     }
@@ -843,7 +925,8 @@ static int run_gemm(const void* a_codes, const void* a_sf, const void* b_codes, 
     GemmParams p = {};
     p.act = fo.act; p.q_rule = fo.rule;
     p.q_codes = static_cast<uint8_t*>(fo.codes); p.q_scales = static_cast<uint8_t*>(fo.scales);
-    p.q_kt = (N / 32 + 3) / 4;
+    p.out_n = fo.act == DW_ACT_SWIGLU ? N / 2 : N;
+    p.q_kt = (p.out_n / 32 + 3) / 4;
     p.d = static_cast<uint16_t*>(d_bf16);
     p.bias = static_cast<const uint16_t*>(bias_bf16);
     p.status = static_cast<int*>(status_word);
@@ -939,7 +1022,9 @@ extern "C" DW_API int dw_mxfp8_gemm_fused(const void* a_codes, const void* a_sf,
                                           float beta, int activation, void* out_codes, void* out_scales, int scale_rule,
                                           void* status_word, void* stream) {
     if (M < 0 || N < 0 || K < 0) return DW_ERR_BAD_ARG;
-    if (activation < DW_ACT_NONE || activation > DW_ACT_SILU) return DW_ERR_BAD_ARG;
+    if (activation < DW_ACT_NONE || activation > DW_ACT_SWIGLU) return DW_ERR_BAD_ARG;
+    // gate/up pairs: whole groups of 64 fused columns, and no accumulation into a previous D
+    if (activation == DW_ACT_SWIGLU && (N % 64 != 0 || beta != 0.0f)) return DW_ERR_BAD_ARG;
     if (scale_rule != DW_RULE_OCP_FLOOR && scale_rule != DW_RULE_REF_CEIL) return DW_ERR_BAD_ARG;
     if ((out_codes == nullptr) != (out_scales == nullptr)) return DW_ERR_BAD_ARG;
     if (d_bf16 == nullptr && out_codes == nullptr) return DW_ERR_BAD_ARG;          // nothing to write
@@ -956,6 +1041,9 @@ extern "C" DW_API int dw_mxfp8_gemm_fused(const void* a_codes, const void* a_sf,
     GemmPlan pl = plan_gemm(M, N, K, pw, di.sms);
     // the scale padding of the quantised output is written per 128-column group: keep column tiles that are multiples of 128
     if (out_codes != nullptr && pl.variant > 4) pl.variant = 3;
+    // gate/up pairs must fall into one epilogue warp's half of a column tile: 128- or 256-wide tiles, and 256-wide ones
+    // when the quantised output's scale tiles (128 output columns) are padded by the tile that owns them
+    if (activation == DW_ACT_SWIGLU && (pl.variant == 5 || pl.variant == 1 || pl.variant == 4)) pl.variant = M <= 128 ? 2 : 3;
     return run_gemm(a_codes, a_sf, b_codes, b_sf, d_bf16, bias_bf16, M, N, K, alpha, beta, pl.variant, 1, nullptr, status_word,
                     pw, di, static_cast<cudaStream_t>(stream), fo);
 }

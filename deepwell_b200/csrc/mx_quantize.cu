@@ -123,6 +123,73 @@ mx_quant_row_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes,
     }
 }
 
+// The same arithmetic for a launch that shares the SMs with a GEMM of another stream (DW_QUANT_BACKGROUND).  The GEMM
+// keeps one CTA of 320 threads x ~168 registers and nearly all shared memory on every SM, which leaves room for about
+// 11 K registers: one CTA of this kernel (128 threads).  To keep HBM busy from that little, each thread has kDeep
+// 32-byte loads in flight (8 x 128 threads x 32 B = 32 KB per SM) instead of two, and CTAs are short-lived: one slab
+// of 128 x kDeep chunks each, so none of them holds an SM the GEMM is waiting for.
+template <int kDeep, bool kWide>
+__global__ void __maxnreg__(88)      // 128 threads x 88 registers: what fits next to the GEMM's CTA
+mx_quant_row_bg_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes, uint8_t* __restrict__ scales,
+                       uint32_t total_chunks, FastDiv cpr, int rule, int layout, int packed_sf) {
+    const uint32_t chunks_per_row = cpr.div;
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t kb_per_row = chunks_per_row >> 1;
+    const int64_t kt = (kb_per_row + 3) >> 2;
+    constexpr uint32_t kSlab = 128u * kDeep;
+    for (uint64_t slab = blockIdx.x; slab * kSlab < total_chunks; slab += gridDim.x) {
+        const uint32_t first = static_cast<uint32_t>(slab * kSlab) + threadIdx.x;     // chunk u of this thread: first + 128 u
+        uint32_t w[kDeep][8];
+#pragma unroll
+        for (int u = 0; u < kDeep; ++u) {
+            const uint32_t idx = first + 128u * u;
+            if (idx < total_chunks && idx >= first) {        // second test guards uint32 wrap-around
+                const uint16_t* p = x + static_cast<int64_t>(idx) * 16;
+                if (kWide) {
+                    ldg_nc_v8(p, w[u]);
+                } else {
+                    const uint4 a = ldg_nc_v4(p), b = ldg_nc_v4(p + 8);
+                    w[u][0] = a.x; w[u][1] = a.y; w[u][2] = a.z; w[u][3] = a.w;
+                    w[u][4] = b.x; w[u][5] = b.y; w[u][6] = b.z; w[u][7] = b.w;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) w[u][i] = 0;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kDeep; ++u) {
+            const uint32_t idx = first + 128u * u;
+            const bool valid = idx < total_chunks && idx >= first;
+            uint32_t m2 = amax_words(w[u]);
+            m2 = absmax_bf16x2(m2, __shfl_xor_sync(0xFFFFFFFFu, m2, 1));
+            const uint32_t sb = e8m0_from_amax(fold_amax(m2), rule);
+            const uint32_t inv = e8m0_inverse_bf16x2(sb);
+            uint4 q;
+            q.x = quant_word(w[u][0], inv) | (quant_word(w[u][1], inv) << 16);
+            q.y = quant_word(w[u][2], inv) | (quant_word(w[u][3], inv) << 16);
+            q.z = quant_word(w[u][4], inv) | (quant_word(w[u][5], inv) << 16);
+            q.w = quant_word(w[u][6], inv) | (quant_word(w[u][7], inv) << 16);
+            if (valid) stg_v4(codes + static_cast<int64_t>(idx) * 16, q);
+            auto sf_offset = [&]() -> int64_t {
+                if (layout != DW_SF_TILED) return idx >> 1;
+                const uint32_t row = cpr.quot(idx);
+                return sf_tiled_offset(row, (idx - row * chunks_per_row) >> 1, kt);
+            };
+            if (packed_sf) {
+                // cols % 128 == 0: lanes 0,2,4,6 of each group of 8 hold k-blocks kb..kb+3 of one row
+                uint32_t pk = sb;
+                pk |= __shfl_down_sync(0xFFFFFFFFu, sb, 2) << 8;
+                pk |= __shfl_down_sync(0xFFFFFFFFu, sb, 4) << 16;
+                pk |= __shfl_down_sync(0xFFFFFFFFu, sb, 6) << 24;
+                if (valid && (lane & 7u) == 0u) *reinterpret_cast<uint32_t*>(scales + sf_offset()) = pk;
+            } else if (valid && (lane & 1u) == 0u) {
+                scales[sf_offset()] = static_cast<uint8_t>(sb);
+            }
+        }
+    }
+}
+
 // Writes 127 into the padding bytes of a tiled scale buffer that mx_quant_row_kernel does not
 // touch (rows beyond `rows` in the last row tile, k-blocks beyond `kb` in the last k tile).
 __global__ void mx_sf_pad_kernel(uint8_t* __restrict__ scales, int64_t rows, int64_t kb, int64_t rt, int64_t kt) {
@@ -462,15 +529,27 @@ static int quantize_row_fast(const uint16_t* x, uint8_t* codes, uint8_t* scales,
     const FastDiv cpr = FastDiv::make(static_cast<uint32_t>(cols / 16));
     const int packed = (cols % 128 == 0) && aligned(scales, 4);
     const int64_t want = (total_chunks + 511) / 512;
-    // Default: a persistent grid that fills every SM (8 CTAs each) and strides over the matrix.  DW_QUANT_BACKGROUND: one
-    // short-lived CTA per 16 KB slab instead, so that a kernel of another stream that needs whole SMs (the GEMM: one
-    // 213 KB CTA per SM) is not kept waiting until a persistent grid retires, and this launch runs in what is left over.
-    const bool background = (flags & DW_QUANT_BACKGROUND) != 0 && total_chunks <= (1ll << 30);
-    const int grid = static_cast<int>(background ? want : std::min<int64_t>(want, static_cast<int64_t>(di.sms) * 8));
+    // Default: a persistent grid that fills every SM (8 CTAs each) and strides over the matrix.  DW_QUANT_BACKGROUND:
+    // mx_quant_row_bg_kernel, short-lived 128-thread CTAs with eight loads in flight per thread, sized to run in what a
+    // GEMM of another stream (one 213 KB, 320-thread CTA per SM) leaves free and never to keep that GEMM waiting for an SM.
+    const bool background = (flags & DW_QUANT_BACKGROUND) != 0;
+    const int grid = static_cast<int>(std::min<int64_t>(want, static_cast<int64_t>(di.sms) * 8));
     if (layout == DW_SF_TILED && (rows % 128 != 0 || (cols / 32) % 4 != 0)) {
         const int64_t nb = cols / 32, rt = (rows + 127) / 128, kt = (nb + 3) / 4;
         mx_sf_pad_kernel<<<static_cast<int>(std::min<int64_t>((rt * kt * 512 + 255) / 256, 4096)), 256, 0, st>>>(
             scales, rows, nb, rt, kt);
+    }
+    if (background) {
+        constexpr int kDeep = 8;
+        const int64_t slabs = (total_chunks + 128 * kDeep - 1) / (128 * kDeep);
+        const unsigned bg_grid = static_cast<unsigned>(std::min<int64_t>(slabs, 1ll << 30));
+        if (aligned(x, 32))
+            mx_quant_row_bg_kernel<kDeep, true><<<bg_grid, 128, 0, st>>>(x, codes, scales, static_cast<uint32_t>(total_chunks),
+                                                                       cpr, rule, layout, packed);
+        else
+            mx_quant_row_bg_kernel<kDeep, false><<<bg_grid, 128, 0, st>>>(x, codes, scales, static_cast<uint32_t>(total_chunks),
+                                                                        cpr, rule, layout, packed);
+        return launch_status();
     }
     if (aligned(x, 32))
         mx_quant_row_kernel<true><<<grid, 256, 0, st>>>(x, codes, scales, static_cast<uint32_t>(total_chunks), cpr, rule,

@@ -164,6 +164,67 @@ class FusedMLP(nn.Module):
         return y.reshape(*lead, self.down.out_features).to(x.dtype)
 
 
+class FusedSwiGLUMLP(nn.Module):
+    """The gated MLP of Llama-style models: down(silu(gate(x)) * up(x)), parameters named as in those models
+    (gate_proj, up_proj, down_proj; no biases).
+
+    Without autograd the whole block is one quantiser launch and two GEMMs.  gate and up are one GEMM against their
+    weights interleaved in groups of 32 rows, whose epilogue (DW_ACT_SWIGLU) forms silu(gate) * up from the fp32
+    accumulators, rounds to bf16 once and writes the result already quantised as the down projection's A operand:
+    neither the [tokens, 2 F] gate/up activations nor the [tokens, F] product ever exist in bf16 in memory, and the
+    quantiser pass over the largest activation of the block is gone.  With autograd the three DWLinear layers run
+    separately (the backward of the gated unit needs gate and up).  ``fuse=False`` forces that path for comparison.
+    Gives EpilogueConfig::Op::BiasSwish (csrc/cutlass_kernels.h:65-77 of the reference, declared and never applied) the
+    gated form this model family needs."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, config: Optional[BlackwellConfig] = None, fuse: bool = True):
+        super().__init__()
+        if hidden_size % 32 or intermediate_size % 32:
+            raise ValueError("hidden_size and intermediate_size must be multiples of 32 (the MX block size)")
+        self.config = config or BlackwellConfig()
+        self.fuse = fuse
+        self.gate_proj = DWLinear(hidden_size, intermediate_size, bias=False, dtype=torch.bfloat16)
+        self.up_proj = DWLinear(hidden_size, intermediate_size, bias=False, dtype=torch.bfloat16)
+        self.down_proj = DWLinear(intermediate_size, hidden_size, bias=False, dtype=torch.bfloat16)
+        self._gu_key = None
+        self._gu_operand = None            # interleaved gate+up weight, quantised (persistent buffers)
+
+    def _gate_up_operand(self):
+        g, u = self.gate_proj.weight, self.up_proj.weight
+        key = (g.data_ptr(), g._version, u.data_ptr(), u._version, g.device)
+        if key != self._gu_key or self._gu_operand is None:
+            fused = nv.interleave_gate_up(g.detach().to(torch.bfloat16), u.detach().to(torch.bfloat16)).contiguous()
+            if self._gu_operand is None or self._gu_operand[0].device != fused.device:
+                n, k = fused.shape
+                self._gu_operand = (torch.empty(n, k, dtype=torch.uint8, device=fused.device),
+                                    torch.empty(nv.scale_bytes(n, k, nv.SF_TILED), dtype=torch.uint8, device=fused.device))
+            nv.quantize_into(fused, self._gu_operand[0], self._gu_operand[1], nv.DIR_ROW, self.gate_proj.scale_rule, nv.SF_TILED)
+            self._gu_key = key
+        return self._gu_operand
+
+    def invalidate_weight_cache(self) -> None:
+        """After a write through ``weight.data`` (see DWLinear.invalidate_weight_cache)."""
+        self._gu_key = None
+        for m in (self.gate_proj, self.up_proj, self.down_proj):
+            m.invalidate_weight_cache()
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if not x.is_cuda:
+            raise RuntimeError("FusedSwiGLUMLP runs on CUDA (sm_100a) only; there is no CPU path")
+        needs_grad = torch.is_grad_enabled() and (x.requires_grad or any(p.requires_grad for p in self.parameters()))
+        if needs_grad or not self.fuse:
+            return self.down_proj(F.silu(self.gate_proj(x)) * self.up_proj(x))
+        lead = x.shape[:-1]
+        x2d = x.reshape(-1, self.gate_proj.in_features).to(torch.bfloat16)
+        gu_codes, gu_sf = self._gate_up_operand()
+        (dw_, ds), _ = self.down_proj._quantized_weight(need_col=False)
+        xc, xs = nv.quantize(x2d, nv.DIR_ROW, self.gate_proj.scale_rule, nv.SF_TILED)
+        _, hc, hs = nv.gemm_fused(xc, xs, gu_codes, gu_sf, activation="swiglu", quantize_out=True, write_d=False,
+                                  rule=self.gate_proj.scale_rule)
+        y = nv.gemm(hc, hs, dw_, ds)
+        return y.reshape(*lead, self.down_proj.out_features).to(x.dtype)
+
+
 class FusedLayerNormLinear(nn.Module):
     """LayerNorm followed by an MXFP8 linear layer.  The normalisation is torch's; the linear layer is DWLinear (the
     reference's class of this name computes both with torch, src/deepwell/kernels/blackwell_production.py:554-575)."""

@@ -149,6 +149,16 @@ int dw_mxfp8_gemm(const void *a_codes, const void *a_sf, const void *b_codes, co
 #define DW_ACT_RELU 1
 #define DW_ACT_GELU 2   /* exact: 0.5 x (1 + erf(x / sqrt 2)) */
 #define DW_ACT_SILU 3
+/* DW_ACT_SWIGLU: the gated unit of a Llama-style MLP in the epilogue of the fused gate+up projection.  B holds the
+ * gate and the up weight with their rows interleaved in groups of 32: rows [64 j, 64 j + 32) are gate rows
+ * [32 j, 32 j + 32), rows [64 j + 32, 64 j + 64) are the up rows of the same outputs (bias, if any, interleaved the
+ * same way).  N is the fused width (a multiple of 64); the outputs have N / 2 columns:
+ *     h[m, f] = silu(alpha * gate[m, f] + bias_g[f]) * (alpha * up[m, f] + bias_u[f])      (fp32, rounded to bf16 once)
+ * d_bf16 is [M, N/2] (may be NULL), out_codes [M, N/2] and out_scales the DW_SF_TILED scales of an [M, (N/2)/32]
+ * operand: exactly dw_mxfp8_quantize(DW_DIR_ROW) of h, i.e. the down projection's A operand.  The 2 x [M, N/2] bf16
+ * gate and up activations never exist in memory.  beta must be 0.  Body of EpilogueConfig::Op::BiasSwish
+ * (csrc/cutlass_kernels.h:65-77) in the gated form the Llama shapes of the target need. */
+#define DW_ACT_SWIGLU 4
 int dw_mxfp8_gemm_fused(const void *a_codes, const void *a_sf, const void *b_codes, const void *b_sf,
                         void *d_bf16, const void *bias_bf16, int64_t M, int64_t N, int64_t K, float alpha,
                         float beta, int activation, void *out_codes, void *out_scales, int scale_rule,

@@ -284,6 +284,58 @@ def test_fused_epilogue_activation_and_quantised_output(nv, act, shape):
     assert d2 is None and torch.equal(codes2.view(torch.uint8), codes.view(torch.uint8)) and torch.equal(scales2, scales)
 
 
+@pytest.mark.parametrize("shape", [(384, 512, 256), (300, 320, 96), (129, 1024 + 64, 160), (2048, 2048, 512)])
+@pytest.mark.parametrize("variant", [0, 2, 3])
+def test_swiglu_epilogue(nv, shape, variant):
+    """dw_mxfp8_gemm_fused(DW_ACT_SWIGLU): gate and up rows interleaved in groups of 32, h = silu(gate) * up formed from
+    the fp32 accumulators.  The bf16 h is within the GEMM tolerance of silu(g) * u computed from the oracle's fp32 GEMM,
+    and the quantised output (codes, tiled scales, padding bytes) is bit for bit the oracle's row-wise quantisation of
+    that bf16 h, with and without the bf16 copy being written.  Shapes cover ragged row tiles, F not a multiple of 128
+    (padded scale k-blocks) and several column tiles; variants the single-CTA and the CTA-pair kernel."""
+    M, F2, K = shape
+    Fh = F2 // 2
+    nv.set_gemm_variant(variant)
+    g = torch.Generator("cpu").manual_seed(M + F2 + K)
+    x = torch.randn(M, K, generator=g).bfloat16().cuda()
+    wg = (torch.randn(Fh, K, generator=g) * 0.1).bfloat16().cuda()
+    wu = (torch.randn(Fh, K, generator=g) * 0.1).bfloat16().cuda()
+    w = nv.interleave_gate_up(wg, wu).contiguous()
+    assert torch.equal(w[:32], wg[:32]) and torch.equal(w[32:64], wu[:32]) and torch.equal(w[64:96], wg[32:64])
+    xc, xs = nv.quantize(x, nv.DIR_ROW, 0, nv.SF_TILED)
+    wc, ws = nv.quantize(w, nv.DIR_ROW, 0, nv.SF_TILED)
+    h, codes, scales = nv.gemm_fused(xc, xs, wc, ws, activation="swiglu")
+    nv.check_status()
+    nv.set_gemm_variant(0)
+    assert h.shape == (M, Fh) and codes.shape == (M, Fh)
+    gate, up = oracle_gemm(nv, x, wg), oracle_gemm(nv, x, wu)
+    assert_close(h.cpu(), torch.nn.functional.silu(gate) * up)
+    bits = h.cpu().view(torch.int16).numpy().view(np.uint16)
+    ec, es = o.quantize_rowwise(bits)
+    assert np.array_equal(host(codes), ec)
+    assert np.array_equal(host(scales), o.sf_flat_to_tiled(es))
+    nv.set_gemm_variant(variant)
+    h2, codes2, scales2 = nv.gemm_fused(xc, xs, wc, ws, activation="swiglu", write_d=False)
+    nv.check_status()
+    nv.set_gemm_variant(0)
+    assert h2 is None and torch.equal(codes2.view(torch.uint8), codes.view(torch.uint8)) and torch.equal(scales2, scales)
+    # per-thread stores instead of TMA stores for the bf16 copy: same bits
+    nv.set_gemm_variant(variant, direct_stores=True)
+    h3, _, _ = nv.gemm_fused(xc, xs, wc, ws, activation="swiglu", quantize_out=False)
+    nv.check_status()
+    nv.set_gemm_variant(0)
+    assert torch.equal(h3.view(torch.int16), h.view(torch.int16))
+
+
+def test_swiglu_rejects_bad_arguments(nv, native_lib):
+    p16 = 16
+    L = native_lib
+    args = (p16, p16, p16, p16, p16, None, 128, 96, 128, 1.0)
+    assert L.dw_mxfp8_gemm_fused(*args, 0.0, 4, None, None, 0, None, None) == -1        # fused width not a multiple of 64
+    args = (p16, p16, p16, p16, p16, None, 128, 128, 128, 1.0)
+    assert L.dw_mxfp8_gemm_fused(*args, 1.0, 4, None, None, 0, None, None) == -1        # beta with the gated epilogue
+    assert L.dw_mxfp8_gemm_fused(*args, 0.0, 5, None, None, 0, None, None) == -1        # no such activation
+
+
 def test_fused_mlp_chain_never_stores_the_activation(nv):
     """up-projection with bias + GELU + quantise fused, then the down-projection consumes the codes directly:
     identical bits to GEMM -> bf16 -> quantise -> GEMM."""

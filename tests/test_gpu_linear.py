@@ -269,11 +269,12 @@ def test_captured_graph_sees_weight_updates(dw):
     with torch.cuda.graph(graph):
         y_static = step()
     assert [t.data_ptr() for pair in (m._wq_row, m._wq_col) for t in pair] == buffers      # never replaced
+    static = [y_static, x.grad, m.weight.grad, m.bias.grad]       # the tensors every replay writes (an eager step rebinds .grad)
 
     def replay_equals_eager():
         graph.replay()
         torch.cuda.synchronize()
-        got = [y_static.clone(), x.grad.clone(), m.weight.grad.clone(), m.bias.grad.clone()]
+        got = [t.clone() for t in static]
         y = step()
         torch.cuda.synchronize()
         for a, b in zip(got, [y, x.grad, m.weight.grad, m.bias.grad]):
@@ -372,6 +373,70 @@ def test_blackwell_production_gemm_and_fused_linear_gelu(dw):
     assert ln(x).shape == (300, 128)
     seq = optimize_model_for_blackwell(nn.Sequential(nn.Linear(256, 128), nn.GELU(), nn.Linear(128, 64)).cuda().bfloat16())
     assert isinstance(seq[0], dw.DWLinear) and isinstance(seq[2], dw.DWLinear)
+
+
+def test_fused_swiglu_mlp_equals_the_unfused_layers(dw):
+    """FusedSwiGLUMLP without autograd (gate+up GEMM with the gated epilogue writing the down projection's operand) gives
+    the bits of the three separate MXFP8 layers whenever those round the same way, i.e. within the GEMM tolerance of
+    them always; with autograd it IS the three layers and trains."""
+    from deepwell_b200.kernels.blackwell_production import FusedSwiGLUMLP
+    torch.manual_seed(7)
+    m = FusedSwiGLUMLP(256, 704).cuda()               # F = 704 = 5.5 scale tiles: padded k-blocks on the output
+    x = torch.randn(3, 100, 256, device="cuda", dtype=torch.bfloat16)
+    with torch.no_grad():
+        y_fused = m(x)
+        m.fuse = False
+        y_three = m(x)
+        m.fuse = True
+    assert y_fused.shape == (3, 100, 256)
+    # the unfused path rounds gate and up to bf16 before the product; the fused one keeps them in fp32
+    assert close(y_fused.reshape(-1, 256).cpu(), y_three.float().reshape(-1, 256).cpu(), rtol=3e-2)
+    ref = torch.nn.functional.linear(torch.nn.functional.silu(torch.nn.functional.linear(x.float(), m.gate_proj.weight.float()))
+                                     * torch.nn.functional.linear(x.float(), m.up_proj.weight.float()), m.down_proj.weight.float())
+    assert ((y_fused.float() - ref).norm() / ref.norm()).item() < 0.08        # two quantised layers against fp32
+    xg = x.clone().requires_grad_(True)
+    m(xg).float().pow(2).mean().backward()
+    assert xg.grad is not None and m.gate_proj.weight.grad is not None and m.down_proj.weight.grad is not None
+    with torch.no_grad():                              # a weight update reaches the cached interleaved operand
+        m.gate_proj.weight.mul_(2.0)
+        y2 = m(x)
+    assert not torch.equal(y2, y_fused)
+    from deepwell_b200 import _native
+    _native.check_status()
+
+
+def test_engine_mlp_executor(dw):
+    """ExecutableModel._mlp_with_cutlass (the reference's second caller of the GEMM, src/deepwell/engine.py:132-209):
+    Linear -> GELU -> Linear runs as two GEMMs with the fused epilogue and equals FusedMLP's bits; a lone Linear with a
+    ReLU, layers the path does not cover (LayerNorm, a Linear with odd features) and a 3-D input are handled."""
+    import deepwell
+    from deepwell.engine import ExecutableModel
+    from deepwell_b200.kernels.blackwell_production import FusedMLP
+    torch.manual_seed(3)
+    fm = FusedMLP(128, 512, activation="gelu").cuda()
+    mlp = nn.Sequential(nn.Linear(128, 512), nn.GELU(), nn.Linear(512, 128)).cuda().bfloat16()
+    with torch.no_grad():
+        mlp[0].weight.copy_(fm.up.weight); mlp[0].bias.copy_(fm.up.bias)
+        mlp[2].weight.copy_(fm.down.weight); mlp[2].bias.copy_(fm.down.bias)
+    ex = ExecutableModel(None, mlp)
+    x = torch.randn(4, 40, 128, device="cuda", dtype=torch.bfloat16)
+    with torch.no_grad():
+        want = fm(x)
+    got = ex._mlp_with_cutlass(x, mlp, 0)
+    assert got.shape == (4, 40, 128) and torch.equal(got, want)
+    assert torch.equal(ex._mlp_with_cutlass(x, mlp, 0), want)                 # cached weight operands
+    with torch.no_grad():
+        mlp[0].weight.mul_(2.0)
+    assert not torch.equal(ex._mlp_with_cutlass(x, mlp, 0), want)             # ... follow the parameter
+    odd = nn.Sequential(nn.LayerNorm(128), nn.Linear(128, 96), nn.ReLU(), nn.Linear(96, 50)).cuda().bfloat16()
+    got = ex._mlp_with_cutlass(x, odd, 1)
+    with torch.no_grad():
+        ref = odd(x)
+    assert got.shape == ref.shape
+    assert ((got.float() - ref.float()).norm() / ref.float().norm()).item() < 0.06
+    assert torch.equal(ex(x), mlp(x))                                          # forward runs the original model
+    from deepwell_b200 import _native
+    _native.check_status()
 
 
 def test_fused_mlp_inference_equals_the_unfused_layers(dw):

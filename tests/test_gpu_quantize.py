@@ -44,6 +44,12 @@ def check_all_forms(nv, x, rule):
         exp_ts = ets if layout == nv.SF_FLAT else o.sf_flat_to_tiled(ets)
         gc, gs = nv.quantize(x, nv.DIR_ROW, rule, layout)
         assert np.array_equal(host(gc), er) and np.array_equal(host(gs).reshape(exp_rs.shape), exp_rs)
+        # the launch shape for running underneath a GEMM (DW_QUANT_BACKGROUND): same bytes
+        bc, bs = torch.zeros_like(gc.view(torch.uint8)), torch.full_like(gs.view(torch.uint8), 127)
+        rows, cols = x.shape
+        nv.check(nv.load().dw_mxfp8_quantize_ex(x.data_ptr(), bc.data_ptr(), bs.data_ptr(), rows, cols, nv.DIR_ROW, rule, layout,
+                                                nv.QUANT_BACKGROUND, torch.cuda.current_stream().cuda_stream), "quantize_ex")
+        assert np.array_equal(host(bc), er) and np.array_equal(host(bs).reshape(exp_rs.shape), exp_rs)
         gc, gs = nv.quantize(x, nv.DIR_COL_T, rule, layout)
         assert np.array_equal(host(gc), et) and np.array_equal(host(gs).reshape(exp_ts.shape), exp_ts)
         gc, gs = nv.quantize(x, nv.DIR_COL, rule, layout)
