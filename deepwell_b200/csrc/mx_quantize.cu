@@ -19,6 +19,7 @@
 // All arithmetic is on bit patterns; no fast-math; results are bit-exact against the oracle.
 
 #include <algorithm>
+#include <atomic>
 #include <mutex>
 
 #include "dw_common.cuh"
@@ -212,11 +213,17 @@ __global__ void mx_sf_pad_kernel(uint8_t* __restrict__ scales, int64_t rows, int
 // or the four blocks of two consecutive rows, land in 8 different 16-byte bank groups.
 __device__ __forceinline__ uint32_t tile_chunk(uint32_t c, uint32_t r) { return c ^ (r & 7u) ^ ((c >> 3) << 1); }
 
+constexpr int64_t kStagedFromRows = 1ll << 19;     // transposed rows 512 KiB apart and more: staged write-out
 constexpr int kTileSmemBytes = 2 * 128 * 16 * 16 + 1024 + 2048;   // two 32 KB tiles + two 512-byte scale staging areas + column sums
 
 // kColSum: also leave the fp32 sum of every column over this tile's 128 rows in colsum_partial[tile row][column]
 // (the bias gradient of a linear layer is the column sum of the output gradient that is being quantised here).
-template <bool kDoRow, bool kDoCol, bool kColSum = false>
+// kStaged: the transposed payload of a tile (128 output rows x 128 bytes) is first collected in the tile buffer the
+// column pass has just read, then written out by whole 128-byte row segments, four output rows per store instruction.
+// The direct form writes each thread's 32 codes straight from registers: a warp's store then touches 32 different
+// output rows, `rows` bytes apart.  Once that stride reaches the page size (rows >= 2^20 or so) every store instruction
+// needs 32 address translations and the kernel falls to half its rate; staged, it needs four.
+template <bool kDoRow, bool kDoCol, bool kColSum = false, bool kStaged = false>
 __global__ void __launch_bounds__(256)
 mx_quant_tile_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes_row, uint8_t* __restrict__ scales_row,
                      uint8_t* __restrict__ codes_col_t, uint8_t* __restrict__ scales_col, int64_t rows, int64_t cols,
@@ -358,7 +365,29 @@ mx_quant_tile_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes
             qb[i] = __byte_perm(cb[0], cb[1], 0x5410);
         }
         const int64_t gcol = c0 + 2 * p, grow = r0 + rb * 32;
-        if (grow < rows) {
+        if (kStaged) {
+            // stage[c][128 bytes]: the 16-byte piece j of output row c sits at piece j ^ ((c >> 1) & 7), which spreads a
+            // warp's stores (32 different rows, same pieces) over all banks
+            __syncthreads();                                   // every thread has read its part of the tile
+            uint8_t* stage = tile_smem + buf * (128 * 16 * 16);
+            const uint32_t sw = p & 7u;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint32_t piece = (2 * rb + h) ^ sw;
+                *reinterpret_cast<uint4*>(stage + (2 * p) * 128 + piece * 16) = make_uint4(qa[4 * h], qa[4 * h + 1], qa[4 * h + 2], qa[4 * h + 3]);
+                *reinterpret_cast<uint4*>(stage + (2 * p + 1) * 128 + piece * 16) = make_uint4(qb[4 * h], qb[4 * h + 1], qb[4 * h + 2], qb[4 * h + 3]);
+            }
+            __syncthreads();
+            const uint32_t warp = t >> 5, lane = t & 31u;
+            const int64_t row_bytes = (rows - r0) < 128 ? (rows - r0) : 128;      // valid bytes of every output row of this tile
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t c = i * 32 + warp * 4 + (lane >> 3), j = lane & 7u;
+                const uint4 v = *reinterpret_cast<const uint4*>(stage + c * 128 + ((j ^ ((c >> 1) & 7u)) * 16));
+                if (c0 + c < cols && static_cast<int64_t>(j) * 16 < row_bytes)
+                    stg_v4(codes_col_t + (c0 + c) * rows + r0 + j * 16, v);
+            }
+        } else if (grow < rows) {
             // 32 codes of one column = one whole 32-byte sector: a single 256-bit store when the payload allows
             auto store32 = [&](uint8_t* d, const uint32_t (&q)[8]) {
                 if (wide_cols) {
@@ -560,17 +589,19 @@ static int quantize_row_fast(const uint16_t* x, uint8_t* codes, uint8_t* scales,
     return launch_status();
 }
 
-template <bool kDoRow, bool kDoCol, bool kColSum = false>
-static int launch_tile_kernel(const uint16_t* x, uint8_t* cr, uint8_t* sr, uint8_t* ct, uint8_t* sc, int64_t rows, int64_t cols,
-                              uint32_t tiles_c, uint32_t tiles, int rule, int layout, const DeviceInfo& di, cudaStream_t st,
-                              float* colsum_partial = nullptr) {
+static std::atomic<int> g_quant_tuning{0};     // dw_mxfp8_quantize_set_tuning
+
+template <bool kDoRow, bool kDoCol, bool kColSum = false, bool kStaged = false>
+static int launch_tile_kernel_impl(const uint16_t* x, uint8_t* cr, uint8_t* sr, uint8_t* ct, uint8_t* sc, int64_t rows, int64_t cols,
+                                   uint32_t tiles_c, uint32_t tiles, int rule, int layout, const DeviceInfo& di, cudaStream_t st,
+                                   float* colsum_partial = nullptr) {
     {   // the opt-in to more than 48 KB of dynamic shared memory is a per-device attribute of the kernel
         static std::mutex mu;
         static bool done[kMaxDevices] = {};
         std::lock_guard<std::mutex> lock(mu);
         if (!done[di.device]) {
-            if (cudaFuncSetAttribute(mx_quant_tile_kernel<kDoRow, kDoCol, kColSum>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     kTileSmemBytes) != cudaSuccess) {
+            if (cudaFuncSetAttribute(mx_quant_tile_kernel<kDoRow, kDoCol, kColSum, kStaged>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, kTileSmemBytes) != cudaSuccess) {
                 cudaGetLastError();
                 return DW_ERR_LAUNCH;
             }
@@ -578,9 +609,24 @@ static int launch_tile_kernel(const uint16_t* x, uint8_t* cr, uint8_t* sr, uint8
         }
     }
     const uint32_t grid = std::min<uint32_t>(tiles, static_cast<uint32_t>(di.sms) * 3u);   // 3 CTAs of 65 KB per SM
-    mx_quant_tile_kernel<kDoRow, kDoCol, kColSum><<<grid, 256, kTileSmemBytes, st>>>(x, cr, sr, ct, sc, rows, cols, tiles_c, tiles,
-                                                                                    rule, layout, colsum_partial);
+    mx_quant_tile_kernel<kDoRow, kDoCol, kColSum, kStaged><<<grid, 256, kTileSmemBytes, st>>>(x, cr, sr, ct, sc, rows, cols, tiles_c,
+                                                                                             tiles, rule, layout, colsum_partial);
     return launch_status();
+}
+
+// Staged write-out of the transposed payload where its row stride would cost an address translation per lane
+// (see mx_quant_tile_kernel); the codes need 16-byte alignment of every output row for it (rows % 16 == 0 holds: rows % 32 == 0).
+template <bool kDoRow, bool kDoCol, bool kColSum = false>
+static int launch_tile_kernel(const uint16_t* x, uint8_t* cr, uint8_t* sr, uint8_t* ct, uint8_t* sc, int64_t rows, int64_t cols,
+                              uint32_t tiles_c, uint32_t tiles, int rule, int layout, const DeviceInfo& di, cudaStream_t st,
+                              float* colsum_partial = nullptr) {
+    const int mode = g_quant_tuning.load(std::memory_order_relaxed) & 3;           // 0 automatic, 1 never staged, 2 always
+    const bool staged = kDoCol && (mode == 2 || (mode == 0 && rows >= kStagedFromRows));
+    if (staged)
+        return launch_tile_kernel_impl<kDoRow, kDoCol, kColSum, true>(x, cr, sr, ct, sc, rows, cols, tiles_c, tiles, rule, layout, di,
+                                                                      st, colsum_partial);
+    return launch_tile_kernel_impl<kDoRow, kDoCol, kColSum, false>(x, cr, sr, ct, sc, rows, cols, tiles_c, tiles, rule, layout, di, st,
+                                                                   colsum_partial);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -723,6 +769,12 @@ mx_colsum_reduce_kernel(const float* __restrict__ partial, int64_t tiles_r, int6
     } else {
         static_cast<float*>(out)[c] = acc;
     }
+}
+
+extern "C" DW_API int dw_mxfp8_quantize_set_tuning(int word) {
+    if (word < 0 || (word & 3) == 3 || (word >> 2) != 0) return DW_ERR_BAD_ARG;
+    g_quant_tuning.store(word, std::memory_order_relaxed);
+    return DW_OK;
 }
 
 extern "C" DW_API size_t dw_mxfp8_colsum_workspace(int64_t rows, int64_t cols) {

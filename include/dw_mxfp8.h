@@ -81,6 +81,12 @@ int dw_mxfp8_quantize(const void *x_bf16, void *codes, void *scales, int64_t row
 int dw_mxfp8_quantize_ex(const void *x_bf16, void *codes, void *scales, int64_t rows, int64_t cols,
                          int direction, int scale_rule, int scale_layout, int flags, void *stream);
 
+/* Tuning switch of the column-wise (transposed-payload) kernel, process-wide: bits [0,2) = 0 automatic (the transposed
+ * payload is written through a shared-memory staging buffer, whole 128-byte row segments per store, when its rows are
+ * 512 KiB apart or more, i.e. rows >= 2^19; straight from registers otherwise), 1 never staged, 2 always staged.  Same
+ * bytes either way.  For measurements; the reference has no column-wise kernel (csrc/mxfp8_quantization.cu:216-226 is empty). */
+int dw_mxfp8_quantize_set_tuning(int word);
+
 /* One read of x, both operand forms: row-wise (codes_row [rows, cols]) and column-wise
  * transposed (codes_col_t [cols, rows]).  Either output pair may be NULL.
  * Counterpart of MicroscaleManager::transpose_mxfp8 (csrc/cutlass_kernels.cpp:412-424, empty). */
