@@ -747,8 +747,6 @@ def main():
     ap.add_argument("--emulate-world", type=int, default=0,
                     help="tuning aid: on one GPU, run the shard sizes rank 0 would get in a job of this many GPUs")
     ap.add_argument("--serial", action="store_true", help="quantise and GEMM on one stream (no overlap between layers)")
-    ap.add_argument("--quant-persistent", action="store_true",
-                    help="second-stream quantiser launches as persistent grids (default: DW_QUANT_BACKGROUND, short-lived blocks)")
     ap.add_argument("--profile-case", default=None, choices=["gemm", "quant_row", "quant_both", "quant_col"],
                     help="run a few launches of one kernel on a small case (for an ncu capture) and exit")
     ap.add_argument("--workload", default="linears", choices=["linears", "decoder_step"],
@@ -828,17 +826,15 @@ def main():
         l["consumed"] = torch.cuda.Event()             # the GEMM that read them has finished
     gemm_events = []
 
-    qflags = nv.QUANT_BACKGROUND if (qstream is not stream and not args.quant_persistent) else 0
-
     def step(record: bool, after_gemm=None):
         launches = 0
         for l in layers:
             if qstream is not stream:
                 qstream.wait_event(l["consumed"])      # do not overwrite operands a GEMM may still read
-            nv.check(L.dw_mxfp8_quantize_ex(l["x"].data_ptr(), l["xc"].data_ptr(), l["xs"].data_ptr(), M_TOKENS, l["k"],
-                                            nv.DIR_ROW, nv.RULE_OCP_FLOOR, nv.SF_TILED, qflags, sq), "quantize X")
-            nv.check(L.dw_mxfp8_quantize_ex(l["w"].data_ptr(), l["wc"].data_ptr(), l["ws"].data_ptr(), l["n"], l["k"],
-                                            nv.DIR_ROW, nv.RULE_OCP_FLOOR, nv.SF_TILED, qflags, sq), "quantize W")
+            nv.check(L.dw_mxfp8_quantize(l["x"].data_ptr(), l["xc"].data_ptr(), l["xs"].data_ptr(), M_TOKENS, l["k"],
+                                         nv.DIR_ROW, nv.RULE_OCP_FLOOR, nv.SF_TILED, sq), "quantize X")
+            nv.check(L.dw_mxfp8_quantize(l["w"].data_ptr(), l["wc"].data_ptr(), l["ws"].data_ptr(), l["n"], l["k"],
+                                         nv.DIR_ROW, nv.RULE_OCP_FLOOR, nv.SF_TILED, sq), "quantize W")
             if qstream is not stream:
                 l["quantised"].record(qstream)
                 stream.wait_event(l["quantised"])
@@ -1121,8 +1117,7 @@ def main():
                 "config": {"workload": WORKLOAD, "M": M_TOKENS, "layers": {n: [k, nn] for n, k, nn in LAYERS},
                            "parallelism": f"N-sharded x{world}, X replicated, no data-path collective",
                            "step": "per layer: quantise X, quantise W shard, block-scaled GEMM"
-                                   + ("" if args.serial else "; quantisation of the next layer on a second, lower-priority stream"
-                                      + ("" if args.quant_persistent else " as short-lived thread blocks (DW_QUANT_BACKGROUND)")),
+                                   + ("" if args.serial else "; quantisation of the next layer on a second, lower-priority stream"),
                            "l2": f"inputs larger than L2: {bytes_step / 1e9:.2f} GB touched per step per GPU",
                            "gemm_variant": args.variant,
                            **({"emulated_world": args.emulate_world,

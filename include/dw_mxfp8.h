@@ -71,19 +71,9 @@ size_t dw_mxfp8_scale_bytes(int64_t rows, int64_t k, int scale_layout);
 int dw_mxfp8_quantize(const void *x_bf16, void *codes, void *scales, int64_t rows, int64_t cols,
                       int direction, int scale_rule, int scale_layout, void *stream);
 
-/* dw_mxfp8_quantize with launch flags.  DW_QUANT_BACKGROUND: the launch is meant to run underneath a GEMM that
- * another stream issues (the next layer's operands while this layer multiplies).  The row-wise kernel then uses one
- * short-lived thread block per 16 KB of input instead of a persistent grid that fills every SM, so the GEMM's
- * thread blocks (one per SM, nearly all of its shared memory) get their SMs as soon as they are ready and the
- * quantiser takes what is left.  Same bytes out; the other directions ignore the flag.
- * The reference has one launch shape (one block per 32 elements, csrc/mxfp8_quantization.cu:232-240). */
-#define DW_QUANT_BACKGROUND 1
-int dw_mxfp8_quantize_ex(const void *x_bf16, void *codes, void *scales, int64_t rows, int64_t cols,
-                         int direction, int scale_rule, int scale_layout, int flags, void *stream);
-
 /* Tuning switch of the column-wise (transposed-payload) kernel, process-wide: bits [0,2) = 0 automatic (the transposed
  * payload is written through a shared-memory staging buffer, whole 128-byte row segments per store, when its rows are
- * 512 KiB apart or more, i.e. rows >= 2^19; straight from registers otherwise), 1 never staged, 2 always staged.  Same
+ * 1 MiB apart or more (2 MiB for the fused both-forms call), i.e. rows >= 2^20 (2^21); straight from registers otherwise), 1 never staged, 2 always staged.  Same
  * bytes either way.  For measurements; the reference has no column-wise kernel (csrc/mxfp8_quantization.cu:216-226 is empty). */
 int dw_mxfp8_quantize_set_tuning(int word);
 

@@ -39,7 +39,7 @@ def golden():
 
 
 def config1_inputs():
-    """BASELINE config 1: X [2048,4096] N(0,1) with 1% entries x50, W [4096,4096] N(0,0.02), seed 1234."""
+    """The CPU-reference workload: X [2048,4096] N(0,1) with 1% of the entries x50 (outliers), W [4096,4096] N(0,0.02), seed 1234."""
     import torch
     g = torch.Generator("cpu").manual_seed(1234)
     X = torch.randn(2048, 4096, generator=g)

@@ -44,12 +44,6 @@ def check_all_forms(nv, x, rule):
         exp_ts = ets if layout == nv.SF_FLAT else o.sf_flat_to_tiled(ets)
         gc, gs = nv.quantize(x, nv.DIR_ROW, rule, layout)
         assert np.array_equal(host(gc), er) and np.array_equal(host(gs).reshape(exp_rs.shape), exp_rs)
-        # the launch shape for running underneath a GEMM (DW_QUANT_BACKGROUND): same bytes
-        bc, bs = torch.zeros_like(gc.view(torch.uint8)), torch.full_like(gs.view(torch.uint8), 127)
-        rows, cols = x.shape
-        nv.check(nv.load().dw_mxfp8_quantize_ex(x.data_ptr(), bc.data_ptr(), bs.data_ptr(), rows, cols, nv.DIR_ROW, rule, layout,
-                                                nv.QUANT_BACKGROUND, torch.cuda.current_stream().cuda_stream), "quantize_ex")
-        assert np.array_equal(host(bc), er) and np.array_equal(host(bs).reshape(exp_rs.shape), exp_rs)
         gc, gs = nv.quantize(x, nv.DIR_COL_T, rule, layout)
         assert np.array_equal(host(gc), et) and np.array_equal(host(gs).reshape(exp_ts.shape), exp_ts)
         gc, gs = nv.quantize(x, nv.DIR_COL, rule, layout)
@@ -72,7 +66,8 @@ def test_kat_vectors(nv, golden, rule):
 
 
 @pytest.mark.parametrize("shape", [(128, 128), (256, 512), (96, 160), (32, 96), (33, 64), (1, 32), (7, 50), (129, 4096),
-                                   (4096, 128), (300, 1000), (1, 1), (31, 31), (64, 8), (2048, 1024)])
+                                   (4096, 128), (300, 1000), (1, 1), (31, 31), (64, 8), (2048, 1024),
+                                   (2048 + 3, 1024 + 32), (1031, 2080)])     # the last two: the large-input row kernel, ragged slabs
 @pytest.mark.parametrize("rule", [0, 1])
 def test_shapes_fast_and_ragged(nv, shape, rule):
     g = torch.Generator("cpu").manual_seed(shape[0] * 7919 + shape[1])
