@@ -555,21 +555,6 @@ static int quantize_generic(const uint16_t* x, uint8_t* codes, uint8_t* scales, 
     return launch_status();
 }
 
-// Kernels of this file that may share an SM with the GEMM ask for the GEMM's shared-memory carve-out (all of it shared
-// memory): an SM cannot hold CTAs of kernels whose carve-outs differ, so with the default (L1-heavy) preference these
-// launches would wait for the GEMM's CTAs to retire instead of running beside them.  They use no L1 (ld.global.nc
-// L1::no_allocate) and lose nothing.  Per device, like every function attribute.
-template <typename Kernel>
-static void prefer_shared_carveout(Kernel kernel, bool (&done)[kMaxDevices], const DeviceInfo& di) {
-    static std::mutex mu;
-    std::lock_guard<std::mutex> lock(mu);
-    if (!done[di.device]) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess)
-            cudaGetLastError();                      // a hint: the launch works without it
-        done[di.device] = true;
-    }
-}
-
 static int quantize_row_fast(const uint16_t* x, uint8_t* codes, uint8_t* scales, int64_t rows, int64_t cols, int rule,
                              int layout, const DeviceInfo& di, cudaStream_t st) {
     const int64_t total_chunks = rows * cols / 16;
@@ -589,9 +574,6 @@ static int quantize_row_fast(const uint16_t* x, uint8_t* codes, uint8_t* scales,
         constexpr int kDeep = 8;
         const int64_t slabs = (total_chunks + 128 * kDeep - 1) / (128 * kDeep);
         const unsigned bg_grid = static_cast<unsigned>(std::min<int64_t>(slabs, 1ll << 30));
-        static bool hinted_wide[kMaxDevices] = {}, hinted_narrow[kMaxDevices] = {};
-        if (aligned(x, 32)) prefer_shared_carveout(mx_quant_row_bg_kernel<kDeep, true>, hinted_wide, di);
-        else prefer_shared_carveout(mx_quant_row_bg_kernel<kDeep, false>, hinted_narrow, di);
         if (aligned(x, 32))
             mx_quant_row_bg_kernel<kDeep, true><<<bg_grid, 128, 0, st>>>(x, codes, scales, static_cast<uint32_t>(total_chunks),
                                                                        cpr, rule, layout, packed);
@@ -625,9 +607,6 @@ static int launch_tile_kernel_impl(const uint16_t* x, uint8_t* cr, uint8_t* sr, 
                 cudaGetLastError();
                 return DW_ERR_LAUNCH;
             }
-            if (cudaFuncSetAttribute(mx_quant_tile_kernel<kDoRow, kDoCol, kColSum, kStaged>,
-                                     cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess)
-                cudaGetLastError();                  // a hint
             done[di.device] = true;
         }
     }

@@ -213,6 +213,84 @@ std::tuple<Tensor, Tensor, Tensor> linear_backward(const Tensor& dy_in, const c1
   return {dx, dw, db};
 }
 
+// The linear layer as one autograd node: forward and backward above, with the quantised operands the backward needs
+// (the column-wise form of x for the weight gradient, of W for the input gradient) carried in the node.  `weight` takes
+// part only so that autograd asks for its gradient; the arithmetic reads the quantised operands the caller keeps.
+// Having the node here rather than in Python keeps the interpreter out of the backward pass (a GPT-2-sized layer's
+// kernels take less time than a Python-level backward costs).
+class MXFP8LinearFunction : public torch::autograd::Function<MXFP8LinearFunction> {
+ public:
+  static Tensor forward(torch::autograd::AutogradContext* ctx, const Tensor& x2d, const Tensor& weight,
+                        const c10::optional<Tensor>& bias, const Tensor& w_row_codes, const Tensor& w_row_sf,
+                        const c10::optional<Tensor>& w_col_codes, const c10::optional<Tensor>& w_col_sf, int64_t rule,
+                        const Tensor& status, bool check_status) {
+    const bool grad_mode = c10::GradMode::is_enabled();
+    const bool need_dx = grad_mode && x2d.requires_grad();
+    const bool need_dw = grad_mode && weight.requires_grad();
+    TORCH_CHECK(!need_dx || w_col_codes.has_value(), "the input gradient needs the column-wise weight operand");
+    const Tensor xb = x2d.scalar_type() == torch::kBFloat16 ? x2d : x2d.to(torch::kBFloat16);
+    c10::optional<Tensor> bias_b;
+    if (bias.has_value() && bias->defined())
+      bias_b = bias->scalar_type() == torch::kBFloat16 ? *bias : bias->to(torch::kBFloat16);
+    Tensor y, xc, xcs;
+    std::tie(y, xc, xcs) = linear_forward(xb.detach(), w_row_codes, w_row_sf, bias_b, need_dw, rule, status);
+    ctx->saved_data["m"] = xb.size(0);
+    ctx->saved_data["rule"] = rule;
+    ctx->saved_data["status"] = status;
+    ctx->saved_data["check_status"] = check_status;
+    ctx->saved_data["x_dtype"] = static_cast<int64_t>(x2d.scalar_type());
+    ctx->saved_data["w_dtype"] = static_cast<int64_t>(weight.scalar_type());
+    ctx->saved_data["bias_dtype"] = bias_b.has_value() ? static_cast<int64_t>(bias->scalar_type()) : int64_t(-1);
+    if (need_dw) {
+      ctx->saved_data["x_col_codes"] = xc;
+      ctx->saved_data["x_col_sf"] = xcs;
+    }
+    if (need_dx) {
+      ctx->saved_data["w_col_codes"] = *w_col_codes;
+      ctx->saved_data["w_col_sf"] = *w_col_sf;
+    }
+    return x2d.scalar_type() == torch::kBFloat16 ? y : y.to(x2d.scalar_type());
+  }
+
+  static torch::autograd::variable_list backward(torch::autograd::AutogradContext* ctx,
+                                                 torch::autograd::variable_list grad_outputs) {
+    const Tensor& dy_in = grad_outputs[0];
+    const bool need_dx = ctx->needs_input_grad(0) && ctx->saved_data.count("w_col_codes") > 0;
+    const bool need_dw = ctx->needs_input_grad(1) && ctx->saved_data.count("x_col_codes") > 0;
+    const int64_t bias_dtype = ctx->saved_data["bias_dtype"].toInt();
+    const bool need_db = ctx->needs_input_grad(2) && bias_dtype >= 0;
+    const Tensor dy = dy_in.scalar_type() == torch::kBFloat16 ? dy_in : dy_in.to(torch::kBFloat16);
+    c10::optional<Tensor> w_cc, w_cs, x_cc, x_cs;
+    if (need_dx) { w_cc = ctx->saved_data["w_col_codes"].toTensor(); w_cs = ctx->saved_data["w_col_sf"].toTensor(); }
+    if (need_dw) { x_cc = ctx->saved_data["x_col_codes"].toTensor(); x_cs = ctx->saved_data["x_col_sf"].toTensor(); }
+    // bf16 column sums only for a bf16 bias; fp32 sums otherwise
+    const int64_t db_mode = !need_db ? 0 : (bias_dtype == static_cast<int64_t>(torch::kBFloat16) ? 1 : 2);
+    const Tensor status = ctx->saved_data["status"].toTensor();
+    Tensor dx, dw, db;
+    std::tie(dx, dw, db) = linear_backward(dy, w_cc, w_cs, x_cc, x_cs, ctx->saved_data["m"].toInt(),
+                                           ctx->saved_data["rule"].toInt(), db_mode, status);
+    const auto x_dtype = static_cast<torch::ScalarType>(ctx->saved_data["x_dtype"].toInt());
+    const auto w_dtype = static_cast<torch::ScalarType>(ctx->saved_data["w_dtype"].toInt());
+    if (dx.defined() && dx.scalar_type() != x_dtype) dx = dx.to(x_dtype);
+    if (dw.defined() && dw.scalar_type() != w_dtype) dw = dw.to(w_dtype);
+    if (db.defined() && bias_dtype >= 0 && db.scalar_type() != static_cast<torch::ScalarType>(bias_dtype))
+      db = db.to(static_cast<torch::ScalarType>(bias_dtype));
+    if (ctx->saved_data["check_status"].toBool()) {
+      const c10::cuda::CUDAGuard guard(dy.device());
+      check_rc(dw_mxfp8_check_status(status.data_ptr(), stream_of(dy)), "DWLinear backward");
+    }
+    return {dx, dw, db, Tensor(), Tensor(), Tensor(), Tensor(), Tensor(), Tensor(), Tensor()};
+  }
+};
+
+// y = x2d . W^T + bias with gradients (see MXFP8LinearFunction); the weight's quantised operands come from the caller.
+Tensor linear(const Tensor& x2d, const Tensor& weight, const c10::optional<Tensor>& bias, const Tensor& w_row_codes,
+              const Tensor& w_row_sf, const c10::optional<Tensor>& w_col_codes, const c10::optional<Tensor>& w_col_sf,
+              int64_t rule, const Tensor& status, bool check_status) {
+  return MXFP8LinearFunction::apply(x2d, weight, bias, w_row_codes, w_row_sf, w_col_codes, w_col_sf, rule, status,
+                                    check_status);
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -224,6 +302,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("quantize_both_colsum", &quantize_both_colsum, py::arg("x"), py::arg("rule"), py::arg("layout"), py::arg("sum_bf16"));
   m.def("gemm", &gemm, py::arg("a"), py::arg("a_sf"), py::arg("b"), py::arg("b_sf"), py::arg("out") = py::none(),
         py::arg("bias") = py::none(), py::arg("alpha") = 1.0, py::arg("beta") = 0.0, py::arg("status"), py::arg("plan") = -1);
+  m.def("linear", &linear, py::arg("x2d"), py::arg("weight"), py::arg("bias"), py::arg("w_row_codes"), py::arg("w_row_sf"),
+        py::arg("w_col_codes"), py::arg("w_col_sf"), py::arg("rule"), py::arg("status"), py::arg("check_status") = false);
   m.def("linear_forward", &linear_forward);
   m.def("linear_backward", &linear_backward);
 }

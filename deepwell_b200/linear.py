@@ -42,56 +42,6 @@ from . import _native as nv
 _CHECK_STATUS = os.environ.get("DW_CHECK_STATUS", "0") not in ("", "0")
 
 
-class _MXFP8LinearFn(torch.autograd.Function):
-    """One call into deepwell_b200._C per direction (linear_forward / linear_backward of
-    csrc/python_bindings.cpp): the quantiser and GEMM launches and their output allocations happen
-    there, so the host cost per layer is one Python->C++ transition each way."""
-
-    @staticmethod
-    def forward(ctx, x2d: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], module: "DWLinear"):
-        need_x_grad, need_w_grad = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
-        w_row, w_col = module._quantized_weight(need_col=need_x_grad)
-        bf16 = torch.bfloat16
-        xb = x2d if x2d.dtype is bf16 else x2d.to(bf16)
-        bias_b = bias if bias is None or bias.dtype is bf16 else bias.to(bf16)
-        y, xc_c, xc_s = nv.ext().linear_forward(xb, w_row[0], w_row[1], bias_b, need_w_grad, module.scale_rule,
-                                                nv.status_word(xb.device))
-        ctx.module = module
-        ctx.m = xb.shape[0]
-        ctx.x_dtype, ctx.w_dtype = x2d.dtype, weight.dtype
-        ctx.bias_dtype = None if bias is None else bias.dtype
-        ctx.x_col = (xc_c, xc_s) if need_w_grad else None
-        ctx.w_col = w_col
-        if _CHECK_STATUS and not (need_x_grad or need_w_grad):
-            nv.check_status(xb.device)
-        return y if x2d.dtype is bf16 else y.to(x2d.dtype)
-
-    @staticmethod
-    def backward(ctx, dy: torch.Tensor):
-        module = ctx.module
-        need_dx, need_dw, need_db = ctx.needs_input_grad[:3]
-        bf16 = torch.bfloat16
-        dyb = dy if dy.dtype is bf16 else dy.to(bf16)
-        w_cc = w_cs = x_cc = x_cs = None
-        if need_dx:
-            w_cc, w_cs = ctx.w_col if ctx.w_col is not None else module._quantized_weight(need_col=True)[1]
-        if need_dw:
-            x_cc, x_cs = ctx.x_col
-        need_db = need_db and ctx.bias_dtype is not None
-        db_mode = 0 if not need_db else (1 if ctx.bias_dtype is bf16 else 2)       # bf16 sums only for a bf16 bias
-        dx, dw, db = nv.ext().linear_backward(dyb, w_cc, w_cs, x_cc, x_cs, ctx.m, module.scale_rule, db_mode,
-                                              nv.status_word(dyb.device))
-        if need_dx and ctx.x_dtype is not bf16:
-            dx = dx.to(ctx.x_dtype)
-        if need_dw and ctx.w_dtype is not bf16:
-            dw = dw.to(ctx.w_dtype)
-        if need_db and db.dtype is not ctx.bias_dtype:
-            db = db.to(ctx.bias_dtype)
-        if _CHECK_STATUS:
-            nv.check_status(dyb.device)
-        return dx, dw, db, None
-
-
 class DWLinear(nn.Module):
     """Drop-in for nn.Linear (same parameter names, so state_dicts interchange)."""
 
@@ -179,11 +129,21 @@ class DWLinear(nn.Module):
         return row, col
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """One call into deepwell_b200._C: the autograd node (MXFP8LinearFunction of csrc/python_bindings.cpp) quantises
+        x, runs the GEMM and, in backward, quantises dY and runs the two gradient GEMMs, all without re-entering
+        Python.  The node keeps references to this module's weight operand buffers, not copies: a backward sees the
+        weight as it was last quantised, which is the forward's weight in any loop that does not update the weight
+        between a forward and its backward."""
         if not x.is_cuda:
             raise RuntimeError("DWLinear runs on CUDA (sm_100a) only; there is no CPU path")
         lead = x.shape[:-1]
         x2d = x.reshape(-1, self.in_features)
-        y = _MXFP8LinearFn.apply(x2d, self.weight, self.bias, self)
+        grad = torch.is_grad_enabled()
+        (w_codes, w_sf), w_col = self._quantized_weight(need_col=grad and x2d.requires_grad)
+        y = nv.ext().linear(x2d, self.weight, self.bias, w_codes, w_sf, None if w_col is None else w_col[0],
+                            None if w_col is None else w_col[1], self.scale_rule, nv.status_word(x.device), _CHECK_STATUS)
+        if _CHECK_STATUS and not y.requires_grad:
+            nv.check_status(x.device)
         return y.reshape(*lead, self.out_features)
 
     def extra_repr(self) -> str:

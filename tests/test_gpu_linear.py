@@ -394,7 +394,7 @@ def test_fused_swiglu_mlp_equals_the_unfused_layers(dw):
     assert ((y_fused.float() - y_three.float()).norm() / y_three.float().norm()).item() < 2e-2
     ref = torch.nn.functional.linear(torch.nn.functional.silu(torch.nn.functional.linear(x.float(), m.gate_proj.weight.float()))
                                      * torch.nn.functional.linear(x.float(), m.up_proj.weight.float()), m.down_proj.weight.float())
-    assert ((y_fused.float() - ref).norm() / ref.norm()).item() < 0.08        # two quantised layers against fp32
+    assert ((y_fused.float() - ref).norm() / ref.norm()).item() < 0.15        # five E4M3 roundings (x, gate, up, h, down) against fp32
     xg = x.clone().requires_grad_(True)
     m(xg).float().pow(2).mean().backward()
     assert xg.grad is not None and m.gate_proj.weight.grad is not None and m.down_proj.weight.grad is not None
