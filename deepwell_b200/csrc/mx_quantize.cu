@@ -23,31 +23,13 @@
 #include <mutex>
 
 #include "dw_common.cuh"
+#include "dw_quant_row.cuh"
 
 namespace dw {
 
 // ------------------------------------------------------------------------------------------
 // Row-wise fast path.  cols % 32 == 0.  One thread = 16 consecutive elements (half a block).
 // ------------------------------------------------------------------------------------------
-// Division of a 32-bit index by a run-time constant without a divide instruction
-// (round-up multiplier, Granlund & Montgomery): q = (t + ((n - t) >> 1)) >> shift, t = umulhi(mul, n).
-struct FastDiv {
-    uint32_t mul, shift, div;
-    __host__ static FastDiv make(uint32_t d) {      // d >= 2
-        uint32_t l = 0;
-        while ((1ull << l) < d) ++l;
-        FastDiv f;
-        f.mul = static_cast<uint32_t>(((1ull << 32) * ((1ull << l) - d)) / d + 1);
-        f.shift = l - 1;
-        f.div = d;
-        return f;
-    }
-    __device__ __forceinline__ uint32_t quot(uint32_t n) const {
-        const uint32_t t = __umulhi(mul, n);
-        return (t + ((n - t) >> 1)) >> shift;
-    }
-};
-
 template <bool kWide>  // kWide: 32-byte aligned input -> one 256-bit load per chunk
 __global__ void __launch_bounds__(256)
 mx_quant_row_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes, uint8_t* __restrict__ scales,
@@ -125,71 +107,12 @@ mx_quant_row_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes,
 }
 
 // The same arithmetic with kDeep 32-byte loads in flight per thread instead of two, in short-lived CTAs of 128 threads
-// (one slab of 128 x kDeep chunks each): the kernel for large inputs.  Measured on B200 it runs at the copy bandwidth
-// (16384 x 14336: 107 us against 130 us for the kernel above, 6.6 against 5.4 TB/s).  It is also sized to share an SM
-// with the GEMM of another stream, which keeps one CTA of 320 threads x 168 registers and nearly all shared memory
-// resident: 128 threads x 88 registers is what that leaves, and 8 x 128 x 32 B = 32 KB in flight per SM is enough to
-// keep HBM busy from there; being short-lived, none of its CTAs holds an SM the GEMM is waiting for.
-template <int kDeep, bool kWide>
-__global__ void __maxnreg__(88)      // 128 threads x 88 registers: what fits next to the GEMM's CTA
-mx_quant_row_bg_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes, uint8_t* __restrict__ scales,
-                       uint32_t total_chunks, FastDiv cpr, int rule, int layout, int packed_sf) {
-    const uint32_t chunks_per_row = cpr.div;
-    const uint32_t lane = threadIdx.x & 31u;
-    const uint32_t kb_per_row = chunks_per_row >> 1;
-    const int64_t kt = (kb_per_row + 3) >> 2;
-    constexpr uint32_t kSlab = 128u * kDeep;
-    for (uint64_t slab = blockIdx.x; slab * kSlab < total_chunks; slab += gridDim.x) {
-        const uint32_t first = static_cast<uint32_t>(slab * kSlab) + threadIdx.x;     // chunk u of this thread: first + 128 u
-        uint32_t w[kDeep][8];
-#pragma unroll
-        for (int u = 0; u < kDeep; ++u) {
-            const uint32_t idx = first + 128u * u;
-            if (idx < total_chunks && idx >= first) {        // second test guards uint32 wrap-around
-                const uint16_t* p = x + static_cast<int64_t>(idx) * 16;
-                if (kWide) {
-                    ldg_nc_v8(p, w[u]);
-                } else {
-                    const uint4 a = ldg_nc_v4(p), b = ldg_nc_v4(p + 8);
-                    w[u][0] = a.x; w[u][1] = a.y; w[u][2] = a.z; w[u][3] = a.w;
-                    w[u][4] = b.x; w[u][5] = b.y; w[u][6] = b.z; w[u][7] = b.w;
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) w[u][i] = 0;
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < kDeep; ++u) {
-            const uint32_t idx = first + 128u * u;
-            const bool valid = idx < total_chunks && idx >= first;
-            uint32_t m2 = amax_words(w[u]);
-            m2 = absmax_bf16x2(m2, __shfl_xor_sync(0xFFFFFFFFu, m2, 1));
-            const uint32_t sb = e8m0_from_amax(fold_amax(m2), rule);
-            const uint32_t inv = e8m0_inverse_bf16x2(sb);
-            uint4 q;
-            q.x = quant_word(w[u][0], inv) | (quant_word(w[u][1], inv) << 16);
-            q.y = quant_word(w[u][2], inv) | (quant_word(w[u][3], inv) << 16);
-            q.z = quant_word(w[u][4], inv) | (quant_word(w[u][5], inv) << 16);
-            q.w = quant_word(w[u][6], inv) | (quant_word(w[u][7], inv) << 16);
-            if (valid) stg_v4(codes + static_cast<int64_t>(idx) * 16, q);
-            auto sf_offset = [&]() -> int64_t {
-                if (layout != DW_SF_TILED) return idx >> 1;
-                const uint32_t row = cpr.quot(idx);
-                return sf_tiled_offset(row, (idx - row * chunks_per_row) >> 1, kt);
-            };
-            if (packed_sf) {
-                // cols % 128 == 0: lanes 0,2,4,6 of each group of 8 hold k-blocks kb..kb+3 of one row
-                uint32_t pk = sb;
-                pk |= __shfl_down_sync(0xFFFFFFFFu, sb, 2) << 8;
-                pk |= __shfl_down_sync(0xFFFFFFFFu, sb, 4) << 16;
-                pk |= __shfl_down_sync(0xFFFFFFFFu, sb, 6) << 24;
-                if (valid && (lane & 7u) == 0u) *reinterpret_cast<uint32_t*>(scales + sf_offset()) = pk;
-            } else if (valid && (lane & 1u) == 0u) {
-                scales[sf_offset()] = static_cast<uint8_t>(sb);
-            }
-        }
-    }
+// (one slab of 128 x kDeep chunks each; body in dw_quant_row.cuh): the kernel for large inputs.  Measured on B200 it
+// runs at the copy bandwidth (16384 x 14336: 107 us against 130 us for the kernel above, 6.6 against 5.4 TB/s).
+template <int kDeep>
+__global__ void __maxnreg__(88)      // 128 threads x 88 registers
+mx_quant_row_bg_kernel(const RowQuantJob job) {
+    quant_row_slabs<kDeep>(job, blockIdx.x, gridDim.x, threadIdx.x);
 }
 
 // Writes 127 into the padding bytes of a tiled scale buffer that mx_quant_row_kernel does not
@@ -572,14 +495,10 @@ static int quantize_row_fast(const uint16_t* x, uint8_t* codes, uint8_t* scales,
     }
     if (background) {
         constexpr int kDeep = 8;
+        RowQuantJob job;
+        if (!make_row_quant_job(&job, x, codes, scales, rows, cols, rule, layout)) return DW_ERR_BAD_ARG;
         const int64_t slabs = (total_chunks + 128 * kDeep - 1) / (128 * kDeep);
-        const unsigned bg_grid = static_cast<unsigned>(std::min<int64_t>(slabs, 1ll << 30));
-        if (aligned(x, 32))
-            mx_quant_row_bg_kernel<kDeep, true><<<bg_grid, 128, 0, st>>>(x, codes, scales, static_cast<uint32_t>(total_chunks),
-                                                                       cpr, rule, layout, packed);
-        else
-            mx_quant_row_bg_kernel<kDeep, false><<<bg_grid, 128, 0, st>>>(x, codes, scales, static_cast<uint32_t>(total_chunks),
-                                                                        cpr, rule, layout, packed);
+        mx_quant_row_bg_kernel<kDeep><<<static_cast<unsigned>(std::min<int64_t>(slabs, 1ll << 30)), kRowSlabThreads, 0, st>>>(job);
         return launch_status();
     }
     if (aligned(x, 32))
@@ -766,6 +685,17 @@ mx_colsum_reduce_kernel(const float* __restrict__ partial, int64_t tiles_r, int6
     } else {
         static_cast<float*>(out)[c] = acc;
     }
+}
+
+extern "C" DW_API int dw_mxfp8_pad_tiled_scales(void* scales, int64_t rows, int64_t k, void* stream) {
+    if (scales == nullptr || rows <= 0 || k <= 0) return DW_ERR_BAD_ARG;
+    DeviceInfo di;
+    const int drc = current_device(&di);
+    if (drc != DW_OK) return drc;
+    const int64_t nb = (k + 31) / 32, rt = (rows + 127) / 128, kt = (nb + 3) / 4;
+    mx_sf_pad_kernel<<<static_cast<int>(std::min<int64_t>((rt * kt * 512 + 255) / 256, 4096)), 256, 0,
+                       static_cast<cudaStream_t>(stream)>>>(static_cast<uint8_t*>(scales), rows, nb, rt, kt);
+    return launch_status();
 }
 
 extern "C" DW_API int dw_mxfp8_quantize_set_tuning(int word) {

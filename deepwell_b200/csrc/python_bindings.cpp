@@ -223,10 +223,8 @@ class MXFP8LinearFunction : public torch::autograd::Function<MXFP8LinearFunction
   static Tensor forward(torch::autograd::AutogradContext* ctx, const Tensor& x2d, const Tensor& weight,
                         const c10::optional<Tensor>& bias, const Tensor& w_row_codes, const Tensor& w_row_sf,
                         const c10::optional<Tensor>& w_col_codes, const c10::optional<Tensor>& w_col_sf, int64_t rule,
-                        const Tensor& status, bool check_status) {
-    const bool grad_mode = c10::GradMode::is_enabled();
-    const bool need_dx = grad_mode && x2d.requires_grad();
-    const bool need_dw = grad_mode && weight.requires_grad();
+                        const Tensor& status, bool check_status, bool need_dx, bool need_dw) {
+    // need_dx / need_dw come from the caller: inside forward() gradient mode is switched off
     TORCH_CHECK(!need_dx || w_col_codes.has_value(), "the input gradient needs the column-wise weight operand");
     const Tensor xb = x2d.scalar_type() == torch::kBFloat16 ? x2d : x2d.to(torch::kBFloat16);
     c10::optional<Tensor> bias_b;
@@ -279,7 +277,7 @@ class MXFP8LinearFunction : public torch::autograd::Function<MXFP8LinearFunction
       const c10::cuda::CUDAGuard guard(dy.device());
       check_rc(dw_mxfp8_check_status(status.data_ptr(), stream_of(dy)), "DWLinear backward");
     }
-    return {dx, dw, db, Tensor(), Tensor(), Tensor(), Tensor(), Tensor(), Tensor(), Tensor()};
+    return {dx, dw, db, Tensor(), Tensor(), Tensor(), Tensor(), Tensor(), Tensor(), Tensor(), Tensor(), Tensor()};
   }
 };
 
@@ -287,8 +285,9 @@ class MXFP8LinearFunction : public torch::autograd::Function<MXFP8LinearFunction
 Tensor linear(const Tensor& x2d, const Tensor& weight, const c10::optional<Tensor>& bias, const Tensor& w_row_codes,
               const Tensor& w_row_sf, const c10::optional<Tensor>& w_col_codes, const c10::optional<Tensor>& w_col_sf,
               int64_t rule, const Tensor& status, bool check_status) {
+  const bool grad_mode = c10::GradMode::is_enabled();
   return MXFP8LinearFunction::apply(x2d, weight, bias, w_row_codes, w_row_sf, w_col_codes, w_col_sf, rule, status,
-                                    check_status);
+                                    check_status, grad_mode && x2d.requires_grad(), grad_mode && weight.requires_grad());
 }
 
 }  // namespace
