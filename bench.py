@@ -746,9 +746,7 @@ def main():
     ap.add_argument("--traffic-from-csv", default=None, help="ncu CSV of the GEMM launches -> bench_gemm_dram_traffic.json")
     ap.add_argument("--emulate-world", type=int, default=0,
                     help="tuning aid: on one GPU, run the shard sizes rank 0 would get in a job of this many GPUs")
-    ap.add_argument("--serial", action="store_true", help="quantise and GEMM as separate launches on one stream (no overlap)")
-    ap.add_argument("--two-streams", action="store_true",
-                    help="separate launches, the next layer's quantisers on a second stream (they wait for the GEMM's SMs)")
+    ap.add_argument("--serial", action="store_true", help="quantise and GEMM on one stream")
     ap.add_argument("--profile-case", default=None, choices=["gemm", "quant_row", "quant_both", "quant_col"],
                     help="run a few launches of one kernel on a small case (for an ncu capture) and exit")
     ap.add_argument("--workload", default="linears", choices=["linears", "decoder_step"],
@@ -815,54 +813,22 @@ def main():
                        "y": torch.empty(M_TOKENS, nl, dtype=torch.bfloat16, device=dev)})
     status = nv.status_word(dev)
     # GEMMs (and the step timer) run on `stream`.  The four layers are independent problems, so the (HBM-bound)
-    # quantisation of layer i+1 overlaps the (tensor-bound) GEMM of layer i.  Default: inside the GEMM's own launch
-    # (dw_mxfp8_gemm_quantize: two quantiser warps per GEMM thread block), the only way the two really run at the same
-    # time, since nothing is scheduled beside a persistent GEMM.  --two-streams: separate launches, quantisers on a second,
-    # lower-priority stream.  --serial: separate launches on one stream.
-    fused = not (args.serial or args.two_streams)
+    # quantisers of layer i+1 are issued on a second, lower-priority stream while the (tensor-bound) GEMM of layer i runs.
+    # No kernel is scheduled beside a GEMM thread block on its SM (measured), so what this buys is the SMs the GEMM
+    # leaves free: those it does not need for its number of rounds of tiles, and those whose last tile is done.
+    # --serial keeps everything on one stream.
     lo_pri, hi_pri = torch.cuda.Stream.priority_range()
     stream = torch.cuda.Stream(dev, priority=hi_pri)
     torch.cuda.set_stream(stream)
     st = stream.cuda_stream
-    qstream = torch.cuda.Stream(dev, priority=lo_pri) if args.two_streams else stream
+    qstream = stream if args.serial else torch.cuda.Stream(dev, priority=lo_pri)
     sq = qstream.cuda_stream
     for l in layers:
         l["quantised"] = torch.cuda.Event()            # operands of this layer are ready
         l["consumed"] = torch.cuda.Event()             # the GEMM that read them has finished
     gemm_events = []
 
-    def quantise_operands(l, s):
-        nv.check(L.dw_mxfp8_quantize(l["x"].data_ptr(), l["xc"].data_ptr(), l["xs"].data_ptr(), M_TOKENS, l["k"],
-                                     nv.DIR_ROW, nv.RULE_OCP_FLOOR, nv.SF_TILED, s), "quantize X")
-        nv.check(L.dw_mxfp8_quantize(l["w"].data_ptr(), l["wc"].data_ptr(), l["ws"].data_ptr(), l["n"], l["k"],
-                                     nv.DIR_ROW, nv.RULE_OCP_FLOOR, nv.SF_TILED, s), "quantize W")
-
-    def fused_step(record: bool, after_gemm=None):
-        """Each layer's GEMM launch also quantises the NEXT layer's X and W (the last layer's launch those of the first
-        layer, for the next step): per step 4 launches, 4 GEMMs, 4 activation and 4 weight quantisations."""
-        for i, l in enumerate(layers):
-            nxt = layers[(i + 1) % len(layers)]
-            if after_gemm is not None and "gather_done" in l:
-                stream.wait_event(l["gather_done"])    # the previous step's all-gather has read this layer's Y
-            if record:
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record(stream)
-            nv.check(L.dw_mxfp8_gemm_quantize(
-                l["xc"].data_ptr(), l["xs"].data_ptr(), l["wc"].data_ptr(), l["ws"].data_ptr(), l["y"].data_ptr(), None,
-                M_TOKENS, l["n"], l["k"], 1.0, 0.0,
-                nxt["x"].data_ptr(), nxt["xc"].data_ptr(), nxt["xs"].data_ptr(), M_TOKENS, nxt["k"],
-                nxt["w"].data_ptr(), nxt["wc"].data_ptr(), nxt["ws"].data_ptr(), nxt["n"], nxt["k"],
-                nv.RULE_OCP_FLOOR, status.data_ptr(), st), "gemm + quantize")
-            if record:
-                e1.record(stream)
-                gemm_events.append((e0, e1))
-            if after_gemm is not None:
-                after_gemm(l)
-        return len(layers)
-
     def step(record: bool, after_gemm=None):
-        if fused:
-            return fused_step(record, after_gemm)
         launches = 0
         for l in layers:
             if qstream is not stream:
@@ -919,8 +885,6 @@ def main():
         barrier()
         return max_over_ranks(t0.elapsed_time(t1)), n_launch
 
-    if fused:
-        quantise_operands(layers[0], st)              # the pipeline's first operands; every later one comes from a GEMM launch
     for _ in range(warmup):
         step(False)
     nv.check_status(dev)
@@ -977,17 +941,12 @@ def main():
     # quantisation runs underneath them and takes its share of power and issue slots)
     if not args.serial:
         torch.cuda.synchronize(dev)
-        if fused:
-            for l in layers:                           # every layer's operands in place (the pipeline leaves them so anyway)
-                quantise_operands(l, st)
         alone_ms = gemm_only(3)
         alone_tf = gemm_flops_step / (alone_ms * 1e-3) / 1e12
         roofline["achieved_alone"] = alone_tf
         roofline["frac_alone_of_burst"] = alone_tf / peak_burst
-        roofline["note"] = ("achieved/frac: live in the timed region, where the next layer's quantiser shares the GPU "
-                            + ("(inside the same launch: the durations are those of mx_gemm_kernel with its quantiser warps); "
-                               if fused else "; ")
-                            + "achieved_alone: the four plain GEMM launches back to back with nothing else running")
+        roofline["note"] = ("achieved/frac: live in the timed region, where the next layer's quantiser shares the GPU; "
+                            "achieved_alone: the same four launches back to back with nothing else running")
 
     # ---- sustained leg: the same step for >= args.sustained_seconds, clocks sampled throughout ----
     sustained = None
@@ -1160,10 +1119,7 @@ def main():
                 "config": {"workload": WORKLOAD, "M": M_TOKENS, "layers": {n: [k, nn] for n, k, nn in LAYERS},
                            "parallelism": f"N-sharded x{world}, X replicated, no data-path collective",
                            "step": "per layer: quantise X, quantise W shard, block-scaled GEMM"
-                                   + ("; the quantisation of the next layer's X and W rides in the GEMM's launch "
-                                      "(dw_mxfp8_gemm_quantize: 4 launches per step)" if fused else
-                                      "; separate launches, " + ("one stream" if args.serial else
-                                                                 "quantisers of the next layer on a second, lower-priority stream")),
+                                   + ("" if args.serial else "; quantisers of the next layer on a second, lower-priority stream"),
                            "l2": f"inputs larger than L2: {bytes_step / 1e9:.2f} GB touched per step per GPU",
                            "gemm_variant": args.variant,
                            **({"emulated_world": args.emulate_world,

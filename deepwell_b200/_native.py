@@ -40,7 +40,7 @@ ABI_SYMBOLS = (
     "dw_mxfp8_colsum_workspace", "dw_mxfp8_quantize_both_colsum", "dw_mxfp8_gemm_grouped",
     "dw_mxfp8_update_amax_history", "dw_mxfp8_gemm_planned", "dw_mxfp8_gemm_workspace_planned",
     "dw_mxfp8_selftest_bounded_wait", "dw_mxfp8_debug_fake_device", "dw_mxfp8_debug_counter",
-    "dw_mxfp8_quantize_set_tuning", "dw_mxfp8_gemm_quantize", "dw_mxfp8_pad_tiled_scales",
+    "dw_mxfp8_quantize_set_tuning",
 )
 
 _lib = None
@@ -73,8 +73,6 @@ def load() -> ctypes.CDLL:
     L.dw_mxfp8_scale_bytes.restype = sz
     L.dw_mxfp8_quantize.argtypes = [p, p, p, i64, i64, i32, i32, i32, p]
     L.dw_mxfp8_quantize_set_tuning.argtypes = [i32]
-    L.dw_mxfp8_gemm_quantize.argtypes = [p, p, p, p, p, p, i64, i64, i64, f32, f32, p, p, p, i64, i64, p, p, p, i64, i64, i32, p, p]
-    L.dw_mxfp8_pad_tiled_scales.argtypes = [p, i64, i64, p]
     L.dw_mxfp8_quantize_both.argtypes = [p, p, p, p, p, i64, i64, i32, i32, p]
     L.dw_mxfp8_dequantize.argtypes = [p, p, p, i64, i64, i32, p]
     L.dw_mxfp8_update_amax_history.argtypes = [p, p, i32, i64, p]

@@ -1,6 +1,5 @@
-// Row-wise MX quantisation of one slab of a bf16 matrix by a few warps: the body shared by the stand-alone kernel for
-// large inputs (mx_quant_row_bg_kernel: 128 threads, 8 loads in flight each) and by the quantiser warps that ride inside
-// the GEMM kernel (mx_gemm.cu: 64 threads, 16 loads in flight each).
+// Row-wise MX quantisation of one slab of a bf16 matrix by a few warps, many loads in flight per thread: the body of the
+// kernel for large inputs (mx_quant_row_bg_kernel: 128 threads, 8 loads of 32 bytes in flight each).
 #pragma once
 
 #include "dw_common.cuh"
@@ -104,10 +103,9 @@ __device__ __forceinline__ void quant_row_slab(const RowQuantJob& j, uint64_t sl
 template <int kDeep, int kThreads = kRowSlabThreads>
 __device__ __forceinline__ void quant_row_slabs(const RowQuantJob& j, uint64_t first, uint64_t stride, uint32_t tid) {
     constexpr uint64_t kSlab = static_cast<uint64_t>(kThreads) * kDeep;
-    if (j.wide) {
-        for (uint64_t slab = first; slab * kSlab < j.total_chunks; slab += stride) quant_row_slab<kDeep, true, kThreads>(j, slab, tid);
-    } else {
-        for (uint64_t slab = first; slab * kSlab < j.total_chunks; slab += stride) quant_row_slab<kDeep, false, kThreads>(j, slab, tid);
+    for (uint64_t slab = first; slab * kSlab < j.total_chunks; slab += stride) {
+        if (j.wide) quant_row_slab<kDeep, true, kThreads>(j, slab, tid);
+        else quant_row_slab<kDeep, false, kThreads>(j, slab, tid);
     }
 }
 

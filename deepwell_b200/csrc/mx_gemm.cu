@@ -15,12 +15,6 @@
 //               the fp32 accumulator, alpha/beta/bias/activation, bf16, then shared memory and a TMA
 //               store per 32 x 32 box (per-thread stores for ragged N, beta reads, split-K partials
 //               and the fused quantised output)
-//   warps 10-11 (kSide only) quantiser warps: row-wise MX quantisation of up to two OTHER bf16 matrices
-//               (the next layer's activation and weight) from HBM to HBM while this GEMM multiplies.  A
-//               persistent GEMM holds every SM with one CTA that takes nearly all shared memory, and no
-//               kernel of another stream is scheduled beside it (measured: not even a one-block kernel
-//               starts before the GEMM's CTAs retire), so HBM-bound work overlaps the tensor-bound GEMM
-//               only from inside its own CTAs.
 //
 // kCtas == 2 pairs two CTAs (a cluster of 2 along M) on one 256 x BN tile with cta_group::2: each
 // CTA stages its own half of A and its own half of B; the leader CTA issues the MMAs for both.
@@ -35,7 +29,6 @@
 
 #include "dw_common.cuh"
 #include "dw_ptx.cuh"
-#include "dw_quant_row.cuh"
 
 namespace dw {
 
@@ -72,22 +65,12 @@ struct GemmParams {
     // weight (rows [g N, (g + 1) N) of B) that tile multiplies.  nullptr: one ordinary GEMM.
     const int* tile_group;
     uint32_t num_groups;
-    // Quantiser warps (kSide kernels): row-wise MX quantisation jobs unrelated to this GEMM's operands, slabs
-    // distributed over the CTAs by blockIdx.
-    RowQuantJob side[2];
-    int num_side;
 };
 constexpr int kWaitCounters = 8;
 // warp 0: TMA producer, warp 1: MMA issuer, warps 2-9: epilogue (two warps per TMEM lane quadrant,
 // each taking half of the accumulator's columns)
 constexpr int kEpilogueWarps = 8;
 constexpr int kGemmThreads = 64 + 32 * kEpilogueWarps;
-// Quantiser warps of the kSide kernels: two warps, so that the CTA has 12 warps = 3 per SM sub-partition like the plain
-// kernel and every thread keeps its 168 registers (a 13th warp would put 4 on one sub-partition and cap all threads at 128,
-// spilling the epilogue); 16 loads of 32 bytes in flight per thread = 32 KB per SM.
-constexpr int kSideThreads = 64;
-constexpr int kSideDeep = 16;
-
 template <int BN, int kCtas, int kGroup>
 struct GemmCfg {
     static constexpr int kBM = 128;                       // rows per CTA
@@ -143,8 +126,8 @@ __device__ __forceinline__ float apply_activation(float x, int act) {
 
 enum : int { kErrProducer = 1, kErrMmaFull = 2, kErrMmaAcc = 3, kErrEpilogue = 4, kErrSelfTest = 5 };
 
-template <int BN, int kCtas, int kGroup, bool kSide = false>
-__global__ void __launch_bounds__(kGemmThreads + (kSide ? kSideThreads : 0), 1)
+template <int BN, int kCtas, int kGroup>
+__global__ void __launch_bounds__(kGemmThreads, 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                const __grid_constant__ CUtensorMap tm_sfa, const __grid_constant__ CUtensorMap tm_sfb,
                const __grid_constant__ CUtensorMap tm_d, const GemmParams p) {
@@ -345,10 +328,6 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 if (++acc == kAcc) { acc = 0; acc_phase ^= 1u; }
             }
         }
-    } else if (kSide && warp >= 2 + kEpilogueWarps) {
-        // ================= quantiser warps: other matrices, HBM to HBM, under this CTA's mainloop =================
-        const uint32_t tid = threadIdx.x - kGemmThreads;
-        for (int j = 0; j < p.num_side; ++j) quant_row_slabs<kSideDeep, kSideThreads>(p.side[j], blockIdx.x, gridDim.x, tid);
     } else {
         // ================= epilogue (8 warps: 4 TMEM lane quadrants x 2 column halves) =================
         const uint32_t q = warp & 3u;                    // TMEM lane quadrant this warp may read
@@ -816,7 +795,7 @@ struct PlanWord {
 static std::atomic<int> g_default_plan{0};          // dw_mxfp8_gemm_set_variant: the plan word of calls that pass none
 static std::atomic<long long*> g_timing{nullptr};   // optional per-CTA wait counters (dw_mxfp8_gemm_set_timing_buffer)
 
-template <int BN, int kCtas, int kGroup, bool kSide = false>
+template <int BN, int kCtas, int kGroup>
 static int launch_gemm(const void* a, const void* a_sf, const void* b, const void* b_sf, GemmParams p, const PlanWord& pw,
                        const DeviceInfo& di, cudaStream_t st) {
     using Cfg = GemmCfg<BN, kCtas, kGroup>;
@@ -856,7 +835,7 @@ static int launch_gemm(const void* a, const void* a_sf, const void* b, const voi
         static bool done[kMaxDevices] = {};
         std::lock_guard<std::mutex> lock(mu);
         if (!done[di.device]) {
-            if (cudaFuncSetAttribute(mx_gemm_kernel<BN, kCtas, kGroup, kSide>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+            if (cudaFuncSetAttribute(mx_gemm_kernel<BN, kCtas, kGroup>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      Cfg::kSmemBytes) != cudaSuccess) {
                 cudaGetLastError();
                 return DW_ERR_LAUNCH;
@@ -867,10 +846,15 @@ static int launch_gemm(const void* a, const void* a_sf, const void* b, const voi
 
     p.kb_per_split = (p.num_kblocks + p.splits - 1) / p.splits;
     p.splits = (p.num_kblocks + p.kb_per_split - 1) / p.kb_per_split;      // every split owns at least one k-block
-    const int workers = std::min<int64_t>(static_cast<int64_t>(p.num_tiles) * p.splits, di.sms / kCtas);
+    // Work units are dealt round-robin to the workers (CTAs or CTA pairs), so the kernel lasts ceil(units / workers) units
+    // whatever the remainder: the smallest worker count with that many rounds finishes at the same time and leaves the
+    // other SMs to kernels of other streams (nothing is scheduled next to a GEMM CTA on its own SM).
+    const int64_t units = static_cast<int64_t>(p.num_tiles) * p.splits, max_workers = di.sms / kCtas;
+    const int64_t rounds = (units + max_workers - 1) / max_workers;
+    const int workers = static_cast<int>(std::min<int64_t>((units + rounds - 1) / rounds, max_workers));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(workers * kCtas));
-    cfg.blockDim = dim3(kGemmThreads + (kSide ? kSideThreads : 0));
+    cfg.blockDim = dim3(kGemmThreads);
     cfg.dynamicSmemBytes = Cfg::kSmemBytes;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -878,7 +862,7 @@ static int launch_gemm(const void* a, const void* a_sf, const void* b, const voi
     attr[0].val.clusterDim.x = kCtas; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (cudaLaunchKernelEx(&cfg, mx_gemm_kernel<BN, kCtas, kGroup, kSide>, tm_a, tm_b, tm_sfa, tm_sfb, tm_d, p) != cudaSuccess) {
+    if (cudaLaunchKernelEx(&cfg, mx_gemm_kernel<BN, kCtas, kGroup>, tm_a, tm_b, tm_sfa, tm_sfb, tm_d, p) != cudaSuccess) {
         cudaGetLastError();
         return DW_ERR_LAUNCH;
     }
@@ -936,7 +920,6 @@ static GemmPlan plan_gemm(int64_t M, int64_t N, int64_t K, const PlanWord& pw, i
 struct FusedOut {
     int act = DW_ACT_NONE; int rule = DW_RULE_OCP_FLOOR; void* codes = nullptr; void* scales = nullptr;
     const int* tile_group = nullptr; uint32_t num_groups = 0;
-    RowQuantJob side[2] = {}; int num_side = 0;
 };
 
 static int run_gemm(const void* a_codes, const void* a_sf, const void* b_codes, const void* b_sf, void* d_bf16,
@@ -955,15 +938,6 @@ static int run_gemm(const void* a_codes, const void* a_sf, const void* b_codes, 
     p.splits = splits; p.partial = partial;
     p.wait_cycles = g_timing.load(std::memory_order_relaxed);
     p.tile_group = fo.tile_group; p.num_groups = fo.num_groups;
-    p.num_side = fo.num_side;
-    for (int j = 0; j < fo.num_side; ++j) p.side[j] = fo.side[j];
-    if (fo.num_side > 0) {
-        switch (variant) {       // callers choose among the variants that have quantiser warps
-            case 2: return launch_gemm<256, 1, 1, true>(a_codes, a_sf, b_codes, b_sf, p, pw, di, st);
-            case 3: return launch_gemm<256, 2, 1, true>(a_codes, a_sf, b_codes, b_sf, p, pw, di, st);
-            default: return launch_gemm<192, 2, 1, true>(a_codes, a_sf, b_codes, b_sf, p, pw, di, st);
-        }
-    }
     switch (variant) {
         case 1: return launch_gemm<128, 1, 1>(a_codes, a_sf, b_codes, b_sf, p, pw, di, st);
         case 2: return launch_gemm<256, 1, 1>(a_codes, a_sf, b_codes, b_sf, p, pw, di, st);
@@ -1096,48 +1070,6 @@ extern "C" DW_API int dw_mxfp8_gemm_grouped(const void* a_codes, const void* a_s
     const PlanWord pw(g_default_plan.load(std::memory_order_relaxed) & (1 << 24));     // the store mode only
     return run_gemm(a_codes, a_sf, b_codes, b_sf, d_bf16, nullptr, M_total, N, K, alpha, 0.0f, variant, 1, nullptr, status_word,
                     pw, di, static_cast<cudaStream_t>(stream), fo);
-}
-
-extern "C" DW_API int dw_mxfp8_gemm_quantize(const void* a_codes, const void* a_sf, const void* b_codes, const void* b_sf,
-                                             void* d_bf16, const void* bias_bf16, int64_t M, int64_t N, int64_t K, float alpha,
-                                             float beta, const void* q1_x, void* q1_codes, void* q1_scales, int64_t q1_rows,
-                                             int64_t q1_cols, const void* q2_x, void* q2_codes, void* q2_scales,
-                                             int64_t q2_rows, int64_t q2_cols, int scale_rule, void* status_word, void* stream) {
-    if (M <= 0 || N <= 0 || K <= 0) return DW_ERR_BAD_ARG;
-    if (scale_rule != DW_RULE_OCP_FLOOR && scale_rule != DW_RULE_REF_CEIL) return DW_ERR_BAD_ARG;
-    FusedOut fo;
-    const void* qx[2] = {q1_x, q2_x};
-    void* qc[2] = {q1_codes, q2_codes};
-    void* qs[2] = {q1_scales, q2_scales};
-    const int64_t qr[2] = {q1_rows, q2_rows}, qcol[2] = {q1_cols, q2_cols};
-    for (int j = 0; j < 2; ++j) {
-        if (qx[j] == nullptr) continue;                    // this job is not given
-        if (qc[j] == nullptr || qs[j] == nullptr || qr[j] < 0 || qcol[j] < 0) return DW_ERR_BAD_ARG;
-        if (qr[j] == 0 || qcol[j] == 0) continue;
-        if (qr[j] * qcol[j] >= (1ll << 35)) return DW_ERR_TOO_LARGE;
-        // the quantiser warps run the vectorised row-wise path only: whole blocks of 32, 16-byte aligned
-        if (!make_row_quant_job(&fo.side[fo.num_side], qx[j], qc[j], qs[j], qr[j], qcol[j], scale_rule, DW_SF_TILED))
-            return DW_ERR_BAD_ARG;
-        ++fo.num_side;
-    }
-    DeviceInfo di;
-    const int rc = check_gemm_args(a_codes, a_sf, b_codes, b_sf, d_bf16, bias_bf16, M, N, K, &di);
-    if (rc != DW_OK) return rc;
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
-    // tiled scale buffers of the side jobs: padding bytes the quantiser warps do not touch
-    for (int j = 0, k = 0; j < 2; ++j) {
-        if (qx[j] == nullptr || qr[j] == 0 || qcol[j] == 0) continue;
-        ++k;
-        if (qr[j] % 128 != 0 || (qcol[j] / 32) % 4 != 0) {
-            const int prc = dw_mxfp8_pad_tiled_scales(qs[j], qr[j], qcol[j], stream);
-            if (prc != DW_OK) return prc;
-        }
-    }
-    const PlanWord pw(g_default_plan.load(std::memory_order_relaxed));
-    GemmPlan pl = plan_gemm(M, N, K, pw, di.sms);
-    if (fo.num_side > 0 && (pl.variant == 1 || pl.variant == 4)) pl.variant = M <= 128 ? 2 : 3;   // variants with quantiser warps
-    return run_gemm(a_codes, a_sf, b_codes, b_sf, d_bf16, bias_bf16, M, N, K, alpha, beta, pl.variant, 1, nullptr, status_word,
-                    pw, di, st, fo);
 }
 
 // ------------------------------------------------------------------------------------------

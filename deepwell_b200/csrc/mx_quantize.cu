@@ -687,17 +687,6 @@ mx_colsum_reduce_kernel(const float* __restrict__ partial, int64_t tiles_r, int6
     }
 }
 
-extern "C" DW_API int dw_mxfp8_pad_tiled_scales(void* scales, int64_t rows, int64_t k, void* stream) {
-    if (scales == nullptr || rows <= 0 || k <= 0) return DW_ERR_BAD_ARG;
-    DeviceInfo di;
-    const int drc = current_device(&di);
-    if (drc != DW_OK) return drc;
-    const int64_t nb = (k + 31) / 32, rt = (rows + 127) / 128, kt = (nb + 3) / 4;
-    mx_sf_pad_kernel<<<static_cast<int>(std::min<int64_t>((rt * kt * 512 + 255) / 256, 4096)), 256, 0,
-                       static_cast<cudaStream_t>(stream)>>>(static_cast<uint8_t*>(scales), rows, nb, rt, kt);
-    return launch_status();
-}
-
 extern "C" DW_API int dw_mxfp8_quantize_set_tuning(int word) {
     if (word < 0 || (word & 3) == 3 || (word >> 2) != 0) return DW_ERR_BAD_ARG;
     g_quant_tuning.store(word, std::memory_order_relaxed);

@@ -173,27 +173,6 @@ int dw_mxfp8_gemm_grouped(const void *a_codes, const void *a_sf, const void *b_c
                           void *d_bf16, const int *tile_group, int64_t M_total, int64_t N, int64_t K,
                           int num_groups, int rows_per_tile, float alpha, void *status_word, void *stream);
 
-/* dw_mxfp8_gemm plus the row-wise MX quantisation (DW_DIR_ROW, DW_SF_TILED) of up to two OTHER bf16 matrices in the
- * same launch, done by two extra warps of every GEMM thread block while the tensor cores multiply: typically the
- * next layer's activation (q1) and weight (q2), so that the HBM-bound quantiser costs no time of its own.  (A
- * persistent GEMM holds every SM; on B200 no kernel of another stream runs beside it, so a quantiser launched on a
- * second stream simply waits for the GEMM to end.)  q?_x NULL = job not given.  The jobs' outputs are bit for bit those
- * of dw_mxfp8_quantize.  Conditions for a job: cols % 32 == 0, x and codes 16-byte aligned (DW_ERR_BAD_ARG otherwise);
- * they must not alias this GEMM's operands or output.  The GEMM itself runs unsplit; alpha, beta, bias as in dw_mxfp8_gemm.
- * This is the "quantise fused with the GEMM" of the path: the reference keeps the two as separate launches
- * (csrc/cutlass_kernels.cpp:348-380 and :173-204). */
-int dw_mxfp8_gemm_quantize(const void *a_codes, const void *a_sf, const void *b_codes, const void *b_sf,
-                           void *d_bf16, const void *bias_bf16, int64_t M, int64_t N, int64_t K, float alpha,
-                           float beta, const void *q1_x, void *q1_codes, void *q1_scales, int64_t q1_rows,
-                           int64_t q1_cols, const void *q2_x, void *q2_codes, void *q2_scales, int64_t q2_rows,
-                           int64_t q2_cols, int scale_rule, void *status_word, void *stream);
-
-/* Writes the padding bytes (127) of a DW_SF_TILED scale buffer for an operand of `rows` rows and `k` elements along
- * its scaled dimension: the bytes of rows beyond `rows` and k-blocks beyond k/32 in the last tiles, which the GEMM
- * reads.  The quantiser entry points do this themselves; a caller that fills a tiled scale buffer by other means
- * needs it.  No counterpart in the reference (its scales are flat fp32, csrc/mxfp8_quantization.cu:124-130). */
-int dw_mxfp8_pad_tiled_scales(void *scales, int64_t rows, int64_t k, void *stream);
-
 /* Replaces BlackwellGemmKernel::get_workspace_size, csrc/cutlass_kernels.cpp:229-231. */
 size_t dw_mxfp8_gemm_workspace(int64_t M, int64_t N, int64_t K);
 

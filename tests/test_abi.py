@@ -83,8 +83,6 @@ def test_wrong_architecture_is_reported_by_every_launcher(native_lib):
         assert L.dw_mxfp8_gemm_grouped(p16, p16, p16, p16, p16, ctypes.cast(groups, ctypes.c_void_p), 128, 128, 128, 1, 128, 1.0,
                                        None, None) == -2
         assert L.dw_mxfp8_selftest_bounded_wait(1000, p16, None) == -2
-        assert L.dw_mxfp8_gemm_quantize(*gemm_args, p16, p16, p16, 64, 64, None, None, None, 0, 0, 0, None, None) == -2
-        assert L.dw_mxfp8_pad_tiled_scales(p16, 100, 96, None) == -2
         # argument errors are still reported first
         assert L.dw_mxfp8_gemm(p16, p16, p16, p16, p16, None, 128, 128, 100, 1.0, 0.0, None, 0, None, None) == -1
         assert L.dw_mxfp8_gemm_planned(*gemm_args, None, 0, 77, None, None) == -1       # no such variant

@@ -559,59 +559,3 @@ def test_bounded_wait_runs_out_and_is_reported(nv, native_lib):
         nv.check_status("cuda:0")
     # the context is intact: a GEMM right after gives the right answer
     run(nv, 256, 256, 256)
-
-
-@pytest.mark.parametrize("variant", [0, 2, 3, 5])
-@pytest.mark.parametrize("jobs", [((512, 256), (384, 512)), ((300, 96), None), (None, (129, 2080)), (None, None),
-                                  ((4096, 1024), (2048 + 64, 4096))])
-def test_gemm_with_quantiser_warps(nv, native_lib, variant, jobs):
-    """dw_mxfp8_gemm_quantize: the GEMM's output is bit for bit that of dw_mxfp8_gemm, and the matrices quantised by the
-    extra warps of the same launch (none, one or two; whole and ragged scale tiles; more slabs than thread blocks and
-    fewer) are bit for bit what dw_mxfp8_quantize and the oracle give."""
-    L = native_lib
-    nv.set_gemm_variant(variant)
-    M, N, K = 640, 768, 512
-    g = torch.Generator("cpu").manual_seed(77)
-    x = torch.randn(M, K, generator=g).bfloat16().cuda()
-    w = (torch.randn(N, K, generator=g) * 0.03).bfloat16().cuda()
-    bias = torch.randn(N, generator=g).bfloat16().cuda()
-    xc, xs = nv.quantize(x, nv.DIR_ROW, 0, nv.SF_TILED)
-    wc, ws = nv.quantize(w, nv.DIR_ROW, 0, nv.SF_TILED)
-    want = nv.gemm(xc, xs, wc, ws, bias=bias, alpha=0.5)
-    side, args = [], []
-    for shape in jobs:
-        if shape is None:
-            args += [None, None, None, 0, 0]
-            continue
-        q = torch.randn(shape, generator=g)
-        q[torch.rand(shape, generator=g) < 0.01] *= 50
-        q = q.bfloat16().cuda()
-        codes = torch.zeros(shape, dtype=torch.uint8, device="cuda")
-        scales = torch.zeros(nv.scale_bytes(shape[0], shape[1], nv.SF_TILED), dtype=torch.uint8, device="cuda")
-        side.append((q, codes, scales))
-        args += [q.data_ptr(), codes.data_ptr(), scales.data_ptr(), shape[0], shape[1]]
-    got = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
-    st = torch.cuda.current_stream().cuda_stream
-    rc = L.dw_mxfp8_gemm_quantize(xc.data_ptr(), xs.data_ptr(), wc.data_ptr(), ws.data_ptr(), got.data_ptr(), bias.data_ptr(),
-                                  M, N, K, 0.5, 0.0, *args, 0, nv.status_word("cuda:0").data_ptr(), st)
-    assert rc == 0, L.dw_mxfp8_error_string(rc)
-    nv.check_status()
-    nv.set_gemm_variant(0)
-    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
-    for q, codes, scales in side:
-        ec, es = nv.quantize(q, nv.DIR_ROW, 0, nv.SF_TILED)
-        assert torch.equal(codes, ec.view(torch.uint8)) and torch.equal(scales, es)
-        oc, osf = o.quantize_rowwise(q.cpu().view(torch.int16).numpy().view(np.uint16))
-        assert np.array_equal(host(codes), oc) and np.array_equal(host(scales), o.sf_flat_to_tiled(osf))
-
-
-def test_gemm_with_quantiser_warps_rejects_bad_jobs(nv, native_lib):
-    L = native_lib
-    p16 = 16
-    g = (p16, p16, p16, p16, p16, None, 128, 128, 128, 1.0, 0.0)
-    none = (None, None, None, 0, 0)
-    assert L.dw_mxfp8_gemm_quantize(*g, p16, p16, p16, 64, 40, *none, 0, None, None) == -1          # cols % 32
-    assert L.dw_mxfp8_gemm_quantize(*g, p16 + 2, p16, p16, 64, 64, *none, 0, None, None) == -1      # unaligned input
-    assert L.dw_mxfp8_gemm_quantize(*g, p16, None, p16, 64, 64, *none, 0, None, None) == -1         # no output
-    assert L.dw_mxfp8_gemm_quantize(*g, *none, *none, 7, None, None) == -1                          # bad scale rule
-    assert L.dw_mxfp8_pad_tiled_scales(None, 4, 32, None) == -1
