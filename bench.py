@@ -746,7 +746,8 @@ def main():
     ap.add_argument("--traffic-from-csv", default=None, help="ncu CSV of the GEMM launches -> bench_gemm_dram_traffic.json")
     ap.add_argument("--emulate-world", type=int, default=0,
                     help="tuning aid: on one GPU, run the shard sizes rank 0 would get in a job of this many GPUs")
-    ap.add_argument("--serial", action="store_true", help="quantise and GEMM on one stream")
+    ap.add_argument("--serial", action="store_true", help="quantise and GEMM on one stream, every launch after the previous one has finished")
+    ap.add_argument("--two-streams", action="store_true", help="the next layer's quantisers on a second, lower-priority stream")
     ap.add_argument("--profile-case", default=None, choices=["gemm", "quant_row", "quant_both", "quant_col"],
                     help="run a few launches of one kernel on a small case (for an ncu capture) and exit")
     ap.add_argument("--workload", default="linears", choices=["linears", "decoder_step"],
@@ -812,23 +813,55 @@ def main():
                        "ws": u8(nv.scale_bytes(nl, k, nv.SF_TILED)),
                        "y": torch.empty(M_TOKENS, nl, dtype=torch.bfloat16, device=dev)})
     status = nv.status_word(dev)
-    # GEMMs (and the step timer) run on `stream`.  The four layers are independent problems, so the (HBM-bound)
-    # quantisers of layer i+1 are issued on a second, lower-priority stream while the (tensor-bound) GEMM of layer i runs.
-    # No kernel is scheduled beside a GEMM thread block on its SM (measured), so what this buys is the SMs the GEMM
-    # leaves free: those it does not need for its number of rounds of tiles, and those whose last tile is done.
-    # --serial keeps everything on one stream.
+    # Everything runs on `stream`.  The four layers are independent problems, so the (HBM-bound) quantisers of layer i+1
+    # can run while the (tensor-bound) GEMM of layer i does.  No kernel is scheduled beside a GEMM thread block on its own
+    # SM (measured), so the overlap that exists is on the SMs the GEMM leaves free: those it does not need for its number
+    # of rounds of tiles, and those whose last tile is done.  Default: one stream, GEMM(i) issued BEFORE the quantisers of
+    # layer i+1, which are launched with DW_QUANT_OVERLAP_PREVIOUS (they start once the GEMM's blocks are resident).
+    # --two-streams: the quantisers on a second, lower-priority stream with events.  --serial: one stream, no overlap.
+    overlap = not (args.serial or args.two_streams)
     lo_pri, hi_pri = torch.cuda.Stream.priority_range()
     stream = torch.cuda.Stream(dev, priority=hi_pri)
     torch.cuda.set_stream(stream)
     st = stream.cuda_stream
-    qstream = stream if args.serial else torch.cuda.Stream(dev, priority=lo_pri)
+    qstream = torch.cuda.Stream(dev, priority=lo_pri) if args.two_streams else stream
     sq = qstream.cuda_stream
     for l in layers:
         l["quantised"] = torch.cuda.Event()            # operands of this layer are ready
         l["consumed"] = torch.cuda.Event()             # the GEMM that read them has finished
-    gemm_events = []
+    gemm_events, pair_events = [], []
 
-    def step(record: bool, after_gemm=None):
+    def quantise_operands(l, flags):
+        nv.check(L.dw_mxfp8_quantize_ex(l["x"].data_ptr(), l["xc"].data_ptr(), l["xs"].data_ptr(), M_TOKENS, l["k"],
+                                        nv.DIR_ROW, nv.RULE_OCP_FLOOR, nv.SF_TILED, flags, st), "quantize X")
+        nv.check(L.dw_mxfp8_quantize_ex(l["w"].data_ptr(), l["wc"].data_ptr(), l["ws"].data_ptr(), l["n"], l["k"],
+                                        nv.DIR_ROW, nv.RULE_OCP_FLOOR, nv.SF_TILED, flags, st), "quantize W")
+
+    def overlapped_step(record: bool, after_gemm=None):
+        """GEMM of layer i, then (behind it on the same stream, allowed to start while it runs) the quantisers of layer
+        i + 1; the last layer's GEMM is followed by the first layer's quantisers for the next step.  Per step: 4 GEMMs,
+        4 activation and 4 weight quantisations, 12 launches."""
+        for i, l in enumerate(layers):
+            nxt = layers[(i + 1) % len(layers)]
+            if after_gemm is not None and "gather_done" in l:
+                stream.wait_event(l["gather_done"])    # the previous step's all-gather has read this layer's Y
+            if record:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+            nv.check(L.dw_mxfp8_gemm(l["xc"].data_ptr(), l["xs"].data_ptr(), l["wc"].data_ptr(), l["ws"].data_ptr(),
+                                     l["y"].data_ptr(), None, M_TOKENS, l["n"], l["k"], 1.0, 0.0, None, 0,
+                                     status.data_ptr(), st), "gemm")
+            quantise_operands(nxt, nv.QUANT_OVERLAP_PREVIOUS)
+            if record:
+                e1.record(stream)                      # GEMM + the quantisers that overlapped it
+                pair_events.append((e0, e1))
+            if after_gemm is not None:
+                after_gemm(l)
+        return 3 * len(layers)
+
+    def step(record: bool, after_gemm=None, force_separate=False):
+        if overlap and not force_separate:
+            return overlapped_step(record, after_gemm)
         launches = 0
         for l in layers:
             if qstream is not stream:
@@ -885,6 +918,8 @@ def main():
         barrier()
         return max_over_ranks(t0.elapsed_time(t1)), n_launch
 
+    if overlap:
+        quantise_operands(layers[0], 0)               # the pipeline's first operands; later ones follow a GEMM
     for _ in range(warmup):
         step(False)
     nv.check_status(dev)
@@ -898,6 +933,13 @@ def main():
     value = total_flops() / (ms_per_step * 1e-3) / 1e12
 
     # ---- roofline of the dominant kernel (GEMM), live CUDA-event durations of this rank ----
+    if overlap:
+        # Inside the timed region a GEMM's end cannot be told apart from the quantisers that overlap it (an event between
+        # them would hold the quantisers back).  The GEMM's own launch durations come from a second pass of the same
+        # steps, straight after the timed region, in which every launch waits for the previous one.
+        for _ in range(args.steps):
+            step(True, force_separate=True)
+        torch.cuda.synchronize(dev)
     gemm_ms = sum(a.elapsed_time(b) for a, b in gemm_events)
     gemm_flops_step = sum(2.0 * M_TOKENS * l["n"] * l["k"] for l in layers)
     achieved = args.steps * gemm_flops_step / (gemm_ms * 1e-3) / 1e12
@@ -921,7 +963,11 @@ def main():
                 "traffic": traffic if world == 1 else None,
                 "traffic_note": "mean DRAM bytes per GEMM launch (ncu, N = 1, bench_gemm_dram_traffic.json); algorithmic mean "
                                 "A + B + D = 5.16e8",
-                "gemm_ms_per_step": gemm_ms / args.steps, "launches_timed": len(gemm_events)}
+                "gemm_ms_per_step": gemm_ms / args.steps, "launches_timed": len(gemm_events),
+                **({"gemm_plus_overlapped_quantisers_ms_per_step": sum(a.elapsed_time(b) for a, b in pair_events) / args.steps,
+                    "timing": "GEMM launch durations from a pass of the same steps right after the timed region in which "
+                              "every launch waits for the previous one; in the timed region itself each GEMM overlaps the "
+                              "next layer's quantisers"} if overlap else {})}
 
     def gemm_only(reps):
         ev = []
@@ -941,12 +987,14 @@ def main():
     # quantisation runs underneath them and takes its share of power and issue slots)
     if not args.serial:
         torch.cuda.synchronize(dev)
+        if overlap:
+            for l in layers:
+                quantise_operands(l, 0)
         alone_ms = gemm_only(3)
         alone_tf = gemm_flops_step / (alone_ms * 1e-3) / 1e12
         roofline["achieved_alone"] = alone_tf
         roofline["frac_alone_of_burst"] = alone_tf / peak_burst
-        roofline["note"] = ("achieved/frac: live in the timed region, where the next layer's quantiser shares the GPU; "
-                            "achieved_alone: the same four launches back to back with nothing else running")
+        roofline["note"] = "achieved_alone: the four GEMM launches back to back with nothing else running, after everything else"
 
     # ---- sustained leg: the same step for >= args.sustained_seconds, clocks sampled throughout ----
     sustained = None
@@ -1119,7 +1167,9 @@ def main():
                 "config": {"workload": WORKLOAD, "M": M_TOKENS, "layers": {n: [k, nn] for n, k, nn in LAYERS},
                            "parallelism": f"N-sharded x{world}, X replicated, no data-path collective",
                            "step": "per layer: quantise X, quantise W shard, block-scaled GEMM"
-                                   + ("" if args.serial else "; quantisers of the next layer on a second, lower-priority stream"),
+                                   + ("; each GEMM is issued before the next layer's quantisers, which may start while it "
+                                      "runs (DW_QUANT_OVERLAP_PREVIOUS)" if overlap else
+                                      ("; quantisers of the next layer on a second, lower-priority stream" if args.two_streams else "")),
                            "l2": f"inputs larger than L2: {bytes_step / 1e9:.2f} GB touched per step per GPU",
                            "gemm_variant": args.variant,
                            **({"emulated_world": args.emulate_world,

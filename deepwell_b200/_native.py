@@ -27,6 +27,7 @@ DW_OK = 0
 DIR_ROW, DIR_COL_T, DIR_COL = 0, 1, 2
 RULE_OCP_FLOOR, RULE_REF_CEIL = 0, 1
 SF_FLAT, SF_TILED = 0, 1
+QUANT_OVERLAP_PREVIOUS = 1
 
 DIRECTIONS = {"row": DIR_ROW, "col": DIR_COL_T, "col_t": DIR_COL_T, "col_inplace": DIR_COL}
 RULES = {"ocp_floor": RULE_OCP_FLOOR, "ref_ceil": RULE_REF_CEIL}
@@ -40,7 +41,7 @@ ABI_SYMBOLS = (
     "dw_mxfp8_colsum_workspace", "dw_mxfp8_quantize_both_colsum", "dw_mxfp8_gemm_grouped",
     "dw_mxfp8_update_amax_history", "dw_mxfp8_gemm_planned", "dw_mxfp8_gemm_workspace_planned",
     "dw_mxfp8_selftest_bounded_wait", "dw_mxfp8_debug_fake_device", "dw_mxfp8_debug_counter",
-    "dw_mxfp8_quantize_set_tuning",
+    "dw_mxfp8_quantize_set_tuning", "dw_mxfp8_quantize_ex",
 )
 
 _lib = None
@@ -73,6 +74,7 @@ def load() -> ctypes.CDLL:
     L.dw_mxfp8_scale_bytes.restype = sz
     L.dw_mxfp8_quantize.argtypes = [p, p, p, i64, i64, i32, i32, i32, p]
     L.dw_mxfp8_quantize_set_tuning.argtypes = [i32]
+    L.dw_mxfp8_quantize_ex.argtypes = [p, p, p, i64, i64, i32, i32, i32, i32, p]
     L.dw_mxfp8_quantize_both.argtypes = [p, p, p, p, p, i64, i64, i32, i32, p]
     L.dw_mxfp8_dequantize.argtypes = [p, p, p, i64, i64, i32, p]
     L.dw_mxfp8_update_amax_history.argtypes = [p, p, i32, i64, p]

@@ -175,6 +175,11 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     if (kCtas == 2) ptx::cluster_sync();   // peer barriers initialised before any remote arrive
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Every CTA of this grid is resident and set up: a kernel that was launched behind this one on the same stream with
+    // programmatic stream serialisation (the quantiser of the next layer's operands, dw_mxfp8_quantize_ex with
+    // DW_QUANT_OVERLAP_PREVIOUS) may start now and take the SMs this grid does not occupy.  Without such a launch
+    // behind it the instruction does nothing.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     const uint32_t num_workers = gridDim.x / kCtas, worker = blockIdx.x / kCtas;
     const uint32_t num_units = p.num_tiles * p.splits;

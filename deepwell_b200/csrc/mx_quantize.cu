@@ -479,7 +479,7 @@ static int quantize_generic(const uint16_t* x, uint8_t* codes, uint8_t* scales, 
 }
 
 static int quantize_row_fast(const uint16_t* x, uint8_t* codes, uint8_t* scales, int64_t rows, int64_t cols, int rule,
-                             int layout, const DeviceInfo& di, cudaStream_t st) {
+                             int layout, int flags, const DeviceInfo& di, cudaStream_t st) {
     const int64_t total_chunks = rows * cols / 16;
     const FastDiv cpr = FastDiv::make(static_cast<uint32_t>(cols / 16));
     const int packed = (cols % 128 == 0) && aligned(scales, 4);
@@ -498,8 +498,24 @@ static int quantize_row_fast(const uint16_t* x, uint8_t* codes, uint8_t* scales,
         RowQuantJob job;
         if (!make_row_quant_job(&job, x, codes, scales, rows, cols, rule, layout)) return DW_ERR_BAD_ARG;
         const int64_t slabs = (total_chunks + 128 * kDeep - 1) / (128 * kDeep);
-        mx_quant_row_bg_kernel<kDeep><<<static_cast<unsigned>(std::min<int64_t>(slabs, 1ll << 30)), kRowSlabThreads, 0, st>>>(job);
-        return launch_status();
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(static_cast<unsigned>(std::min<int64_t>(slabs, 1ll << 30)));
+        cfg.blockDim = dim3(kRowSlabThreads);
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        if (flags & DW_QUANT_OVERLAP_PREVIOUS) {
+            // may start once the preceding kernel of this stream has released its dependents (the GEMM does so as soon
+            // as its CTAs are resident) instead of when it has finished; this kernel reads nothing that kernel writes
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+        }
+        if (cudaLaunchKernelEx(&cfg, mx_quant_row_bg_kernel<kDeep>, job) != cudaSuccess) {
+            cudaGetLastError();
+            return DW_ERR_LAUNCH;
+        }
+        return DW_OK;
     }
     if (aligned(x, 32))
         mx_quant_row_kernel<true><<<grid, 256, 0, st>>>(x, codes, scales, static_cast<uint32_t>(total_chunks), cpr, rule,
@@ -601,7 +617,12 @@ extern "C" DW_API size_t dw_mxfp8_scale_bytes(int64_t rows, int64_t k, int scale
 
 extern "C" DW_API int dw_mxfp8_quantize(const void* x_bf16, void* codes, void* scales, int64_t rows, int64_t cols, int direction,
                                  int scale_rule, int scale_layout, void* stream) {
-    if (rows < 0 || cols < 0) return DW_ERR_BAD_ARG;
+    return dw_mxfp8_quantize_ex(x_bf16, codes, scales, rows, cols, direction, scale_rule, scale_layout, 0, stream);
+}
+
+extern "C" DW_API int dw_mxfp8_quantize_ex(const void* x_bf16, void* codes, void* scales, int64_t rows, int64_t cols, int direction,
+                                    int scale_rule, int scale_layout, int flags, void* stream) {
+    if (rows < 0 || cols < 0 || (flags & ~DW_QUANT_OVERLAP_PREVIOUS) != 0) return DW_ERR_BAD_ARG;
     if (direction < DW_DIR_ROW || direction > DW_DIR_COL) return DW_ERR_BAD_ARG;
     if (scale_rule != DW_RULE_OCP_FLOOR && scale_rule != DW_RULE_REF_CEIL) return DW_ERR_BAD_ARG;
     if (scale_layout != DW_SF_FLAT && scale_layout != DW_SF_TILED) return DW_ERR_BAD_ARG;
@@ -618,7 +639,7 @@ extern "C" DW_API int dw_mxfp8_quantize(const void* x_bf16, void* codes, void* s
     uint8_t* s = static_cast<uint8_t*>(scales);
 
     if (direction == DW_DIR_ROW && cols % 32 == 0 && aligned(x, 16) && aligned(c, 16))
-        return quantize_row_fast(x, c, s, rows, cols, scale_rule, scale_layout, di, st);
+        return quantize_row_fast(x, c, s, rows, cols, scale_rule, scale_layout, flags, di, st);
     if (direction == DW_DIR_COL_T && tile_path_ok(x, rows, cols) && aligned(c, 16) &&
         (scale_layout == DW_SF_FLAT || aligned(s, 16))) {
         const uint32_t tiles_c = static_cast<uint32_t>((cols + 127) / 128);

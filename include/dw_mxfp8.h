@@ -71,6 +71,21 @@ size_t dw_mxfp8_scale_bytes(int64_t rows, int64_t k, int scale_layout);
 int dw_mxfp8_quantize(const void *x_bf16, void *codes, void *scales, int64_t rows, int64_t cols,
                       int direction, int scale_rule, int scale_layout, void *stream);
 
+/* dw_mxfp8_quantize with launch flags.  DW_QUANT_OVERLAP_PREVIOUS: the launch need not wait for the kernel issued just
+ * before it on the same stream to finish (programmatic dependent launch): it starts as soon as that kernel lets its
+ * dependents go, which dw_mxfp8_gemm's kernel does once all its thread blocks are resident.  The pattern it serves:
+ *     dw_mxfp8_gemm(layer i)  ->  dw_mxfp8_quantize_ex(operands of layer i + 1, DW_QUANT_OVERLAP_PREVIOUS)  ->  dw_mxfp8_gemm(layer i + 1)
+ * on one stream.  The GEMM, issued first, takes the SMs it needs (it uses the smallest number that keeps its number
+ * of rounds of tiles); the quantiser's short-lived thread blocks run on the SMs that leaves free, and on all of them
+ * once the GEMM's blocks retire.  (Launched the other way round, or on a second stream, the quantiser fills every SM
+ * first and the GEMM waits for it: nothing is scheduled beside a GEMM thread block on its own SM.)  Only for x, codes
+ * and scales that the preceding kernel neither reads nor writes; the next ordinary launch on the stream still waits
+ * for both kernels.  The flag takes effect on the large-input row-wise path and is ignored elsewhere.
+ * The reference has one launch shape and no overlap (csrc/mxfp8_quantization.cu:232-240). */
+#define DW_QUANT_OVERLAP_PREVIOUS 1
+int dw_mxfp8_quantize_ex(const void *x_bf16, void *codes, void *scales, int64_t rows, int64_t cols,
+                         int direction, int scale_rule, int scale_layout, int flags, void *stream);
+
 /* Tuning switch of the column-wise (transposed-payload) kernel, process-wide: bits [0,2) = 0 automatic (the transposed
  * payload is written through a shared-memory staging buffer, whole 128-byte row segments per store, when its rows are
  * 1 MiB apart or more (2 MiB for the fused both-forms call), i.e. rows >= 2^20 (2^21); straight from registers otherwise), 1 never staged, 2 always staged.  Same
