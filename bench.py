@@ -23,8 +23,9 @@ Prints ONE JSON line (rank 0).  Keys beyond the basic contract:
                      the power cap, which the short timed region does not reach
   roofline_quantize  the row quantiser on the largest activation, against the measured copy bandwidth
   vendor_gemm        the vendor's block-scaled GEMM (torch._scaled_mm) alternated with ours on the same operands
-  gpt2_mlp, decoder_step   two secondary workloads (GPT-2-small MLP forward+backward; the end-to-end optimize()
-                     training step of a 12-layer decoder), each beside the same layers in bf16 (N = 1 only)
+  gpt2_mlp, swiglu_mlp, decoder_step   secondary workloads (GPT-2-small MLP forward+backward; the Llama-3-8B gated MLP
+                     with and without the SwiGLU epilogue; the end-to-end optimize() training step of a 12-layer
+                     decoder), each beside the same layers in bf16 (N = 1 only)
   with_gather, sharded     N > 1: the step with every layer's output all-gathered over NVLink, and a parity check of
                      ColumnParallelDWLinear / RowParallelDWLinear under NCCL against the unsharded layer
   cpu_baseline       the CPU restatement of the same path on the host cores (rank 0, N = 1)
@@ -34,7 +35,8 @@ for the GEMM stage is a Python module calling torch.matmul, which is loaded from
 baseline/_ref when that is present).
 
 Other modes (each prints its own JSON): --workload decoder_step, --sweep-quantize (quantise-only bandwidth sweep),
---compare-vendor, --profile-case (a few launches of one kernel on a small case, for an ncu capture),
+--compare-vendor, --probe-corun (what runs beside the GEMM), --profile-case (a few launches of one kernel on a small
+case, for an ncu capture),
 --traffic-from-csv (turns an ncu CSV of the GEMM launches into bench_gemm_dram_traffic.json),
 --emulate-world W (tuning aid: rank 0's shard sizes of a W-GPU job on one GPU).
 """
@@ -251,14 +253,15 @@ def run_profile_case(args):
                                       M, N, K, 1.0, 0.0, None, 0, sw.data_ptr(), st)
         units = f"gemm M={M} N={N} K={K}: {2.0 * M * N * K / 1e9:.1f} GFLOP per launch"
     else:
-        R, C = 16384, 8192
+        # quant_col_long: 2^21 rows, the transposed payload's rows 2 MiB apart (staged write-out)
+        R, C = ((1 << 21), 128) if args.profile_case == "quant_col_long" else (16384, 8192)
         x = torch.randn(R, C, device=dev, generator=g).bfloat16()
         cr, ct = u8(R, C), u8(C, R)
         sr, sc = u8(nv.scale_bytes(R, C, 1)), u8(nv.scale_bytes(C, R, 1))
         if args.profile_case == "quant_row":
             run = lambda: L.dw_mxfp8_quantize(x.data_ptr(), cr.data_ptr(), sr.data_ptr(), R, C, 0, 0, 1, st)
             bpe = 3.03125
-        elif args.profile_case == "quant_col":
+        elif args.profile_case in ("quant_col", "quant_col_long"):
             run = lambda: L.dw_mxfp8_quantize(x.data_ptr(), ct.data_ptr(), sc.data_ptr(), R, C, 1, 0, 1, st)
             bpe = 3.03125
         else:
@@ -451,6 +454,104 @@ def run_compare_vendor(args):
 
 
 # ----------------------------------------------------------------------------------------------
+# what runs beside the GEMM?  (evidence for the step's launch order)
+# ----------------------------------------------------------------------------------------------
+def run_probe_corun(args):
+    """Stream A: one long GEMM.  Stream B, released when A reaches the GEMM: a one-block kernel, a 256 MB device copy, the
+    row quantiser of a 16384 x 14336 activation.  Reported: when B's work was done, counted from the start of the GEMM,
+    beside the durations of both alone; for the quantiser also the single-stream order GEMM -> quantiser with and
+    without DW_QUANT_OVERLAP_PREVIOUS.  The first GEMM shape occupies 64 of the 74 CTA pairs (20 SMs free), the others all."""
+    from deepwell_b200 import _native as nv
+    L = nv.load()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    lo, hi = torch.cuda.Stream.priority_range()
+    sw = nv.status_word(dev)
+    QM, QK = 16384, 14336
+    qx = torch.randn(QM, QK, device=dev).bfloat16()
+    qc = torch.empty(QM, QK, dtype=torch.uint8, device=dev)
+    qs = torch.empty(nv.scale_bytes(QM, QK, nv.SF_TILED), dtype=torch.uint8, device=dev)
+    small = torch.zeros(32, device=dev)
+    big_src = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    big_dst = torch.empty_like(big_src)
+
+    def alone(fn, st, n=5):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(st)
+        for _ in range(n):
+            fn()
+        e1.record(st)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n * 1e3
+
+    def median(v):
+        return sorted(v)[len(v) // 2]
+
+    rows = []
+    for (M, N, K) in [(32768, 768, 14336), (16384, 28672, 4096), (16384, 4096, 14336)]:
+        g = torch.Generator(device=dev).manual_seed(M + N)
+        x = torch.randn(M, K, device=dev, generator=g).bfloat16()
+        w = (torch.randn(N, K, device=dev, generator=g) * 0.02).bfloat16()
+        xc, xs = nv.quantize(x, nv.DIR_ROW, 0, nv.SF_TILED)
+        wc, ws = nv.quantize(w, nv.DIR_ROW, 0, nv.SF_TILED)
+        y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        del x, w
+        sa, sb = torch.cuda.Stream(dev, priority=hi), torch.cuda.Stream(dev, priority=lo)
+        gemm = lambda s: nv.check(L.dw_mxfp8_gemm(xc.data_ptr(), xs.data_ptr(), wc.data_ptr(), ws.data_ptr(), y.data_ptr(), None,
+                                                  M, N, K, 1.0, 0.0, None, 0, sw.data_ptr(), s.cuda_stream), "gemm")
+
+        def work(kind, s, flags=0):
+            with torch.cuda.stream(s):
+                if kind == "one_block_kernel":
+                    small.add_(1.0)
+                elif kind == "copy_256MB":
+                    big_dst.copy_(big_src)
+                else:
+                    nv.check(L.dw_mxfp8_quantize_ex(qx.data_ptr(), qc.data_ptr(), qs.data_ptr(), QM, QK, nv.DIR_ROW, 0, nv.SF_TILED,
+                                                    flags, s.cuda_stream), "quantize")
+
+        gemm_alone = alone(lambda: gemm(sa), sa)
+        for kind in ("one_block_kernel", "copy_256MB", "quantize_rowwise"):
+            b_alone = alone(lambda: work(kind, sb), sb)
+            tg, tb = [], []
+            for _ in range(5):
+                torch.cuda.synchronize()
+                a0, a1, b1 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+                a0.record(sa)
+                gemm(sa)
+                a1.record(sa)
+                sb.wait_event(a0)
+                work(kind, sb)
+                b1.record(sb)
+                torch.cuda.synchronize()
+                tg.append(a0.elapsed_time(a1) * 1e3)
+                tb.append(a0.elapsed_time(b1) * 1e3)
+            row = {"gemm": [M, N, K], "gemm_alone_us": round(gemm_alone, 1), "other_work": kind, "other_alone_us": round(b_alone, 1),
+                   "second_stream": {"gemm_us": round(median(tg), 1), "other_done_at_us": round(median(tb), 1)}}
+            if kind == "quantize_rowwise":
+                for name, flags in (("same_stream_overlap_previous", nv.QUANT_OVERLAP_PREVIOUS), ("same_stream_plain", 0)):
+                    t = []
+                    for _ in range(5):
+                        torch.cuda.synchronize()
+                        a0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        a0.record(sa)
+                        gemm(sa)
+                        work(kind, sa, flags)
+                        b1.record(sa)
+                        torch.cuda.synchronize()
+                        t.append(a0.elapsed_time(b1) * 1e3)
+                    row[name] = {"both_done_at_us": round(median(t), 1)}
+            rows.append(row)
+            print(json.dumps(row), flush=True)
+        del xc, xs, wc, ws, y
+    nv.check_status(dev)
+    print(json.dumps({"probe": "corun", "cases": len(rows)}))
+
+
+# ----------------------------------------------------------------------------------------------
 # Secondary workloads
 # ----------------------------------------------------------------------------------------------
 def build_decoder(vocab, hidden, heads, ffn, layers):
@@ -605,6 +706,52 @@ def gpt2_mlp_numbers(reps=30):
     return res
 
 
+def swiglu_mlp_numbers(reps=10):
+    """The Llama-3-8B MLP at 16384 tokens (hidden 4096, intermediate 14336), forward without autograd: gate+up projection,
+    silu(gate) * up, down projection.  Fused: one quantiser launch and two GEMMs, the gated product formed in the first
+    GEMM's epilogue and written as the second GEMM's quantised operand (FusedSwiGLUMLP).  Unfused: the same module with
+    three MXFP8 layers and torch's silu and product in bf16 between them.  Beside both, three bf16 nn.Linear layers."""
+    import torch.nn as nn
+    import torch.nn.functional as F
+    from deepwell_b200.kernels.blackwell_production import FusedSwiGLUMLP
+    dev = torch.device("cuda", torch.cuda.current_device())
+    h, f, m = 4096, 14336, M_TOKENS
+    torch.manual_seed(99)
+    mlp = FusedSwiGLUMLP(h, f).to(dev)
+    with torch.no_grad():
+        for lin in (mlp.gate_proj, mlp.up_proj, mlp.down_proj):
+            lin.weight.normal_(0.0, 0.02)
+    x = torch.randn(m, h, device=dev).bfloat16()
+    gate, up, down = (nn.Linear(a, b, bias=False).to(dev).bfloat16() for a, b in ((h, f), (h, f), (f, h)))
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        return e0.elapsed_time(e1) / reps * 1e3
+
+    res = {"tokens": m, "hidden": h, "intermediate": f, "gflop": 6.0 * m * h * f / 1e9}
+    with torch.no_grad():
+        mlp.fuse = True
+        y_fused = mlp(x)
+        res["fused_us"] = timed(lambda: mlp(x))
+        mlp.fuse = False
+        y_three = mlp(x)
+        res["unfused_mxfp8_us"] = timed(lambda: mlp(x))
+        mlp.fuse = True
+        res["bf16_nn_linear_us"] = timed(lambda: down(F.silu(gate(x)) * up(x)))
+    res["fused_vs_unfused_rel_frobenius"] = float((y_fused.float() - y_three.float()).norm() / y_three.float().norm())
+    res["speedup_fused_vs_unfused"] = res["unfused_mxfp8_us"] / res["fused_us"]
+    res["speedup_fused_vs_bf16"] = res["bf16_nn_linear_us"] / res["fused_us"]
+    res["fused_tflops"] = res["gflop"] / res["fused_us"] / 1e3
+    return res
+
+
 # ----------------------------------------------------------------------------------------------
 # N > 1: the sharded modules under NCCL, checked against the unsharded layer
 # ----------------------------------------------------------------------------------------------
@@ -743,12 +890,14 @@ def main():
     ap.add_argument("--sweep-log2-max", type=int, default=32)
     ap.add_argument("--compare-vendor", action="store_true",
                     help="alternate the vendor block-scaled GEMM (torch._scaled_mm) with dw_mxfp8_gemm on the workload's shapes")
+    ap.add_argument("--probe-corun", action="store_true",
+                    help="measure what runs beside the GEMM (a second stream's kernel, copy, quantiser) and exit")
     ap.add_argument("--traffic-from-csv", default=None, help="ncu CSV of the GEMM launches -> bench_gemm_dram_traffic.json")
     ap.add_argument("--emulate-world", type=int, default=0,
                     help="tuning aid: on one GPU, run the shard sizes rank 0 would get in a job of this many GPUs")
     ap.add_argument("--serial", action="store_true", help="quantise and GEMM on one stream, every launch after the previous one has finished")
     ap.add_argument("--two-streams", action="store_true", help="the next layer's quantisers on a second, lower-priority stream")
-    ap.add_argument("--profile-case", default=None, choices=["gemm", "quant_row", "quant_both", "quant_col"],
+    ap.add_argument("--profile-case", default=None, choices=["gemm", "quant_row", "quant_both", "quant_col", "quant_col_long"],
                     help="run a few launches of one kernel on a small case (for an ncu capture) and exit")
     ap.add_argument("--workload", default="linears", choices=["linears", "decoder_step"],
                     help="linears: the headline Llama-3-8B linear shapes; decoder_step: end-to-end optimize() training step (1 GPU)")
@@ -773,6 +922,10 @@ def main():
     if args.compare_vendor:
         if rank == 0:
             run_compare_vendor(args)
+        return
+    if args.probe_corun:
+        if rank == 0:
+            run_probe_corun(args)
         return
     if args.workload == "decoder_step":
         if rank == 0:
@@ -1143,7 +1296,7 @@ def main():
             extra["sharded_parity"] = extra["sharded"].get("parity")
         elif rank == 0:
             for key, fn in (("vendor_gemm", lambda: compare_vendor(dev, {n: (M_TOKENS, nn, k) for n, k, nn in LAYERS})),
-                            ("gpt2_mlp", gpt2_mlp_numbers),
+                            ("gpt2_mlp", gpt2_mlp_numbers), ("swiglu_mlp", swiglu_mlp_numbers),
                             ("decoder_step", lambda: decoder_step_numbers(steps=5, warmup=3))):
                 try:
                     for l in layers:                      # the headline tensors are no longer needed
