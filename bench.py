@@ -748,7 +748,7 @@ def swiglu_mlp_numbers(reps=10):
     res["fused_vs_unfused_rel_frobenius"] = float((y_fused.float() - y_three.float()).norm() / y_three.float().norm())
     res["speedup_fused_vs_unfused"] = res["unfused_mxfp8_us"] / res["fused_us"]
     res["speedup_fused_vs_bf16"] = res["bf16_nn_linear_us"] / res["fused_us"]
-    res["fused_tflops"] = res["gflop"] / res["fused_us"] / 1e3
+    res["fused_tflops"] = res["gflop"] / res["fused_us"] * 1e3
     return res
 
 
@@ -1178,7 +1178,7 @@ def main():
     torch.cuda.synchronize(dev)
     q_ms = qe0.elapsed_time(qe1) / reps
     q_gbs = M_TOKENS * big["k"] * 3.03125 / (q_ms * 1e-3) / 1e9
-    roofline_q = {"bound": "hbm", "kernel": "mx_quant_row_kernel", "achieved": q_gbs, "peak": peaks["hbm_gbs"],
+    roofline_q = {"bound": "hbm", "kernel": "mx_quant_row_bg_kernel", "achieved": q_gbs, "peak": peaks["hbm_gbs"],
                   "unit": "GB/s", "frac": q_gbs / peaks["hbm_gbs"], "frac_of_nominal_8000": q_gbs / 8000.0,
                   "shape": [M_TOKENS, big["k"]], "bytes_per_element": 3.03125}
 
