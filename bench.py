@@ -1263,8 +1263,10 @@ def main():
                     hy.copy_(y, non_blocking=True)
                     y.record_stream(s_out)
                 outs.append(y)
-            torch.cuda.synchronize(dev)
 
+        # Steps follow one another without a host synchronisation in between (the device-side events above order every
+        # buffer's reuse), so the download of step s overlaps the upload of step s + 1: PCIe carries both directions
+        # all the time.  Every step's copies are inside the timed region, which ends when the last download has landed.
         for _ in range(2):
             e2e_step()
         barrier()
@@ -1280,7 +1282,7 @@ def main():
                "d2h_bytes_per_step": int(sum(hy.numel() * 2 for hy in host_y)) * world, "ms_per_step": dt * 1e3,
                "steps": args.e2e_steps, "warmup": 2,
                "api": "deepwell_b200.cutlass_kernels.BlackwellGemmKernel.gemm, pinned host X in, pinned host Y out, "
-                      "copies on their own streams" + ("; X uploaded as 1/N row slices and all-gathered over NVLink"
+                      "copies on their own streams, steps back to back" + ("; X uploaded as 1/N row slices and all-gathered over NVLink"
                                                        if even_rows else "")}
         nv.check_status(dev)
         del host_x, host_y, dev_x, kernels

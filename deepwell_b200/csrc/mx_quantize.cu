@@ -149,11 +149,15 @@ constexpr int kTileSmemBytes = 2 * 128 * 16 * 16 + 1024 + 2048;   // two 32 KB t
 // The direct form writes each thread's 32 codes straight from registers: a warp's store then touches 32 different
 // output rows, `rows` bytes apart.  Once that stride reaches the page size (rows >= 2^20 or so) every store instruction
 // needs 32 address translations and the kernel falls to half its rate; staged, it needs four.
-template <bool kDoRow, bool kDoCol, bool kColSum = false, bool kStaged = false>
-__global__ void __launch_bounds__(256)
+// kSplit (fused both-forms only): 512 threads, threads 0-255 run the row pass of a tile while threads 256-511 run its
+// column pass, instead of 256 threads running one pass after the other: the two passes only read the tile, so they
+// overlap, and a tile is done in the time of the longer one.
+template <bool kDoRow, bool kDoCol, bool kColSum = false, bool kStaged = false, bool kSplit = false>
+__global__ void __launch_bounds__(kSplit ? 512 : 256, kSplit ? 2 : 1)
 mx_quant_tile_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes_row, uint8_t* __restrict__ scales_row,
                      uint8_t* __restrict__ codes_col_t, uint8_t* __restrict__ scales_col, int64_t rows, int64_t cols,
                      uint32_t tiles_c, uint32_t num_tiles, int rule, int layout, float* __restrict__ colsum_partial = nullptr) {
+    static_assert(!kSplit || (kDoRow && kDoCol), "the split form is for the fused both-forms kernel");
     // Persistent CTA, two tile buffers: the 16-byte cp.async copies of the next tile are in flight
     // while this tile is quantised, so the SM always has loads outstanding.
     extern __shared__ __align__(16) uint8_t tile_smem[];
@@ -162,14 +166,20 @@ mx_quant_tile_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes
     uint8_t* sf_col = sf_row + 512;
     float* cs_stage = reinterpret_cast<float*>(sf_col + 512);       // [4 row blocks][128 columns]
 
-    const uint32_t t = threadIdx.x;
-    const uint32_t cc = t & 15u;
+    constexpr uint32_t kThreads = kSplit ? 512u : 256u;
+    constexpr int kCopies = kSplit ? 2 : 4;                          // 16-byte copies per thread and half tile
+    constexpr uint32_t kCopyRows = kThreads / 16u;                   // rows covered by one copy of every thread
+    const uint32_t tid = threadIdx.x;
+    const uint32_t t = tid & 255u;                                   // index inside the pass's group of 256 threads
+    const bool row_role = kDoRow && (!kSplit || tid < 256u);
+    const bool col_role = kDoCol && (!kSplit || tid >= 256u);
+    const uint32_t cc = tid & 15u;
     const int64_t kb_row = cols >> 5, kb_col = rows >> 5;           // k-blocks per operand row
     const int64_t kt_row = (kb_row + 3) >> 2, kt_col = (kb_col + 3) >> 2;
     const bool wide_rows = (reinterpret_cast<uintptr_t>(codes_row) & 31) == 0;   // 32-byte stores of the row payload
     const bool wide_cols = (reinterpret_cast<uintptr_t>(codes_col_t) & 31) == 0; // and of the transposed payload (rows % 32 == 0)
 
-    // Copies rows [64 half, 64 half + 64) of tile `id` into buffer `buf` (16-byte cp.async, 4 per thread); the
+    // Copies rows [64 half, 64 half + 64) of tile `id` into buffer `buf` (16-byte cp.async, kCopies per thread); the
     // second half also closes the copy group.  The two halves of the next tile are issued before the row pass and
     // before the column pass of the current one, which keeps the request stream to HBM even.
     auto issue_half = [&](uint32_t id, int buf, int half) {
@@ -177,20 +187,20 @@ mx_quant_tile_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes
         const int64_t ir0 = static_cast<int64_t>(itr) * 128, igc = static_cast<int64_t>(itc) * 128 + cc * 8;
         TilePtr dst = reinterpret_cast<TilePtr>(tile_smem + buf * (128 * 16 * 16));
         if (ir0 + 128 <= rows && static_cast<int64_t>(itc) * 128 + 128 <= cols) {
-            // whole tile inside the matrix (the common case): no per-row guards; the rows of a thread are 16 rows
-            // apart, so they share the swizzled chunk position (row & 7 is the same) and differ by constant strides
-            // in both address spaces
-            const uint32_t row0 = (t >> 4) + 64 * half;
+            // whole tile inside the matrix (the common case): no per-row guards; the rows of a thread are a multiple of
+            // 16 rows apart, so they share the swizzled chunk position (row & 7 is the same) and differ by constant
+            // strides in both address spaces
+            const uint32_t row0 = (tid >> 4) + 64 * half;
             const uint16_t* src = x + (ir0 + row0) * cols + igc;
             const uint32_t d0 = smem_u32(&dst[row0][tile_chunk(cc, row0)]);
-            const int64_t step = 16 * cols;
+            const int64_t step = static_cast<int64_t>(kCopyRows) * cols;
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d0 + j * 4096), "l"(src + j * step) : "memory");
+            for (int j = 0; j < kCopies; ++j)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d0 + j * (kCopyRows * 256u)), "l"(src + j * step) : "memory");
         } else {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const uint32_t row = (t >> 4) + 64 * half + 16 * j;
+            for (int j = 0; j < kCopies; ++j) {
+                const uint32_t row = (tid >> 4) + 64 * half + kCopyRows * j;
                 const int64_t gr = ir0 + row;
                 const bool ok = gr < rows && igc < cols;
                 const uint16_t* src = ok ? x + gr * cols + igc : x;      // out of range: zero fill, nothing read
@@ -212,7 +222,7 @@ mx_quant_tile_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes
     const uint32_t tr = id / tiles_c, tc = id - tr * tiles_c;
     const int64_t r0 = static_cast<int64_t>(tr) * 128, c0 = static_cast<int64_t>(tc) * 128;
 
-    if (kDoRow) {
+    if (row_role) {
         // one thread = one whole 32-element block (row r, block b): four 16-byte chunks, no shuffles;
         // four consecutive lanes cover the 128 bytes of codes of one row, so stores stay coalesced.
         const uint32_t b = t & 3u;
@@ -243,19 +253,20 @@ mx_quant_tile_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes
             }
             sf_row[(r & 31u) * 16 + (r >> 5) * 4 + b] = static_cast<uint8_t>(sb);
         }
-        // Measured: on long runs of tiles the passes run slightly faster when the warps enter the column pass
-        // together; on short runs (a few tiles per CTA) the extra barrier costs ~10 %.
-        if (kDoCol && num_tiles > 8u * gridDim.x) __syncthreads();
     }
+    // Measured (one group of threads running both passes): on long runs of tiles the passes run slightly faster when
+    // the warps enter the column pass together; on short runs (a few tiles per CTA) the extra barrier costs ~10 %.
+    if (!kSplit && kDoRow && kDoCol && num_tiles > 8u * gridDim.x) __syncthreads();
 
     if (next < num_tiles) issue_half(next, buf ^ 1, 1);
-    if (kDoCol) {
-        // thread = (column pair p, row block rb): 32 words down the rows, two columns at once
-        const uint32_t p = t & 63u, rb = t >> 6;
+    uint32_t qa[8], qb[8];                                // the column pass's codes: 32 rows of two columns
+    const uint32_t p = t & 63u, rb = t >> 6;              // column pass: thread = (column pair p, row block rb)
+    if (col_role) {
+        // 32 words down the rows, two columns at once
         const uint32_t* tw = reinterpret_cast<const uint32_t*>(&tile[0][0]);
         uint32_t w[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i)      // chunk index XORed with the row, as written by issue_tile
+        for (int i = 0; i < 32; ++i)      // chunk index XORed with the row, as written by issue_half
             w[i] = tw[(rb * 32 + i) * 64 + ((tile_chunk(p >> 2, i) << 2) | (p & 3u))];
         if (kColSum) {      // rows beyond the matrix were zero-filled, so they add nothing
             float sum_a = 0.0f, sum_b = 0.0f;
@@ -275,7 +286,6 @@ mx_quant_tile_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes
         if (amax_b > 0x7F80u) amax_b = 0;
         const uint32_t sb_a = e8m0_from_amax(amax_a, rule), sb_b = e8m0_from_amax(amax_b, rule);
         const uint32_t inv2 = (e8m0_inverse_bf16x2(sb_a) & 0xFFFFu) | (e8m0_inverse_bf16x2(sb_b) & 0xFFFF0000u);
-        uint32_t qa[8], qb[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             uint32_t ca[2], cb[2];
@@ -290,30 +300,39 @@ mx_quant_tile_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes
             qa[i] = __byte_perm(ca[0], ca[1], 0x5410);
             qb[i] = __byte_perm(cb[0], cb[1], 0x5410);
         }
+        const uint32_t ca = 2 * p, cb = 2 * p + 1;
+        sf_col[(ca & 31u) * 16 + (ca >> 5) * 4 + rb] = static_cast<uint8_t>(sb_a);
+        sf_col[(cb & 31u) * 16 + (cb >> 5) * 4 + rb] = static_cast<uint8_t>(sb_b);
+    }
+    if (kDoCol) {
         const int64_t gcol = c0 + 2 * p, grow = r0 + rb * 32;
         if (kStaged) {
             // stage[c][128 bytes]: the 16-byte piece j of output row c sits at piece j ^ ((c >> 1) & 7), which spreads a
             // warp's stores (32 different rows, same pieces) over all banks
             __syncthreads();                                   // every thread has read its part of the tile
             uint8_t* stage = tile_smem + buf * (128 * 16 * 16);
-            const uint32_t sw = p & 7u;
+            if (col_role) {
+                const uint32_t sw = p & 7u;
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const uint32_t piece = (2 * rb + h) ^ sw;
-                *reinterpret_cast<uint4*>(stage + (2 * p) * 128 + piece * 16) = make_uint4(qa[4 * h], qa[4 * h + 1], qa[4 * h + 2], qa[4 * h + 3]);
-                *reinterpret_cast<uint4*>(stage + (2 * p + 1) * 128 + piece * 16) = make_uint4(qb[4 * h], qb[4 * h + 1], qb[4 * h + 2], qb[4 * h + 3]);
+                for (int h = 0; h < 2; ++h) {
+                    const uint32_t piece = (2 * rb + h) ^ sw;
+                    *reinterpret_cast<uint4*>(stage + (2 * p) * 128 + piece * 16) = make_uint4(qa[4 * h], qa[4 * h + 1], qa[4 * h + 2], qa[4 * h + 3]);
+                    *reinterpret_cast<uint4*>(stage + (2 * p + 1) * 128 + piece * 16) = make_uint4(qb[4 * h], qb[4 * h + 1], qb[4 * h + 2], qb[4 * h + 3]);
+                }
             }
             __syncthreads();
-            const uint32_t warp = t >> 5, lane = t & 31u;
-            const int64_t row_bytes = (rows - r0) < 128 ? (rows - r0) : 128;      // valid bytes of every output row of this tile
+            if (col_role) {
+                const uint32_t warp = t >> 5, lane = t & 31u;
+                const int64_t row_bytes = (rows - r0) < 128 ? (rows - r0) : 128;      // valid bytes of every output row of this tile
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const uint32_t c = i * 32 + warp * 4 + (lane >> 3), j = lane & 7u;
-                const uint4 v = *reinterpret_cast<const uint4*>(stage + c * 128 + ((j ^ ((c >> 1) & 7u)) * 16));
-                if (c0 + c < cols && static_cast<int64_t>(j) * 16 < row_bytes)
-                    stg_v4(codes_col_t + (c0 + c) * rows + r0 + j * 16, v);
+                for (int i = 0; i < 4; ++i) {
+                    const uint32_t c = i * 32 + warp * 4 + (lane >> 3), j = lane & 7u;
+                    const uint4 v = *reinterpret_cast<const uint4*>(stage + c * 128 + ((j ^ ((c >> 1) & 7u)) * 16));
+                    if (c0 + c < cols && static_cast<int64_t>(j) * 16 < row_bytes)
+                        stg_v4(codes_col_t + (c0 + c) * rows + r0 + j * 16, v);
+                }
             }
-        } else if (grow < rows) {
+        } else if (col_role && grow < rows) {
             // 32 codes of one column = one whole 32-byte sector: a single 256-bit store when the payload allows
             auto store32 = [&](uint8_t* d, const uint32_t (&q)[8]) {
                 if (wide_cols) {
@@ -327,35 +346,35 @@ mx_quant_tile_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes
             if (gcol < cols) store32(codes_col_t + gcol * rows + grow, qa);
             if (gcol + 1 < cols) store32(codes_col_t + (gcol + 1) * rows + grow, qb);
         }
-        const uint32_t ca = 2 * p, cb = 2 * p + 1;
-        sf_col[(ca & 31u) * 16 + (ca >> 5) * 4 + rb] = static_cast<uint8_t>(sb_a);
-        sf_col[(cb & 31u) * 16 + (cb >> 5) * 4 + rb] = static_cast<uint8_t>(sb_b);
     }
     // One barrier per tile after both passes: the tile buffer is free for the copy issued at the top of the
     // next iteration, and the staged scale bytes (and column sums) are complete.  The next tile's passes
     // write the staging areas only after the barrier at the top of the loop, which the threads that copy the
     // staged bytes out (below) reach only when they are done.
     __syncthreads();
-    if (kDoRow) {  // scales of the row-wise operand [rows, cols/32]: warp 0 (tiled) or warps 0-3 (flat)
+    if (kDoRow) {  // scales of the row-wise operand [rows, cols/32]: the first warp (tiled) or four warps (flat) of the row group
         if (layout == DW_SF_TILED) {
-            if (t < 32) {
+            if (tid < 32) {
                 uint4* dst = reinterpret_cast<uint4*>(scales_row + (static_cast<int64_t>(tr) * kt_row + tc) * 512);
-                dst[t] = reinterpret_cast<const uint4*>(sf_row)[t];
+                dst[tid] = reinterpret_cast<const uint4*>(sf_row)[tid];
             }
-        } else if (t < 128) {
-            const int64_t gr = r0 + t, kb0 = static_cast<int64_t>(tc) * 4;
+        } else if (tid < 128) {
+            const int64_t gr = r0 + tid, kb0 = static_cast<int64_t>(tc) * 4;
             if (gr < rows) {
 #pragma unroll
                 for (int b = 0; b < 4; ++b)
-                    if (kb0 + b < kb_row) scales_row[gr * kb_row + kb0 + b] = sf_row[(t & 31u) * 16 + (t >> 5) * 4 + b];
+                    if (kb0 + b < kb_row) scales_row[gr * kb_row + kb0 + b] = sf_row[(tid & 31u) * 16 + (tid >> 5) * 4 + b];
             }
         }
     }
-    if (kDoCol) {  // scales of the column-wise operand [cols, rows/32]: warp 7 (tiled) or warps 4-7 (flat)
-        const uint32_t u = 255u - t;
-        if (kColSum && t < 128 && c0 + t < cols)
-            colsum_partial[static_cast<int64_t>(tr) * cols + c0 + t] =
-                (cs_stage[t] + cs_stage[128 + t]) + (cs_stage[256 + t] + cs_stage[384 + t]);
+    if (kDoCol) {  // scales of the column-wise operand [cols, rows/32]: the last warp (tiled) or last four warps (flat) of the CTA
+        const uint32_t u = kThreads - 1u - tid;
+        if (kColSum && u >= 128u && u < 256u) {
+            const uint32_t c = u - 128u;
+            if (c0 + c < cols)
+                colsum_partial[static_cast<int64_t>(tr) * cols + c0 + c] =
+                    (cs_stage[c] + cs_stage[128 + c]) + (cs_stage[256 + c] + cs_stage[384 + c]);
+        }
         if (layout == DW_SF_TILED) {
             if (u < 32) {
                 uint4* dst = reinterpret_cast<uint4*>(scales_col + (static_cast<int64_t>(tc) * kt_col + tr) * 512);
@@ -528,7 +547,7 @@ static int quantize_row_fast(const uint16_t* x, uint8_t* codes, uint8_t* scales,
 
 static std::atomic<int> g_quant_tuning{0};     // dw_mxfp8_quantize_set_tuning
 
-template <bool kDoRow, bool kDoCol, bool kColSum = false, bool kStaged = false>
+template <bool kDoRow, bool kDoCol, bool kColSum = false, bool kStaged = false, bool kSplit = false>
 static int launch_tile_kernel_impl(const uint16_t* x, uint8_t* cr, uint8_t* sr, uint8_t* ct, uint8_t* sc, int64_t rows, int64_t cols,
                                    uint32_t tiles_c, uint32_t tiles, int rule, int layout, const DeviceInfo& di, cudaStream_t st,
                                    float* colsum_partial = nullptr) {
@@ -537,7 +556,7 @@ static int launch_tile_kernel_impl(const uint16_t* x, uint8_t* cr, uint8_t* sr, 
         static bool done[kMaxDevices] = {};
         std::lock_guard<std::mutex> lock(mu);
         if (!done[di.device]) {
-            if (cudaFuncSetAttribute(mx_quant_tile_kernel<kDoRow, kDoCol, kColSum, kStaged>,
+            if (cudaFuncSetAttribute(mx_quant_tile_kernel<kDoRow, kDoCol, kColSum, kStaged, kSplit>,
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, kTileSmemBytes) != cudaSuccess) {
                 cudaGetLastError();
                 return DW_ERR_LAUNCH;
@@ -545,9 +564,10 @@ static int launch_tile_kernel_impl(const uint16_t* x, uint8_t* cr, uint8_t* sr, 
             done[di.device] = true;
         }
     }
-    const uint32_t grid = std::min<uint32_t>(tiles, static_cast<uint32_t>(di.sms) * 3u);   // 3 CTAs of 65 KB per SM
-    mx_quant_tile_kernel<kDoRow, kDoCol, kColSum, kStaged><<<grid, 256, kTileSmemBytes, st>>>(x, cr, sr, ct, sc, rows, cols, tiles_c,
-                                                                                             tiles, rule, layout, colsum_partial);
+    // 3 CTAs of 256 threads and 67 KB per SM, or 2 CTAs of 512 threads (kSplit)
+    const uint32_t grid = std::min<uint32_t>(tiles, static_cast<uint32_t>(di.sms) * (kSplit ? 2u : 3u));
+    mx_quant_tile_kernel<kDoRow, kDoCol, kColSum, kStaged, kSplit><<<grid, kSplit ? 512 : 256, kTileSmemBytes, st>>>(
+        x, cr, sr, ct, sc, rows, cols, tiles_c, tiles, rule, layout, colsum_partial);
     return launch_status();
 }
 
@@ -557,8 +577,18 @@ template <bool kDoRow, bool kDoCol, bool kColSum = false>
 static int launch_tile_kernel(const uint16_t* x, uint8_t* cr, uint8_t* sr, uint8_t* ct, uint8_t* sc, int64_t rows, int64_t cols,
                               uint32_t tiles_c, uint32_t tiles, int rule, int layout, const DeviceInfo& di, cudaStream_t st,
                               float* colsum_partial = nullptr) {
-    const int mode = g_quant_tuning.load(std::memory_order_relaxed) & 3;           // 0 automatic, 1 never staged, 2 always
+    const int word = g_quant_tuning.load(std::memory_order_relaxed);
+    const int mode = word & 3;                                                     // 0 automatic, 1 never staged, 2 always
     const bool staged = kDoCol && (mode == 2 || (mode == 0 && rows >= (kDoRow ? kStagedFromRowsBoth : kStagedFromRowsCol)));
+    constexpr bool kFused = kDoRow && kDoCol;
+    const bool split = kFused && ((word >> 2) & 1) == 0;                           // bit 2: both passes by one group of 256 threads
+    if (kFused && split) {
+        if (staged)
+            return launch_tile_kernel_impl<kDoRow, kDoCol, kColSum, true, kFused>(x, cr, sr, ct, sc, rows, cols, tiles_c, tiles, rule,
+                                                                                  layout, di, st, colsum_partial);
+        return launch_tile_kernel_impl<kDoRow, kDoCol, kColSum, false, kFused>(x, cr, sr, ct, sc, rows, cols, tiles_c, tiles, rule,
+                                                                               layout, di, st, colsum_partial);
+    }
     if (staged)
         return launch_tile_kernel_impl<kDoRow, kDoCol, kColSum, true>(x, cr, sr, ct, sc, rows, cols, tiles_c, tiles, rule, layout, di,
                                                                       st, colsum_partial);
@@ -709,7 +739,7 @@ mx_colsum_reduce_kernel(const float* __restrict__ partial, int64_t tiles_r, int6
 }
 
 extern "C" DW_API int dw_mxfp8_quantize_set_tuning(int word) {
-    if (word < 0 || (word & 3) == 3 || (word >> 2) != 0) return DW_ERR_BAD_ARG;
+    if (word < 0 || (word & 3) == 3 || (word >> 3) != 0) return DW_ERR_BAD_ARG;
     g_quant_tuning.store(word, std::memory_order_relaxed);
     return DW_OK;
 }
