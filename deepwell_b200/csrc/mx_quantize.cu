@@ -137,9 +137,6 @@ __global__ void mx_sf_pad_kernel(uint8_t* __restrict__ scales, int64_t rows, int
 // or the four blocks of two consecutive rows, land in 8 different 16-byte bank groups.
 __device__ __forceinline__ uint32_t tile_chunk(uint32_t c, uint32_t r) { return c ^ (r & 7u) ^ ((c >> 3) << 1); }
 
-// transposed rows this far apart and more: staged write-out (measured: column-wise alone gains from 1 MiB on, the
-// fused form, which pays two more barriers per tile, from 2 MiB on)
-constexpr int64_t kStagedFromRowsCol = 1ll << 20, kStagedFromRowsBoth = 1ll << 21;
 constexpr int kTileSmemBytes = 2 * 128 * 16 * 16 + 1024 + 2048;   // two 32 KB tiles + two 512-byte scale staging areas + column sums
 
 // kColSum: also leave the fp32 sum of every column over this tile's 128 rows in colsum_partial[tile row][column]
@@ -571,17 +568,21 @@ static int launch_tile_kernel_impl(const uint16_t* x, uint8_t* cr, uint8_t* sr, 
     return launch_status();
 }
 
-// Staged write-out of the transposed payload where its row stride would cost an address translation per lane
-// (see mx_quant_tile_kernel); the codes need 16-byte alignment of every output row for it (rows % 16 == 0 holds: rows % 32 == 0).
+// The transposed payload is written out staged (see mx_quant_tile_kernel) unless the tuning word asks for the direct form:
+// measured over several B200s of this pool the staged form is 4-8 % faster on most of them and up to 5 % slower on some
+// for rows <= 2^19, and 1.2-1.6x faster from 2^20 rows on everywhere.  The codes need 16-byte alignment of every output row
+// (rows % 32 == 0 holds on this path).
 template <bool kDoRow, bool kDoCol, bool kColSum = false>
 static int launch_tile_kernel(const uint16_t* x, uint8_t* cr, uint8_t* sr, uint8_t* ct, uint8_t* sc, int64_t rows, int64_t cols,
                               uint32_t tiles_c, uint32_t tiles, int rule, int layout, const DeviceInfo& di, cudaStream_t st,
                               float* colsum_partial = nullptr) {
     const int word = g_quant_tuning.load(std::memory_order_relaxed);
-    const int mode = word & 3;                                                     // 0 automatic, 1 never staged, 2 always
-    const bool staged = kDoCol && (mode == 2 || (mode == 0 && rows >= (kDoRow ? kStagedFromRowsBoth : kStagedFromRowsCol)));
+    const int mode = word & 3;                                                     // 0 automatic (staged), 1 direct, 2 staged
+    const bool staged = kDoCol && mode != 1;
     constexpr bool kFused = kDoRow && kDoCol;
-    const bool split = kFused && ((word >> 2) & 1) == 0;                           // bit 2: both passes by one group of 256 threads
+    // two groups of threads side by side once a CTA has several tiles to work through (measured: 16384 x 4096 and larger
+    // gain 3-5 %, 16384 x 1024 loses 10 %); bit 2 of the tuning word: always one group
+    const bool split = kFused && ((word >> 2) & 1) == 0 && (tiles >= 2048u || ((word >> 3) & 1) != 0);   // bit 3: always two groups
     if (kFused && split) {
         if (staged)
             return launch_tile_kernel_impl<kDoRow, kDoCol, kColSum, true, kFused>(x, cr, sr, ct, sc, rows, cols, tiles_c, tiles, rule,
@@ -739,7 +740,7 @@ mx_colsum_reduce_kernel(const float* __restrict__ partial, int64_t tiles_r, int6
 }
 
 extern "C" DW_API int dw_mxfp8_quantize_set_tuning(int word) {
-    if (word < 0 || (word & 3) == 3 || (word >> 3) != 0) return DW_ERR_BAD_ARG;
+    if (word < 0 || (word & 3) == 3 || (word >> 4) != 0 || (word & 12) == 12) return DW_ERR_BAD_ARG;
     g_quant_tuning.store(word, std::memory_order_relaxed);
     return DW_OK;
 }

@@ -86,10 +86,13 @@ int dw_mxfp8_quantize(const void *x_bf16, void *codes, void *scales, int64_t row
 int dw_mxfp8_quantize_ex(const void *x_bf16, void *codes, void *scales, int64_t rows, int64_t cols,
                          int direction, int scale_rule, int scale_layout, int flags, void *stream);
 
-/* Tuning switch of the column-wise (transposed-payload) kernel, process-wide: bits [0,2) = 0 automatic (the transposed
- * payload is written through a shared-memory staging buffer, whole 128-byte row segments per store, when its rows are
- * 1 MiB apart or more (2 MiB for the fused both-forms call), i.e. rows >= 2^20 (2^21); straight from registers otherwise), 1 never staged, 2 always staged; bit 2 set: the fused both-forms kernel runs its row
- * and column pass one after the other in 256 threads instead of side by side in two groups of 256.  Same bytes either way.  For measurements; the reference has no column-wise kernel (csrc/mxfp8_quantization.cu:216-226 is empty). */
+/* Tuning switch of the column-wise (transposed-payload) kernel, process-wide.  Bits [0,2): 0 or 2 = the transposed payload is
+ * written through a shared-memory staging buffer, whole 128-byte row segments per store (the default); 1 = straight from
+ * registers, 32 bytes per thread and output row (as fast or slightly faster on some GPUs while the output rows are less than
+ * 1 MiB apart, half the rate beyond).  Bit 2 set: the fused both-forms kernel always runs its row and column pass one after
+ * the other in 256 threads instead of side by side in two groups of 256 on large inputs; bit 3 set: always side by side.
+ * Same bytes in every setting.  For
+ * measurements; the reference has no column-wise kernel (csrc/mxfp8_quantization.cu:216-226 is empty). */
 int dw_mxfp8_quantize_set_tuning(int word);
 
 /* One read of x, both operand forms: row-wise (codes_row [rows, cols]) and column-wise

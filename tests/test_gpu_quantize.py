@@ -77,12 +77,11 @@ def test_shapes_fast_and_ragged(nv, shape, rule):
 
 
 @pytest.mark.parametrize("shape", [(128, 128), (256, 512), (96, 160), (32, 96), (2048, 1024), (4096, 128), (160, 96)])
-@pytest.mark.parametrize("one_group", [0, 4])
+@pytest.mark.parametrize("one_group", [4, 8])
 def test_staged_transposed_write_out_gives_the_same_bytes(nv, shape, one_group):
-    """The column-wise kernel's staged write-out (used on its own when the transposed payload's rows are 1 MiB apart
-    or more) forced on for small shapes, whole and ragged tiles, with the fused kernel's two passes run by two groups
-    of threads side by side (default) and by one group one after the other (tuning bit 2): every form still equals the
-    C restatement."""
+    """The column-wise kernel's staged write-out (the default) and the direct one (tuning word 1), whole and ragged
+    tiles, with the fused kernel's two passes run by one group of threads one after the other (tuning bit 2) and by two
+    groups side by side (bit 3; what large inputs get): every form still equals the C restatement."""
     g = torch.Generator("cpu").manual_seed(shape[0] * 31 + shape[1])
     x = torch.randn(shape, generator=g)
     x[torch.rand(shape, generator=g) < 0.01] *= 50
@@ -93,13 +92,14 @@ def test_staged_transposed_write_out_gives_the_same_bytes(nv, shape, one_group):
         check_all_forms(nv, x, 0)
         if shape[0] % 32 == 0 and shape[1] % 32 == 0:
             a = nv.quantize_both_colsum(x, 0, nv.SF_TILED)
-            assert L.dw_mxfp8_quantize_set_tuning(1 | one_group) == 0
+            assert L.dw_mxfp8_quantize_set_tuning(1 | one_group) == 0          # the direct write-out
+            check_all_forms(nv, x, 0)
             b = nv.quantize_both_colsum(x, 0, nv.SF_TILED)
             for u, v in zip(a, b):
                 assert torch.equal(u.view(torch.uint8) if u.element_size() == 1 else u, v.view(torch.uint8) if v.element_size() == 1 else v)
     finally:
         assert L.dw_mxfp8_quantize_set_tuning(0) == 0
-    assert L.dw_mxfp8_quantize_set_tuning(3) == -1 and L.dw_mxfp8_quantize_set_tuning(8) == -1
+    assert L.dw_mxfp8_quantize_set_tuning(3) == -1 and L.dw_mxfp8_quantize_set_tuning(16) == -1 and L.dw_mxfp8_quantize_set_tuning(12) == -1
     assert L.dw_mxfp8_quantize_set_tuning(4) == 0 and L.dw_mxfp8_quantize_set_tuning(0) == 0
 
 
