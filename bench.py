@@ -897,6 +897,8 @@ def main():
                     help="tuning aid: on one GPU, run the shard sizes rank 0 would get in a job of this many GPUs")
     ap.add_argument("--serial", action="store_true", help="quantise and GEMM on one stream, every launch after the previous one has finished")
     ap.add_argument("--two-streams", action="store_true", help="the next layer's quantisers on a second, lower-priority stream")
+    ap.add_argument("--no-exchange", action="store_true",
+                    help="N > 1: every rank quantises the whole of every X itself (no sharing of the quantisation over NVLink)")
     ap.add_argument("--profile-case", default=None, choices=["gemm", "quant_row", "quant_both", "quant_col", "quant_col_long"],
                     help="run a few launches of one kernel on a small case (for an ncu capture) and exit")
     ap.add_argument("--workload", default="linears", choices=["linears", "decoder_step"],
@@ -1012,7 +1014,63 @@ def main():
                 after_gemm(l)
         return 3 * len(layers)
 
+    # ---- N > 1: the ranks share the quantisation of the replicated activations (deepwell_b200/exchange.py) ----
+    # Chosen per layer, largest activation first, while the copies of one step (what a rank receives, at ~700 GB/s) fit
+    # under 80 % of the step's GEMM time; the other activations are quantised whole on every rank as at N = 1.
+    exchange, ex_index, exchange_info = None, {}, None
+    if world > 1 and overlap and not args.no_exchange and not args.emulate_world:
+        gemm_s = total_flops() / world / 2.6e15
+        budget, used = 0.8 * gemm_s, 0.0
+        for i in sorted(range(len(layers)), key=lambda j: -layers[j]["k"]):
+            t = M_TOKENS * layers[i]["k"] * (1 + 1 / 32) * (world - 1) / world / 700e9
+            if M_TOKENS % (128 * world) == 0 and used + t <= budget:
+                ex_index[i] = len(ex_index)
+                used += t
+        if ex_index:
+            try:
+                from deepwell_b200.exchange import QuantizedRowExchange
+                order = sorted(ex_index, key=lambda j: ex_index[j])
+                exchange = QuantizedRowExchange([(M_TOKENS, layers[i]["k"]) for i in order], device=dev)
+                exchange_info = {"layers": [layers[i]["name"] for i in order], "how": exchange.how,
+                                 "bytes_pushed_per_rank_per_step": int(exchange.bytes_pushed_per_call)}
+            except Exception as e:          # no peer mapping on this box: every rank quantises everything itself
+                exchange, ex_index = None, {}
+                exchange_info = {"error": f"{type(e).__name__}: {str(e)[:300]}"}
+    step_no = [0]
+
+    def exchange_step(record: bool, after_gemm=None):
+        """The step with shared quantisation: this rank's row slices of the exchanged activations for the NEXT step are
+        quantised first and travel to the peers while this step's GEMMs run; the other activations and the weight shards
+        are quantised here; a 4-byte all-reduce at the end makes the next step's operands complete on every rank."""
+        now, nxt = step_no[0] % 2, (step_no[0] + 1) % 2
+        order = sorted(ex_index, key=lambda j: ex_index[j])
+        exchange.quantise_and_push([layers[i]["x"] for i in order], nxt)
+        n_launch = len(order)
+        for i, l in enumerate(layers):
+            if i in ex_index:
+                a_codes, a_sf = exchange.operand(now, ex_index[i])
+                a_ptr, s_ptr = a_codes.data_ptr(), a_sf.data_ptr()
+            else:
+                nv.check(L.dw_mxfp8_quantize(l["x"].data_ptr(), l["xc"].data_ptr(), l["xs"].data_ptr(), M_TOKENS, l["k"],
+                                             nv.DIR_ROW, nv.RULE_OCP_FLOOR, nv.SF_TILED, st), "quantize X")
+                a_ptr, s_ptr = l["xc"].data_ptr(), l["xs"].data_ptr()
+                n_launch += 1
+            nv.check(L.dw_mxfp8_quantize(l["w"].data_ptr(), l["wc"].data_ptr(), l["ws"].data_ptr(), l["n"], l["k"],
+                                         nv.DIR_ROW, nv.RULE_OCP_FLOOR, nv.SF_TILED, st), "quantize W")
+            if after_gemm is not None and "gather_done" in l:
+                stream.wait_event(l["gather_done"])
+            nv.check(L.dw_mxfp8_gemm(a_ptr, s_ptr, l["wc"].data_ptr(), l["ws"].data_ptr(), l["y"].data_ptr(), None,
+                                     M_TOKENS, l["n"], l["k"], 1.0, 0.0, None, 0, status.data_ptr(), st), "gemm")
+            n_launch += 2
+            if after_gemm is not None:
+                after_gemm(l)
+        exchange.fence(nxt)
+        step_no[0] += 1
+        return n_launch
+
     def step(record: bool, after_gemm=None, force_separate=False):
+        if exchange is not None and not force_separate:
+            return exchange_step(record, after_gemm)
         if overlap and not force_separate:
             return overlapped_step(record, after_gemm)
         launches = 0
@@ -1073,6 +1131,9 @@ def main():
 
     if overlap:
         quantise_operands(layers[0], 0)               # the pipeline's first operands; later ones follow a GEMM
+    if exchange is not None:                          # the first step's operands: slot 0
+        exchange.quantise_and_push([layers[i]["x"] for i in sorted(ex_index, key=lambda j: ex_index[j])], 0)
+        exchange.fence(0)
     for _ in range(warmup):
         step(False)
     nv.check_status(dev)
@@ -1084,6 +1145,18 @@ def main():
     nv.check_status(dev)
     ms_per_step = elapsed_ms / args.steps
     value = total_flops() / (ms_per_step * 1e-3) / 1e12
+    if exchange is not None:
+        # the operands the exchange assembled (this rank's slice + the peers') against this rank's own quantisation of the whole X
+        same = True
+        for i, j in ex_index.items():
+            l = layers[i]
+            nv.check(L.dw_mxfp8_quantize(l["x"].data_ptr(), l["xc"].data_ptr(), l["xs"].data_ptr(), M_TOKENS, l["k"],
+                                         nv.DIR_ROW, nv.RULE_OCP_FLOOR, nv.SF_TILED, st), "quantize X")
+            codes, scales = exchange.operand(step_no[0] % 2, j)
+            same = same and bool(torch.equal(codes, l["xc"])) and bool(torch.equal(scales, l["xs"]))
+        flag = torch.tensor([1 if same else 0], device=dev, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        exchange_info["parity"] = "ok" if int(flag.item()) == 1 else "MISMATCH"
 
     # ---- roofline of the dominant kernel (GEMM), live CUDA-event durations of this rank ----
     if overlap:
@@ -1320,7 +1393,10 @@ def main():
                 "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "mxfp8(e4m3+e8m0), fp32 accumulate, bf16 out", "data": "synthetic",
                 "config": {"workload": WORKLOAD, "M": M_TOKENS, "layers": {n: [k, nn] for n, k, nn in LAYERS},
-                           "parallelism": f"N-sharded x{world}, X replicated, no data-path collective",
+                           "parallelism": f"N-sharded x{world}, X replicated, no data-path collective" if exchange is None else
+                                          f"N-sharded x{world}, X replicated; the quantisation of X for {exchange_info['layers']} is shared: "
+                                          "each rank quantises 1/N of the rows and copies its slice into every peer's operand buffer over "
+                                          "NVLink (copy engines, under the GEMMs); one 4-byte all-reduce per step as fence",
                            "step": "per layer: quantise X, quantise W shard, block-scaled GEMM"
                                    + ("; each GEMM is issued before the next layer's quantisers, which may start while it "
                                       "runs (DW_QUANT_OVERLAP_PREVIOUS)" if overlap else
@@ -1331,7 +1407,8 @@ def main():
                                "note": "TUNING RUN: one rank's shard on one GPU; value is not a job throughput"}
                               if args.emulate_world else {})},
                 "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "roofline": roofline, "sustained": sustained,
-                "roofline_quantize": roofline_q, "with_gather": with_gather, **extra, "cpu_baseline": cpu_baseline}
+                "roofline_quantize": roofline_q, "with_gather": with_gather, "exchange": exchange_info, **extra,
+                "cpu_baseline": cpu_baseline}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
