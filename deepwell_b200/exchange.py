@@ -6,7 +6,7 @@ has no distributed code at all: src/deepwell/__init__.py:45-83 is a placeholder)
 1/world slice of the rows (whole 128-row scale tiles, so a slice is one contiguous piece of the payload and one of the
 tiled scale buffer) and writes that slice into every peer's operand buffer over NVLink with plain device-to-device copies.
 Those copies are executed by the copy engines, which, unlike any kernel, run while a GEMM's thread blocks hold every SM
-(measured: a 256 MB peer copy issued behind the start of a 1.3 ms GEMM is done after 0.39 ms, the GEMM lasts 1.6 % longer), so
+(measured between two ranks: a 256 MB copy into a peer's buffer issued behind the start of a 1.33 ms GEMM is done after 0.39 ms), so
 the exchange for the next step hides under this step's GEMMs.
 
     ex = QuantizedRowExchange([(M, K0), (M, K1), ...], group)      # once; allocates and maps the operand buffers
@@ -14,8 +14,8 @@ the exchange for the next step hides under this step's GEMMs.
               ... GEMMs of step s on ex.operand(slot=s % 2, i) ...
               ex.fence((s + 1) % 2)                                # all slices of the next slot have landed everywhere
 
-The operand buffers live in memory every rank of the node can address (CUDA IPC handles of ordinary allocations, or torch
-symmetric memory where those are not available).  The fence is one 4-byte all-reduce per step: when it completes on a
+The operand buffers live in memory every rank of the node can address (torch symmetric memory; CUDA IPC handles of ordinary
+allocations as a slow last resort).  The fence is one 4-byte all-reduce per step: when it completes on a
 rank, every rank has passed the point behind its own pushes and behind its GEMMs of the step, so the next slot is complete
 everywhere and the slot just used may be overwritten.
 """
@@ -34,8 +34,19 @@ def _map_on_all_ranks(nbytes: int, device: torch.device, group) -> Tuple[List[to
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     errors = []
     try:
-        # CUDA IPC handles of an ordinary allocation: the peers' views are tensors on the peers' devices, and copies into
-        # them are peer-to-peer copies, which the copy engines execute
+        # symmetric memory: every rank's buffer is mapped into this process's address space on ITS OWN device; a copy into a
+        # peer's view is a device-to-device copy that the copy engines carry over NVLink (measured on B200: 256 MB in
+        # 0.36 ms = 750 GB/s, 16 us of host time, and it runs while a GEMM holds the SMs)
+        import torch.distributed._symmetric_memory as symm_mem
+        local = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+        handle = symm_mem.rendezvous(local, group=group if group is not None else dist.group.WORLD)
+        views = [local if r == rank else handle.get_buffer(r, (nbytes,), torch.uint8) for r in range(world)]
+        return views, "symmetric memory"
+    except Exception as e:                      # no symmetric-memory support in this build / on this box
+        errors.append(f"symmetric memory: {type(e).__name__}: {str(e)[:160]}")
+    try:
+        # CUDA IPC handles of an ordinary allocation: works everywhere, but the peers' views are tensors on the peers'
+        # devices and the copies into them were staged through host memory on the box measured (25 GB/s): a last resort
         from torch.multiprocessing.reductions import reduce_tensor
         local = torch.empty(nbytes, dtype=torch.uint8, device=device)
         torch.cuda.synchronize(device)
@@ -45,14 +56,6 @@ def _map_on_all_ranks(nbytes: int, device: torch.device, group) -> Tuple[List[to
         return views, "CUDA IPC handles"
     except Exception as e:
         errors.append(f"CUDA IPC: {type(e).__name__}: {str(e)[:160]}")
-    try:
-        import torch.distributed._symmetric_memory as symm_mem
-        local = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
-        handle = symm_mem.rendezvous(local, group=group if group is not None else dist.group.WORLD)
-        views = [local if r == rank else handle.get_buffer(r, (nbytes,), torch.uint8) for r in range(world)]
-        return views, "symmetric memory"
-    except Exception as e:                      # no symmetric-memory support in this build / on this box
-        errors.append(f"symmetric memory: {type(e).__name__}: {str(e)[:160]}")
     raise RuntimeError("no way to map peer memory: " + "; ".join(errors))
 
 
