@@ -759,8 +759,10 @@ def sharded_leg(dev, rank, world):
     """ColumnParallelDWLinear (QKV 4096 -> 6144, gather_output) and RowParallelDWLinear (down 14336 -> 4096, all-reduce and
     reduce-scatter) forward + backward on `world` GPUs under NCCL against the unsharded DWLinear computed on every rank
     from the same seeded tensors.  Y of the column-parallel layer must be bit-equal (same kernel, same order over K);
-    gradients and the row-parallel output are sums of per-rank bf16 partials and are held to the GEMM tolerance
-    |got - ref| <= 1e-2 * max(|ref|, mean|ref|) on 99.9 % of the elements and 4e-2 everywhere.  Also times the
+    gradients and the row-parallel output are sums of `world` bf16 partials that the collective adds in bf16, so their
+    tolerance grows with the number of roundings: |got - ref| <= 1e-2 * sqrt(world / 2) * max(|ref|, mean|ref|) on 99.9 % of
+    the elements and 4e-2 * sqrt(world / 2) everywhere (a model of exactly those roundings on normal data puts the 99.9 %
+    quantile at 0.008 / 0.011 / 0.015 and the worst of 4 M elements at 0.017 / 0.029 / 0.034 for 2 / 4 / 8 ranks).  Also times the
     column-parallel forward with and without the gather, and the row-parallel forward with its reduction."""
     import torch.distributed as dist
     import deepwell_b200 as dw
@@ -773,10 +775,11 @@ def sharded_leg(dev, rank, world):
         got, ref = got.float(), ref.float()
         floor = ref.abs().mean()
         err = (got - ref).abs() / torch.maximum(ref.abs(), floor)
-        frac_ok = float((err <= 1e-2).float().mean())
+        widen = max(1.0, world / 2.0) ** 0.5
+        frac_ok = float((err <= 1e-2 * widen).float().mean())
         worst = float(err.max())
         res[what + "_max_rel_err"] = worst
-        return frac_ok >= 0.999 and worst <= 4e-2 and not bool(torch.isnan(got).any())
+        return frac_ok >= 0.999 and worst <= 4e-2 * widen and not bool(torch.isnan(got).any())
 
     def timed(fn, reps=10):
         for _ in range(3):
@@ -897,6 +900,8 @@ def main():
                     help="tuning aid: on one GPU, run the shard sizes rank 0 would get in a job of this many GPUs")
     ap.add_argument("--serial", action="store_true", help="quantise and GEMM on one stream, every launch after the previous one has finished")
     ap.add_argument("--two-streams", action="store_true", help="the next layer's quantisers on a second, lower-priority stream")
+    ap.add_argument("--exchange-push", choices=["graph", "stream"], default="graph",
+                    help="N > 1: the peer copies of the shared quantisation as one replayed CUDA graph per step (default) or issued one by one")
     ap.add_argument("--no-exchange", action="store_true",
                     help="N > 1: every rank quantises the whole of every X itself (no sharing of the quantisation over NVLink)")
     ap.add_argument("--profile-case", default=None, choices=["gemm", "quant_row", "quant_both", "quant_col", "quant_col_long"],
@@ -1030,8 +1035,9 @@ def main():
             try:
                 from deepwell_b200.exchange import QuantizedRowExchange
                 order = sorted(ex_index, key=lambda j: ex_index[j])
-                exchange = QuantizedRowExchange([(M_TOKENS, layers[i]["k"]) for i in order], device=dev)
-                exchange_info = {"layers": [layers[i]["name"] for i in order], "how": exchange.how,
+                exchange = QuantizedRowExchange([(M_TOKENS, layers[i]["k"]) for i in order], device=dev,
+                                                push=args.exchange_push)
+                exchange_info = {"layers": [layers[i]["name"] for i in order], "how": exchange.how, "push": exchange.push,
                                  "bytes_pushed_per_rank_per_step": int(exchange.bytes_pushed_per_call)}
             except Exception as e:          # no peer mapping on this box: every rank quantises everything itself
                 exchange, ex_index = None, {}

@@ -64,7 +64,7 @@ class QuantizedRowExchange:
     rows [rank * rows / world, (rank + 1) * rows / world) and copying them into every peer's buffer."""
 
     def __init__(self, shapes: Sequence[Tuple[int, int]], group=None, device: Optional[torch.device] = None, slots: int = 2,
-                 scale_rule: int = nv.RULE_OCP_FLOOR):
+                 scale_rule: int = nv.RULE_OCP_FLOOR, push: str = "graph"):
         if not dist.is_initialized():
             raise RuntimeError("torch.distributed is not initialised")
         self.group = group
@@ -89,6 +89,13 @@ class QuantizedRowExchange:
         self._pushed = [torch.cuda.Event() for _ in range(slots)]
         self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.bytes_pushed_per_call = sum((cb + sb) // self.world for _, cb, _, sb in self._offsets) * (self.world - 1)
+        # The copies of one slot always run between the same addresses: 2 x activations x (world - 1) of them.  Issued one
+        # by one they cost the host about 16 us each, more than a step's GEMMs last on 8 GPUs, so each slot's copies are
+        # recorded once as a CUDA graph of memcpy nodes and replayed with a single launch.
+        if push not in ("graph", "stream"):
+            raise ValueError("push must be 'graph' or 'stream'")
+        self.push = push
+        self._graphs = [self._capture_copies(slot) for slot in range(slots)] if push == "graph" and self.world > 1 else None
 
     def _region(self, view: torch.Tensor, slot: int, i: int):
         c_off, c_bytes, s_off, s_bytes = self._offsets[i]
@@ -100,33 +107,50 @@ class QuantizedRowExchange:
         codes, scales = self._region(self.views[self.rank], slot, i)
         return codes.view(self.shapes[i]), scales
 
+    def _slice(self, i: int) -> Tuple[int, int, int, int]:
+        """Byte ranges [c_lo, c_hi) of the payload and [s_lo, s_hi) of the tiled scales that hold this rank's rows of activation i."""
+        rows, cols = self.shapes[i]
+        r0, r1 = self.rank * rows // self.world, (self.rank + 1) * rows // self.world
+        sf_per_row_tile = self._offsets[i][3] // (rows // 128)
+        return r0 * cols, r1 * cols, (r0 // 128) * sf_per_row_tile, (r1 // 128) * sf_per_row_tile
+
+    def _issue_copies(self, slot: int) -> None:
+        for step in range(1, self.world):                         # every rank starts with a different peer
+            peer = (self.rank + step) % self.world
+            for i in range(len(self.shapes)):
+                c_lo, c_hi, s_lo, s_hi = self._slice(i)
+                src_c, src_s = self._region(self.views[self.rank], slot, i)
+                dst_c, dst_s = self._region(self.views[peer], slot, i)
+                dst_c[c_lo:c_hi].copy_(src_c[c_lo:c_hi], non_blocking=True)
+                dst_s[s_lo:s_hi].copy_(src_s[s_lo:s_hi], non_blocking=True)
+
+    def _capture_copies(self, slot: int) -> "torch.cuda.CUDAGraph":
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=self.copy_stream, capture_error_mode="thread_local"):
+            self._issue_copies(slot)
+        return graph
+
     def quantise_and_push(self, xs: Sequence[torch.Tensor], slot: int) -> None:
         """Quantises this rank's row slice of every activation into `slot` (current stream) and copies the slices into
         every peer's buffer (copy stream: copy engines over NVLink, asynchronous to the current stream)."""
         if len(xs) != len(self.shapes):
             raise ValueError("one tensor per registered activation")
-        pieces = []
         for i, x in enumerate(xs):
             rows, cols = self.shapes[i]
             if tuple(x.shape) != (rows, cols) or x.dtype != torch.bfloat16 or not x.is_contiguous():
                 raise ValueError(f"activation {i} must be a contiguous bfloat16 [{rows}, {cols}] tensor")
             r0, r1 = self.rank * rows // self.world, (self.rank + 1) * rows // self.world
             codes, scales = self._region(self.views[self.rank], slot, i)
-            sf_per_row_tile = scales.numel() // (rows // 128)
-            c_lo, c_hi = r0 * cols, r1 * cols
-            s_lo, s_hi = (r0 // 128) * sf_per_row_tile, (r1 // 128) * sf_per_row_tile
+            c_lo, c_hi, s_lo, s_hi = self._slice(i)
             nv.quantize_into(x[r0:r1], codes[c_lo:c_hi], scales[s_lo:s_hi], nv.DIR_ROW, self.rule, nv.SF_TILED)
-            pieces.append((i, c_lo, c_hi, s_lo, s_hi))
         self._quantised[slot].record()
         self.copy_stream.wait_event(self._quantised[slot])
         with torch.cuda.stream(self.copy_stream):
-            for step in range(1, self.world):                     # every rank starts with a different peer
-                peer = (self.rank + step) % self.world
-                for i, c_lo, c_hi, s_lo, s_hi in pieces:
-                    src_c, src_s = self._region(self.views[self.rank], slot, i)
-                    dst_c, dst_s = self._region(self.views[peer], slot, i)
-                    dst_c[c_lo:c_hi].copy_(src_c[c_lo:c_hi], non_blocking=True)
-                    dst_s[s_lo:s_hi].copy_(src_s[s_lo:s_hi], non_blocking=True)
+            if self._graphs is not None:
+                self._graphs[slot].replay()
+            else:
+                self._issue_copies(slot)
             self._pushed[slot].record()
 
     def fence(self, slot: int) -> None:
