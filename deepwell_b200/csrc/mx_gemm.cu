@@ -90,6 +90,7 @@ struct GemmCfg {
     static constexpr int kStages = (kFit >= 8 ? 8 : kFit) / (kGroup % 2 ? 2 * kGroup : kGroup) * (kGroup % 2 ? 2 * kGroup : kGroup);
     // stages are handed back to the producer `kGroup` at a time: one tcgen05.commit per group
     static constexpr int kGroups = kStages / kGroup;
+    static_assert(kGroup == 1, "a unit may start in the middle of the ring: stages are handed back one at a time");
     static_assert(kStages % 2 == 0 && kStages % kGroup == 0 && kGroups >= 2, "ring shape");
     // Tensor memory (512 columns): two accumulators and two sets of scale columns.  With BN = 256 the
     // two accumulators cannot both be 256 columns wide next to the scales, so they OVERLAP by 32
@@ -206,13 +207,15 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     };
 
     // Both pipeline roles walk the stage ring with compile-time stage indices (the k loop is unrolled
-    // by the ring depth and every tile starts again at stage 0), so addresses and descriptors are
-    // constants plus one base register and the single issuing thread does almost no arithmetic.
+    // by the ring depth; a tile that starts in the middle of the ring skips the first stages of its
+    // first pass), so addresses and descriptors are constants plus one base register and the single
+    // issuing thread does almost no arithmetic.
     // Each stage's barrier parity is one bit of a mask, flipped on every use of that stage.
     if (warp == 0) {
         // ================= TMA producer (whole warp walks the ring, one elected lane issues) =================
         {
             uint32_t empty_parity = 0;   // bit g: parity of the next wait on empty_bar(g), inverted
+            int ring_at = 0;             // stage of the next k-block
             const uint32_t full0 = (kCtas == 2) ? ptx::map_to_cta(full_bar(0), 0) : full_bar(0);   // leader's barrier
             const int nkb = static_cast<int>(p.num_kblocks);
             for (uint32_t unit = worker; unit < num_units && !err; unit += num_workers) {
@@ -228,11 +231,15 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 const int sfb_row = static_cast<int>(b_first / 128u) * nkb;       // first scale tile the column tile touches
                 const int kb_first = static_cast<int>(split * p.kb_per_split);
                 const int kb_end = min(nkb, kb_first + static_cast<int>(p.kb_per_split));
-                for (int kb0 = kb_first; kb0 < kb_end && !err; kb0 += kStages) {
+                // The ring runs on across tiles: this unit's first k-block takes the stage after the previous unit's last
+                // one (`ring_at`), so the loads of a new tile start as soon as ANY stage is free, not when stage 0 is.  The
+                // stage index stays a compile-time constant: the first pass through the unrolled body skips the stages
+                // before `ring_at`.
+                for (int kb0 = kb_first - ring_at; kb0 < kb_end && !err; kb0 += kStages) {
 #pragma unroll
                     for (int s = 0; s < kStages; ++s) {
                         const int kb = kb0 + s;
-                        if (kb < kb_end && !err) {
+                        if (kb >= kb_first && kb < kb_end && !err) {
                             if (s % kGroup == 0) {        // first stage of a group: wait until the group is free
                                 const int g = s / kGroup;
                                 if (!timed_wait(empty_bar(g), ((empty_parity >> g) & 1u) ^ 1u, 0)) { err = kErrProducer; continue; }
@@ -259,12 +266,14 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         }
                     }
                 }
+                ring_at = (ring_at + (kb_end - kb_first)) % kStages;
             }
         }
     } else if (warp == 1) {
         // ================= MMA issuer (leader CTA only; whole warp walks, one elected lane issues) =================
         if (leader) {
             uint32_t full_parity = 0, acc = 0, acc_phase = 0, tiles_done = 0;
+            int ring_at = 0;             // stage of the next k-block (the producer counts the same way)
             constexpr uint32_t idesc = ptx::idesc_mxf8(128 * kCtas, BN);
             constexpr uint32_t kStageStep = Cfg::kStageBytes >> 4;          // descriptor units of 16 bytes
             const uint32_t a_lo0 = ptx::desc_lo_sw128(stage_a(0)), b_lo0 = ptx::desc_lo_sw128(stage_b(0));
@@ -291,10 +300,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 ptx::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * Cfg::kAccStride;
                 uint32_t accumulate = 0;
-                for (int kb0 = kb_first; kb0 < kb_end && !err; kb0 += kStages) {
+                for (int kb0 = kb_first - ring_at; kb0 < kb_end && !err; kb0 += kStages) {
 #pragma unroll
                     for (int s = 0; s < kStages; ++s) {
-                        if (kb0 + s < kb_end && !err) {
+                        if (kb0 + s >= kb_first && kb0 + s < kb_end && !err) {
                             if (!timed_wait(full_bar(s), (full_parity >> s) & 1u, 2)) { err = kErrMmaFull; continue; }
                             full_parity ^= 1u << s;
                             ptx::tc_fence_after();
@@ -325,6 +334,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     }
                 }
                 if (err) break;
+                ring_at = (ring_at + (kb_end - kb_first)) % kStages;
                 if (ptx::elect_one()) {
                     if (kCtas == 2) ptx::tc_commit_both(accf_bar(acc)); else ptx::tc_commit(accf_bar(acc));
                 }
