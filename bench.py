@@ -902,6 +902,10 @@ def main():
     ap.add_argument("--two-streams", action="store_true", help="the next layer's quantisers on a second, lower-priority stream")
     ap.add_argument("--exchange-push", choices=["graph", "stream"], default="graph",
                     help="N > 1: the peer copies of the shared quantisation as one replayed CUDA graph per step (default) or issued one by one")
+    ap.add_argument("--exchange-budget", default="0.8,1.1,1.4,all",
+                    help="N > 1: share as many rows of X as a rank can receive (at 700 GB/s) in this multiple of the step's GEMM "
+                         "time ('all' = every row); several values, comma-separated: each is tried for a few steps before the "
+                         "timed region and the fastest kept")
     ap.add_argument("--no-exchange", action="store_true",
                     help="N > 1: every rank quantises the whole of every X itself (no sharing of the quantisation over NVLink)")
     ap.add_argument("--profile-case", default=None, choices=["gemm", "quant_row", "quant_both", "quant_col", "quant_col_long"],
@@ -1020,28 +1024,38 @@ def main():
         return 3 * len(layers)
 
     # ---- N > 1: the ranks share the quantisation of the replicated activations (deepwell_b200/exchange.py) ----
-    # Chosen per layer, largest activation first, while the copies of one step (what a rank receives, at ~700 GB/s) fit
-    # under 80 % of the step's GEMM time; the other activations are quantised whole on every rank as at N = 1.
-    exchange, ex_index, exchange_info = None, {}, None
-    if world > 1 and overlap and not args.no_exchange and not args.emulate_world:
+    # How much is shared is a budget: the rows a rank can receive per step (at ~700 GB/s) within a multiple of the step's
+    # GEMM time, largest activation first, the last one partly; the remaining rows every rank quantises itself.  With the
+    # copies longer than the step the fence would wait for them, with too few rows shared the ranks repeat HBM-bound work:
+    # the multiple is measured (a few steps per candidate before the timed region) unless --exchange-budget fixes it.
+    exchange, ex_index, exchange_info, ex_plans = None, {}, None, []
+    if world > 1 and overlap and not args.no_exchange and not args.emulate_world and M_TOKENS % (128 * world) == 0:
+        order = sorted(range(len(layers)), key=lambda j: -layers[j]["k"])
+        ex_index = {i: n for n, i in enumerate(order)}
         gemm_s = total_flops() / world / 2.6e15
-        budget, used = 0.8 * gemm_s, 0.0
-        for i in sorted(range(len(layers)), key=lambda j: -layers[j]["k"]):
-            t = M_TOKENS * layers[i]["k"] * (1 + 1 / 32) * (world - 1) / world / 700e9
-            if M_TOKENS % (128 * world) == 0 and used + t <= budget:
-                ex_index[i] = len(ex_index)
-                used += t
-        if ex_index:
-            try:
-                from deepwell_b200.exchange import QuantizedRowExchange
-                order = sorted(ex_index, key=lambda j: ex_index[j])
-                exchange = QuantizedRowExchange([(M_TOKENS, layers[i]["k"]) for i in order], device=dev,
-                                                push=args.exchange_push)
-                exchange_info = {"layers": [layers[i]["name"] for i in order], "how": exchange.how, "push": exchange.push,
-                                 "bytes_pushed_per_rank_per_step": int(exchange.bytes_pushed_per_call)}
-            except Exception as e:          # no peer mapping on this box: every rank quantises everything itself
-                exchange, ex_index = None, {}
-                exchange_info = {"error": f"{type(e).__name__}: {str(e)[:300]}"}
+
+        def plan_for(factor):
+            left, rows = factor * gemm_s, []
+            for i in order:
+                per_row = layers[i]["k"] * (1 + 1 / 32) * (world - 1) / world / 700e9
+                r = min(M_TOKENS, int(left / per_row)) // (128 * world) * (128 * world)
+                rows.append(r)
+                left -= r * per_row
+            return rows
+
+        factors = [1e9 if f.strip() == "all" else float(f) for f in str(args.exchange_budget).split(",") if f.strip()]
+        for f in factors:
+            plan = plan_for(f)
+            if plan not in [q for _, q in ex_plans]:
+                ex_plans.append((f, plan))
+        try:
+            from deepwell_b200.exchange import QuantizedRowExchange
+            exchange = QuantizedRowExchange([(M_TOKENS, layers[i]["k"]) for i in order], device=dev, push=args.exchange_push)
+            exchange.set_shared_rows(ex_plans[0][1])
+            exchange_info = {"layers": [layers[i]["name"] for i in order], "how": exchange.how, "push": exchange.push}
+        except Exception as e:          # no peer mapping on this box: every rank quantises everything itself
+            exchange, ex_index = None, {}
+            exchange_info = {"error": f"{type(e).__name__}: {str(e)[:300]}"}
     step_no = [0]
 
     def exchange_step(record: bool, after_gemm=None):
@@ -1050,8 +1064,7 @@ def main():
         are quantised here; a 4-byte all-reduce at the end makes the next step's operands complete on every rank."""
         now, nxt = step_no[0] % 2, (step_no[0] + 1) % 2
         order = sorted(ex_index, key=lambda j: ex_index[j])
-        exchange.quantise_and_push([layers[i]["x"] for i in order], nxt)
-        n_launch = len(order)
+        n_launch = exchange.quantise_and_push([layers[i]["x"] for i in order], nxt)
         for i, l in enumerate(layers):
             if i in ex_index:
                 a_codes, a_sf = exchange.operand(now, ex_index[i])
@@ -1137,9 +1150,27 @@ def main():
 
     if overlap:
         quantise_operands(layers[0], 0)               # the pipeline's first operands; later ones follow a GEMM
-    if exchange is not None:                          # the first step's operands: slot 0
+    def prime_exchange():                             # the first step's operands: slot 0
+        step_no[0] = 0
         exchange.quantise_and_push([layers[i]["x"] for i in sorted(ex_index, key=lambda j: ex_index[j])], 0)
         exchange.fence(0)
+
+    if exchange is not None:
+        if len(ex_plans) > 1:                         # measure the candidates, keep the fastest (the same on every rank)
+            tried = []
+            for f, plan in ex_plans:
+                exchange.set_shared_rows(plan)
+                prime_exchange()
+                for _ in range(2):
+                    step(False)
+                t_ms, _ = timed_steps(6, False)
+                tried.append((t_ms / 6, f, plan))
+            best = min(tried, key=lambda t: t[0])
+            exchange.set_shared_rows(best[2])
+            exchange_info["tried_ms_per_step"] = {("all" if f > 1e6 else f"{f:g} x GEMM time"): round(t, 4) for t, f, _ in tried}
+        exchange_info["shared_rows"] = list(exchange.shared_rows)
+        exchange_info["bytes_pushed_per_rank_per_step"] = int(exchange.bytes_pushed_per_call)
+        prime_exchange()
     for _ in range(warmup):
         step(False)
     nv.check_status(dev)
@@ -1241,8 +1272,9 @@ def main():
         sustained = {"value": sus_value, "unit": "TFLOP/s", "ms_per_step": sus_step, "steps": n_sus, "seconds": sus_ms / 1e3,
                      "sm_mhz_median": sus_clocks["sm_mhz"], "sm_max_mhz": sus_clocks["sm_max_mhz"],
                      "reasons": sus_clocks["reasons"], "clock_samples": sus_clocks["samples"],
-                     "frac_of_sustained_peak": sus_value / peak_sustained, "frac_of_burst_peak": sus_value / peak_burst,
-                     "note": "whole step (quantisers + GEMMs) over 2 x measured sustained / burst bf16 rate"}
+                     "frac_of_sustained_peak": sus_value / world / peak_sustained,
+                     "frac_of_burst_peak": sus_value / world / peak_burst,
+                     "note": "whole step (quantisers + GEMMs), per GPU, over 2 x measured sustained / burst bf16 rate"}
         nv.check_status(dev)
 
     # ---- quantiser bandwidth (second kernel of the path), timed alone on the largest activation ----
@@ -1400,9 +1432,10 @@ def main():
                 "vs_baseline": None, "dtype": "mxfp8(e4m3+e8m0), fp32 accumulate, bf16 out", "data": "synthetic",
                 "config": {"workload": WORKLOAD, "M": M_TOKENS, "layers": {n: [k, nn] for n, k, nn in LAYERS},
                            "parallelism": f"N-sharded x{world}, X replicated, no data-path collective" if exchange is None else
-                                          f"N-sharded x{world}, X replicated; the quantisation of X for {exchange_info['layers']} is shared: "
-                                          "each rank quantises 1/N of the rows and copies its slice into every peer's operand buffer over "
-                                          "NVLink (copy engines, under the GEMMs); one 4-byte all-reduce per step as fence",
+                                          f"N-sharded x{world}, X replicated; the quantisation of X is shared (rows {exchange_info['shared_rows']} of "
+                                          f"{exchange_info['layers']}): each rank quantises 1/N of those rows and copies its slice into every peer's "
+                                          "operand buffer over NVLink (copy engines, under the GEMMs), the other rows every rank quantises itself; "
+                                          "one 4-byte all-reduce per step as fence",
                            "step": "per layer: quantise X, quantise W shard, block-scaled GEMM"
                                    + ("; each GEMM is issued before the next layer's quantisers, which may start while it "
                                       "runs (DW_QUANT_OVERLAP_PREVIOUS)" if overlap else

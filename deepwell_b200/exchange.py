@@ -10,6 +10,7 @@ Those copies are executed by the copy engines, which, unlike any kernel, run whi
 the exchange for the next step hides under this step's GEMMs.
 
     ex = QuantizedRowExchange([(M, K0), (M, K1), ...], group)      # once; allocates and maps the operand buffers
+    ex.set_shared_rows([M, M // 2, ...])                           # optional: how many rows of each activation are shared
     step s:   ex.quantise_and_push(xs, slot=(s + 1) % 2)          # own slices -> every rank's buffers, asynchronously
               ... GEMMs of step s on ex.operand(slot=s % 2, i) ...
               ex.fence((s + 1) % 2)                                # all slices of the next slot have landed everywhere
@@ -18,6 +19,10 @@ The operand buffers live in memory every rank of the node can address (torch sym
 allocations as a slow last resort).  The fence is one 4-byte all-reduce per step: when it completes on a
 rank, every rank has passed the point behind its own pushes and behind its GEMMs of the step, so the next slot is complete
 everywhere and the slot just used may be overwritten.
+
+What a rank receives per step crosses its NVLink ports at ~750 GB/s; where the GEMMs of a step are shorter than that transfer
+(eight ranks on the Llama-3-8B shapes) only the first `shared_rows[i]` rows of an activation are shared and every rank
+quantises the remaining rows itself, so that the transfer still ends before the step does.
 """
 from __future__ import annotations
 
@@ -59,6 +64,44 @@ def _map_on_all_ranks(nbytes: int, device: torch.device, group) -> Tuple[List[to
     raise RuntimeError("no way to map peer memory: " + "; ".join(errors))
 
 
+class SlotLayout:
+    """Where the row-wise operands of several activations sit in one slot of the exchange buffer, and which bytes of them
+    belong to which rows.  Pure arithmetic (no device): per activation the payload [rows, cols] then its tiled scales, each
+    256-byte aligned.  Rows come in whole 128-row scale tiles, so rows [r0, r1) are one contiguous byte range of the payload
+    and one of the scale buffer."""
+
+    def __init__(self, shapes: Sequence[Tuple[int, int]], world: int):
+        self.world = int(world)
+        self.shapes = [(int(r), int(c)) for r, c in shapes]
+        for rows, cols in self.shapes:
+            if rows % (128 * self.world) or cols % 32:
+                raise ValueError(f"activation {rows} x {cols}: rows must be a multiple of 128 x world ({128 * self.world}), "
+                                 "cols of 32, so that every rank's slice is whole scale tiles")
+        self.offsets, off = [], 0           # (payload offset, payload bytes, scale offset, scale bytes) per activation
+        for rows, cols in self.shapes:
+            code_bytes, sf_bytes = rows * cols, (rows // 128) * (-(-(cols // 32) // 4)) * 512
+            self.offsets.append((off, code_bytes, off + -(-code_bytes // 256) * 256, sf_bytes))
+            off = self.offsets[-1][2] + -(-sf_bytes // 256) * 256
+        self.slot_bytes = off
+
+    def check_shared_rows(self, shared_rows: Optional[Sequence[int]]) -> List[int]:
+        rows = [r for r, _ in self.shapes]
+        wanted = rows if shared_rows is None else [int(r) for r in shared_rows]
+        if len(wanted) != len(rows) or any(w < 0 or w > r or w % (128 * self.world) for w, r in zip(wanted, rows)):
+            raise ValueError(f"shared_rows must be one multiple of {128 * self.world} in [0, rows] per activation")
+        return wanted
+
+    def rows_of(self, shared: int, rank: int) -> Tuple[int, int]:
+        """The part [r0, r1) of the shared rows [0, shared) that `rank` quantises."""
+        return rank * shared // self.world, (rank + 1) * shared // self.world
+
+    def byte_ranges(self, i: int, r0: int, r1: int) -> Tuple[int, int, int, int]:
+        """[c_lo, c_hi) of the payload and [s_lo, s_hi) of the tiled scales of activation i that hold rows [r0, r1)."""
+        rows, cols = self.shapes[i]
+        sf_per_row_tile = self.offsets[i][3] // (rows // 128)
+        return r0 * cols, r1 * cols, (r0 // 128) * sf_per_row_tile, (r1 // 128) * sf_per_row_tile
+
+
 class QuantizedRowExchange:
     """Row-wise MXFP8 operands (codes [rows, cols] + tiled scales) of replicated activations, each rank quantising
     rows [rank * rows / world, (rank + 1) * rows / world) and copying them into every peer's buffer."""
@@ -70,32 +113,40 @@ class QuantizedRowExchange:
         self.group = group
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
-        self.shapes = [(int(r), int(c)) for r, c in shapes]
+        self.layout = SlotLayout(shapes, self.world)
+        self.shapes, self._offsets, self.slot_bytes = self.layout.shapes, self.layout.offsets, self.layout.slot_bytes
         self.slots, self.rule = slots, scale_rule
-        for rows, cols in self.shapes:
-            if rows % (128 * self.world) or cols % 32:
-                raise ValueError(f"activation {rows} x {cols}: rows must be a multiple of 128 x world ({128 * self.world}), "
-                                 "cols of 32, so that every rank's slice is whole scale tiles")
-        # layout of one slot: per activation, payload then tiled scales, each 256-byte aligned
-        self._offsets, off = [], 0
-        for rows, cols in self.shapes:
-            code_bytes, sf_bytes = rows * cols, nv.scale_bytes(rows, cols, nv.SF_TILED)
-            self._offsets.append((off, code_bytes, off + -(-code_bytes // 256) * 256, sf_bytes))
-            off = self._offsets[-1][2] + -(-sf_bytes // 256) * 256
-        self.slot_bytes = off
+        for (rows, cols), (_, _, _, sf_bytes) in zip(self.shapes, self._offsets):
+            assert sf_bytes == nv.scale_bytes(rows, cols, nv.SF_TILED)       # the library's tiled layout is the one assumed here
         self.views, self.how = _map_on_all_ranks(self.slot_bytes * slots, self.device, group)
         self.copy_stream = torch.cuda.Stream(self.device)
         self._quantised = [torch.cuda.Event() for _ in range(slots)]
         self._pushed = [torch.cuda.Event() for _ in range(slots)]
         self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
-        self.bytes_pushed_per_call = sum((cb + sb) // self.world for _, cb, _, sb in self._offsets) * (self.world - 1)
         # The copies of one slot always run between the same addresses: 2 x activations x (world - 1) of them.  Issued one
         # by one they cost the host about 16 us each, more than a step's GEMMs last on 8 GPUs, so each slot's copies are
         # recorded once as a CUDA graph of memcpy nodes and replayed with a single launch.
         if push not in ("graph", "stream"):
             raise ValueError("push must be 'graph' or 'stream'")
         self.push = push
-        self._graphs = [self._capture_copies(slot) for slot in range(slots)] if push == "graph" and self.world > 1 else None
+        self._graphs = None
+        self.shared_rows: List[int] = []
+        self.set_shared_rows(None)
+
+    def set_shared_rows(self, shared_rows: Optional[Sequence[int]]) -> None:
+        """Collective: rows [0, shared_rows[i]) of activation i are quantised once (1/world of them per rank) and exchanged,
+        rows from shared_rows[i] on by every rank itself.  None = all rows shared.  Each count must be a multiple of
+        128 x world (0 = not shared at all).  The operand buffers hold stale data afterwards until the next
+        quantise_and_push of each slot."""
+        wanted = self.layout.check_shared_rows(shared_rows)
+        torch.cuda.synchronize(self.device)          # no copy of the old plan in flight on this rank ...
+        dist.barrier(group=self.group)               # ... or on any other
+        self.shared_rows = wanted
+        self.bytes_pushed_per_call = sum(self._slice_bytes(i) for i in range(len(self.shapes))) * (self.world - 1)
+        self._graphs = None
+        if self.push == "graph" and self.world > 1 and self.bytes_pushed_per_call > 0:
+            self._graphs = [self._capture_copies(slot) for slot in range(self.slots)]
+        dist.barrier(group=self.group)
 
     def _region(self, view: torch.Tensor, slot: int, i: int):
         c_off, c_bytes, s_off, s_bytes = self._offsets[i]
@@ -107,18 +158,26 @@ class QuantizedRowExchange:
         codes, scales = self._region(self.views[self.rank], slot, i)
         return codes.view(self.shapes[i]), scales
 
+    def _rows_of(self, i: int, rank: int) -> Tuple[int, int]:
+        return self.layout.rows_of(self.shared_rows[i], rank)
+
+    def _byte_ranges(self, i: int, r0: int, r1: int) -> Tuple[int, int, int, int]:
+        return self.layout.byte_ranges(i, r0, r1)
+
     def _slice(self, i: int) -> Tuple[int, int, int, int]:
-        """Byte ranges [c_lo, c_hi) of the payload and [s_lo, s_hi) of the tiled scales that hold this rank's rows of activation i."""
-        rows, cols = self.shapes[i]
-        r0, r1 = self.rank * rows // self.world, (self.rank + 1) * rows // self.world
-        sf_per_row_tile = self._offsets[i][3] // (rows // 128)
-        return r0 * cols, r1 * cols, (r0 // 128) * sf_per_row_tile, (r1 // 128) * sf_per_row_tile
+        return self._byte_ranges(i, *self._rows_of(i, self.rank))
+
+    def _slice_bytes(self, i: int) -> int:
+        c_lo, c_hi, s_lo, s_hi = self._slice(i)
+        return (c_hi - c_lo) + (s_hi - s_lo)
 
     def _issue_copies(self, slot: int) -> None:
         for step in range(1, self.world):                         # every rank starts with a different peer
             peer = (self.rank + step) % self.world
             for i in range(len(self.shapes)):
                 c_lo, c_hi, s_lo, s_hi = self._slice(i)
+                if c_hi == c_lo:
+                    continue
                 src_c, src_s = self._region(self.views[self.rank], slot, i)
                 dst_c, dst_s = self._region(self.views[peer], slot, i)
                 dst_c[c_lo:c_hi].copy_(src_c[c_lo:c_hi], non_blocking=True)
@@ -131,19 +190,27 @@ class QuantizedRowExchange:
             self._issue_copies(slot)
         return graph
 
-    def quantise_and_push(self, xs: Sequence[torch.Tensor], slot: int) -> None:
-        """Quantises this rank's row slice of every activation into `slot` (current stream) and copies the slices into
-        every peer's buffer (copy stream: copy engines over NVLink, asynchronous to the current stream)."""
+    def quantise_and_push(self, xs: Sequence[torch.Tensor], slot: int) -> int:
+        """Quantises this rank's row slice of every activation (and the rows that are not shared) into `slot` on the current
+        stream and copies the slices into every peer's buffer (copy stream: copy engines over NVLink, asynchronous to the
+        current stream).  Returns the number of quantiser launches."""
+        launches = 0
         if len(xs) != len(self.shapes):
             raise ValueError("one tensor per registered activation")
         for i, x in enumerate(xs):
             rows, cols = self.shapes[i]
             if tuple(x.shape) != (rows, cols) or x.dtype != torch.bfloat16 or not x.is_contiguous():
                 raise ValueError(f"activation {i} must be a contiguous bfloat16 [{rows}, {cols}] tensor")
-            r0, r1 = self.rank * rows // self.world, (self.rank + 1) * rows // self.world
             codes, scales = self._region(self.views[self.rank], slot, i)
-            c_lo, c_hi, s_lo, s_hi = self._slice(i)
-            nv.quantize_into(x[r0:r1], codes[c_lo:c_hi], scales[s_lo:s_hi], nv.DIR_ROW, self.rule, nv.SF_TILED)
+            r0, r1 = self._rows_of(i, self.rank)
+            if r1 > r0:                                # this rank's part of the shared rows
+                c_lo, c_hi, s_lo, s_hi = self._byte_ranges(i, r0, r1)
+                nv.quantize_into(x[r0:r1], codes[c_lo:c_hi], scales[s_lo:s_hi], nv.DIR_ROW, self.rule, nv.SF_TILED)
+                launches += 1
+            if self.shared_rows[i] < rows:             # the rows every rank quantises itself
+                c_lo, c_hi, s_lo, s_hi = self._byte_ranges(i, self.shared_rows[i], rows)
+                nv.quantize_into(x[self.shared_rows[i]:], codes[c_lo:c_hi], scales[s_lo:s_hi], nv.DIR_ROW, self.rule, nv.SF_TILED)
+                launches += 1
         self._quantised[slot].record()
         self.copy_stream.wait_event(self._quantised[slot])
         with torch.cuda.stream(self.copy_stream):
@@ -152,6 +219,7 @@ class QuantizedRowExchange:
             else:
                 self._issue_copies(slot)
             self._pushed[slot].record()
+        return launches
 
     def fence(self, slot: int) -> None:
         """After this returns (stream-wise), every rank's slices of `slot` are in this rank's buffer, and every rank has
