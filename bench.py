@@ -906,6 +906,10 @@ def main():
                     help="N > 1: share as many rows of X as a rank can receive (at 700 GB/s) in this multiple of the step's GEMM "
                          "time ('all' = every row); several values, comma-separated: each is tried for a few steps before the "
                          "timed region and the fastest kept")
+    ap.add_argument("--quant-batch-pairs", action="store_true",
+                    help="the activation and the weight shard of a layer quantised by one launch (dw_mxfp8_quantize_rows_batch)")
+    ap.add_argument("--no-quant-batch", action="store_true",
+                    help="N > 1: one quantiser launch per slice and weight shard instead of dw_mxfp8_quantize_rows_batch")
     ap.add_argument("--no-exchange", action="store_true",
                     help="N > 1: every rank quantises the whole of every X itself (no sharing of the quantisation over NVLink)")
     ap.add_argument("--profile-case", default=None, choices=["gemm", "quant_row", "quant_both", "quant_col", "quant_col_long"],
@@ -995,7 +999,18 @@ def main():
         l["consumed"] = torch.cuda.Event()             # the GEMM that read them has finished
     gemm_events, pair_events = [], []
 
+    import ctypes
+    for l in layers:                                   # argument arrays of the one-launch form (X and W of a layer together)
+        P2, I2 = ctypes.c_void_p * 2, ctypes.c_int64 * 2
+        l["batch_args"] = (P2(l["x"].data_ptr(), l["w"].data_ptr()), P2(l["xc"].data_ptr(), l["wc"].data_ptr()),
+                           P2(l["xs"].data_ptr(), l["ws"].data_ptr()), I2(M_TOKENS, l["n"]), I2(l["k"], l["k"]))
+    pair_batch = args.quant_batch_pairs and all(l["n"] % 128 == 0 and l["k"] % 128 == 0 for l in layers) and M_TOKENS % 128 == 0
+
     def quantise_operands(l, flags):
+        if pair_batch:
+            xa, ca, sa, ra, ka = l["batch_args"]
+            nv.check(L.dw_mxfp8_quantize_rows_batch(2, xa, ca, sa, ra, ka, nv.RULE_OCP_FLOOR, nv.SF_TILED, flags, st), "quantize X, W")
+            return
         nv.check(L.dw_mxfp8_quantize_ex(l["x"].data_ptr(), l["xc"].data_ptr(), l["xs"].data_ptr(), M_TOKENS, l["k"],
                                         nv.DIR_ROW, nv.RULE_OCP_FLOOR, nv.SF_TILED, flags, st), "quantize X")
         nv.check(L.dw_mxfp8_quantize_ex(l["w"].data_ptr(), l["wc"].data_ptr(), l["ws"].data_ptr(), l["n"], l["k"],
@@ -1021,7 +1036,7 @@ def main():
                 pair_events.append((e0, e1))
             if after_gemm is not None:
                 after_gemm(l)
-        return 3 * len(layers)
+        return (2 if pair_batch else 3) * len(layers)
 
     # ---- N > 1: the ranks share the quantisation of the replicated activations (deepwell_b200/exchange.py) ----
     # How much is shared is a budget: the rows a rank can receive per step (at ~700 GB/s) within a multiple of the step's
@@ -1064,7 +1079,10 @@ def main():
         are quantised here; a 4-byte all-reduce at the end makes the next step's operands complete on every rank."""
         now, nxt = step_no[0] % 2, (step_no[0] + 1) % 2
         order = sorted(ex_index, key=lambda j: ex_index[j])
-        n_launch = exchange.quantise_and_push([layers[i]["x"] for i in order], nxt)
+        # the rank's row slices and its weight shards are small: all of them leave in one or two launches
+        batch_w = not args.no_quant_batch
+        n_launch = exchange.quantise_and_push([layers[i]["x"] for i in order], nxt,
+                                              extra=[(l["w"], l["wc"].view(torch.uint8), l["ws"]) for l in layers] if batch_w else ())
         for i, l in enumerate(layers):
             if i in ex_index:
                 a_codes, a_sf = exchange.operand(now, ex_index[i])
@@ -1074,13 +1092,15 @@ def main():
                                              nv.DIR_ROW, nv.RULE_OCP_FLOOR, nv.SF_TILED, st), "quantize X")
                 a_ptr, s_ptr = l["xc"].data_ptr(), l["xs"].data_ptr()
                 n_launch += 1
-            nv.check(L.dw_mxfp8_quantize(l["w"].data_ptr(), l["wc"].data_ptr(), l["ws"].data_ptr(), l["n"], l["k"],
-                                         nv.DIR_ROW, nv.RULE_OCP_FLOOR, nv.SF_TILED, st), "quantize W")
+            if not batch_w:
+                nv.check(L.dw_mxfp8_quantize(l["w"].data_ptr(), l["wc"].data_ptr(), l["ws"].data_ptr(), l["n"], l["k"],
+                                             nv.DIR_ROW, nv.RULE_OCP_FLOOR, nv.SF_TILED, st), "quantize W")
+                n_launch += 1
             if after_gemm is not None and "gather_done" in l:
                 stream.wait_event(l["gather_done"])
             nv.check(L.dw_mxfp8_gemm(a_ptr, s_ptr, l["wc"].data_ptr(), l["ws"].data_ptr(), l["y"].data_ptr(), None,
                                      M_TOKENS, l["n"], l["k"], 1.0, 0.0, None, 0, status.data_ptr(), st), "gemm")
-            n_launch += 2
+            n_launch += 1
             if after_gemm is not None:
                 after_gemm(l)
         exchange.fence(nxt)

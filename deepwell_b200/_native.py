@@ -41,7 +41,7 @@ ABI_SYMBOLS = (
     "dw_mxfp8_colsum_workspace", "dw_mxfp8_quantize_both_colsum", "dw_mxfp8_gemm_grouped",
     "dw_mxfp8_update_amax_history", "dw_mxfp8_gemm_planned", "dw_mxfp8_gemm_workspace_planned",
     "dw_mxfp8_selftest_bounded_wait", "dw_mxfp8_debug_fake_device", "dw_mxfp8_debug_counter",
-    "dw_mxfp8_quantize_set_tuning", "dw_mxfp8_quantize_ex",
+    "dw_mxfp8_quantize_set_tuning", "dw_mxfp8_quantize_ex", "dw_mxfp8_quantize_rows_batch",
 )
 
 _lib = None
@@ -75,6 +75,8 @@ def load() -> ctypes.CDLL:
     L.dw_mxfp8_quantize.argtypes = [p, p, p, i64, i64, i32, i32, i32, p]
     L.dw_mxfp8_quantize_set_tuning.argtypes = [i32]
     L.dw_mxfp8_quantize_ex.argtypes = [p, p, p, i64, i64, i32, i32, i32, i32, p]
+    L.dw_mxfp8_quantize_rows_batch.argtypes = [i32, ctypes.POINTER(p), ctypes.POINTER(p), ctypes.POINTER(p),
+                                               ctypes.POINTER(i64), ctypes.POINTER(i64), i32, i32, i32, p]
     L.dw_mxfp8_quantize_both.argtypes = [p, p, p, p, p, i64, i64, i32, i32, p]
     L.dw_mxfp8_dequantize.argtypes = [p, p, p, i64, i64, i32, p]
     L.dw_mxfp8_update_amax_history.argtypes = [p, p, i32, i64, p]
@@ -158,6 +160,43 @@ def quantize_into(x: torch.Tensor, codes: torch.Tensor, scales: torch.Tensor, di
     with torch.cuda.device(x.device):
         check(load().dw_mxfp8_quantize(x.data_ptr(), codes.data_ptr(), scales.data_ptr(), rows, cols, direction, rule, layout,
                                        _stream(x.device)), "dw_mxfp8_quantize")
+
+
+QUANT_BATCH_MAX = 8
+
+
+def quantize_rows_batch_into(xs, codes, scales, rule: int = RULE_OCP_FLOOR, layout: int = SF_TILED, flags: int = 0) -> int:
+    """Row-wise quantisation of several matrices into caller-provided buffers with as few launches as possible
+    (dw_mxfp8_quantize_rows_batch, up to QUANT_BATCH_MAX matrices per launch).  Every matrix must meet that entry point's
+    conditions (cols % 32 == 0, 16-byte aligned; tiled scales: rows % 128 == 0 and cols % 128 == 0).  Returns the number
+    of launches."""
+    if not (len(xs) == len(codes) == len(scales)):
+        raise RuntimeError("one codes and one scales buffer per input")
+    if not xs:
+        return 0
+    dev = xs[0].device
+    for x, c, s in zip(xs, codes, scales):
+        _require_cuda(x, "input")
+        if x.device != dev or c.device != dev or s.device != dev:
+            raise RuntimeError("all tensors of a batch must be on one device")
+        if x.dtype != torch.bfloat16 or x.dim() != 2 or not x.is_contiguous():
+            raise RuntimeError("inputs must be contiguous 2-D bfloat16 tensors")
+        rows, cols = x.shape
+        if c.numel() * c.element_size() != rows * cols or not c.is_contiguous() or not s.is_contiguous() \
+                or s.numel() < scale_bytes(rows, cols, layout):
+            raise RuntimeError("output buffers do not match the operand")
+    L, launches = load(), 0
+    with torch.cuda.device(dev):
+        for at in range(0, len(xs), QUANT_BATCH_MAX):
+            part = range(at, min(at + QUANT_BATCH_MAX, len(xs)))
+            n = len(part)
+            P, I = ctypes.c_void_p * n, ctypes.c_int64 * n
+            check(L.dw_mxfp8_quantize_rows_batch(
+                n, P(*[xs[i].data_ptr() for i in part]), P(*[codes[i].data_ptr() for i in part]),
+                P(*[scales[i].data_ptr() for i in part]), I(*[xs[i].shape[0] for i in part]), I(*[xs[i].shape[1] for i in part]),
+                rule, layout, flags, _stream(dev)), "dw_mxfp8_quantize_rows_batch")
+            launches += 1
+    return launches
 
 
 def quantize_both(x: torch.Tensor, rule: int = RULE_OCP_FLOOR, layout: int = SF_TILED):

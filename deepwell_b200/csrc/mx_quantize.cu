@@ -115,6 +115,26 @@ mx_quant_row_bg_kernel(const RowQuantJob job) {
     quant_row_slabs<kDeep>(job, blockIdx.x, gridDim.x, threadIdx.x);
 }
 
+// Several matrices in one launch (dw_mxfp8_quantize_rows_batch): block b works on slab b - first_slab[j] of the job j whose
+// range of slabs holds b.  For the small operands of a sharded step (a rank's row slices of the activations, its weight
+// shards), where every separate launch pays its own ramp and tail.
+constexpr int kMaxRowQuantJobs = DW_QUANT_BATCH_MAX;
+struct RowQuantBatch {
+    RowQuantJob job[kMaxRowQuantJobs];
+    uint32_t first_slab[kMaxRowQuantJobs + 1];
+    int count;
+};
+template <int kDeep>
+__global__ void __maxnreg__(88)
+mx_quant_row_batch_kernel(const __grid_constant__ RowQuantBatch b) {
+    int j = 0;
+    while (j + 1 < b.count && blockIdx.x >= b.first_slab[j + 1]) ++j;
+    const RowQuantJob job = b.job[j];
+    const uint64_t slab = blockIdx.x - b.first_slab[j];
+    if (job.wide) quant_row_slab<kDeep, true, kRowSlabThreads>(job, slab, threadIdx.x);
+    else quant_row_slab<kDeep, false, kRowSlabThreads>(job, slab, threadIdx.x);
+}
+
 // Writes 127 into the padding bytes of a tiled scale buffer that mx_quant_row_kernel does not
 // touch (rows beyond `rows` in the last row tile, k-blocks beyond `kb` in the last k tile).
 __global__ void mx_sf_pad_kernel(uint8_t* __restrict__ scales, int64_t rows, int64_t kb, int64_t rt, int64_t kt) {
@@ -678,6 +698,54 @@ extern "C" DW_API int dw_mxfp8_quantize_ex(const void* x_bf16, void* codes, void
         return launch_tile_kernel<false, true>(x, nullptr, nullptr, c, s, rows, cols, tiles_c, tiles, scale_rule, scale_layout, di, st);
     }
     return quantize_generic(x, c, s, rows, cols, direction, scale_rule, scale_layout, di, st);
+}
+
+extern "C" DW_API int dw_mxfp8_quantize_rows_batch(int count, const void* const* x_bf16, void* const* codes, void* const* scales,
+                                                   const int64_t* rows, const int64_t* cols, int scale_rule, int scale_layout,
+                                                   int flags, void* stream) {
+    if (count < 0 || count > DW_QUANT_BATCH_MAX || (flags & ~DW_QUANT_OVERLAP_PREVIOUS) != 0) return DW_ERR_BAD_ARG;
+    if (scale_rule != DW_RULE_OCP_FLOOR && scale_rule != DW_RULE_REF_CEIL) return DW_ERR_BAD_ARG;
+    if (scale_layout != DW_SF_FLAT && scale_layout != DW_SF_TILED) return DW_ERR_BAD_ARG;
+    if (count == 0) return DW_OK;
+    if (!x_bf16 || !codes || !scales || !rows || !cols) return DW_ERR_BAD_ARG;
+    constexpr int kDeep = 8;
+    RowQuantBatch b = {};
+    uint64_t slabs = 0;
+    for (int i = 0; i < count; ++i) {
+        if (rows[i] < 0 || cols[i] < 0) return DW_ERR_BAD_ARG;
+        if (rows[i] == 0 || cols[i] == 0) continue;                       // empty matrix: nothing to write
+        if (!x_bf16[i] || !codes[i] || !scales[i]) return DW_ERR_BAD_ARG;
+        if (rows[i] * cols[i] >= (1ll << 35)) return DW_ERR_TOO_LARGE;
+        // whole scale tiles only: this entry point has no padding pass
+        if (scale_layout == DW_SF_TILED && (rows[i] % 128 != 0 || cols[i] % 128 != 0)) return DW_ERR_BAD_ARG;
+        RowQuantJob* job = &b.job[b.count];
+        if (!make_row_quant_job(job, x_bf16[i], codes[i], scales[i], rows[i], cols[i], scale_rule, scale_layout)) return DW_ERR_BAD_ARG;
+        b.first_slab[b.count] = static_cast<uint32_t>(slabs);
+        slabs += (static_cast<uint64_t>(job->total_chunks) + kRowSlabThreads * kDeep - 1) / (kRowSlabThreads * kDeep);
+        ++b.count;
+    }
+    if (b.count == 0) return DW_OK;
+    if (slabs >= (1ull << 31)) return DW_ERR_TOO_LARGE;
+    b.first_slab[b.count] = static_cast<uint32_t>(slabs);
+    DeviceInfo di;
+    const int drc = current_device(&di);
+    if (drc != DW_OK) return drc;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(slabs));
+    cfg.blockDim = dim3(kRowSlabThreads);
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    if (flags & DW_QUANT_OVERLAP_PREVIOUS) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    if (cudaLaunchKernelEx(&cfg, mx_quant_row_batch_kernel<kDeep>, b) != cudaSuccess) {
+        cudaGetLastError();
+        return DW_ERR_LAUNCH;
+    }
+    return DW_OK;
 }
 
 extern "C" DW_API int dw_mxfp8_quantize_both(const void* x_bf16, void* codes_row, void* scales_row, void* codes_col_t,

@@ -190,27 +190,37 @@ class QuantizedRowExchange:
             self._issue_copies(slot)
         return graph
 
-    def quantise_and_push(self, xs: Sequence[torch.Tensor], slot: int) -> int:
+    def quantise_and_push(self, xs: Sequence[torch.Tensor], slot: int,
+                          extra: Sequence[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = ()) -> int:
         """Quantises this rank's row slice of every activation (and the rows that are not shared) into `slot` on the current
         stream and copies the slices into every peer's buffer (copy stream: copy engines over NVLink, asynchronous to the
-        current stream).  Returns the number of quantiser launches."""
-        launches = 0
+        current stream).  `extra`: further (input, codes, tiled scales) triples quantised row-wise in the same launches,
+        e.g. the rank's weight shards: the pieces of a sharded step are small, and one launch for all of them saves each
+        its own ramp and tail.  Returns the number of quantiser launches."""
         if len(xs) != len(self.shapes):
             raise ValueError("one tensor per registered activation")
+        jobs = []
         for i, x in enumerate(xs):
             rows, cols = self.shapes[i]
             if tuple(x.shape) != (rows, cols) or x.dtype != torch.bfloat16 or not x.is_contiguous():
                 raise ValueError(f"activation {i} must be a contiguous bfloat16 [{rows}, {cols}] tensor")
             codes, scales = self._region(self.views[self.rank], slot, i)
             r0, r1 = self._rows_of(i, self.rank)
-            if r1 > r0:                                # this rank's part of the shared rows
-                c_lo, c_hi, s_lo, s_hi = self._byte_ranges(i, r0, r1)
-                nv.quantize_into(x[r0:r1], codes[c_lo:c_hi], scales[s_lo:s_hi], nv.DIR_ROW, self.rule, nv.SF_TILED)
-                launches += 1
-            if self.shared_rows[i] < rows:             # the rows every rank quantises itself
-                c_lo, c_hi, s_lo, s_hi = self._byte_ranges(i, self.shared_rows[i], rows)
-                nv.quantize_into(x[self.shared_rows[i]:], codes[c_lo:c_hi], scales[s_lo:s_hi], nv.DIR_ROW, self.rule, nv.SF_TILED)
-                launches += 1
+            pieces = [(r0, r1)] if r1 > r0 else []                 # this rank's part of the shared rows
+            if self.shared_rows[i] < rows:
+                pieces.append((self.shared_rows[i], rows))         # the rows every rank quantises itself
+            for p0, p1 in pieces:
+                c_lo, c_hi, s_lo, s_hi = self._byte_ranges(i, p0, p1)
+                jobs.append((x[p0:p1], codes[c_lo:c_hi], scales[s_lo:s_hi]))
+        jobs.extend(extra)
+        if all(j[0].shape[0] % 128 == 0 and j[0].shape[1] % 128 == 0 and j[0].data_ptr() % 16 == 0 and j[1].data_ptr() % 16 == 0
+               for j in jobs):
+            launches = nv.quantize_rows_batch_into([j[0] for j in jobs], [j[1] for j in jobs], [j[2] for j in jobs],
+                                                   self.rule, nv.SF_TILED)
+        else:                                                      # shapes the batched launch does not take
+            for x, codes, scales in jobs:
+                nv.quantize_into(x, codes, scales, nv.DIR_ROW, self.rule, nv.SF_TILED)
+            launches = len(jobs)
         self._quantised[slot].record()
         self.copy_stream.wait_event(self._quantised[slot])
         with torch.cuda.stream(self.copy_stream):

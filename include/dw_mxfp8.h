@@ -86,6 +86,19 @@ int dw_mxfp8_quantize(const void *x_bf16, void *codes, void *scales, int64_t row
 int dw_mxfp8_quantize_ex(const void *x_bf16, void *codes, void *scales, int64_t rows, int64_t cols,
                          int direction, int scale_rule, int scale_layout, int flags, void *stream);
 
+/* Up to DW_QUANT_BATCH_MAX row-wise quantisations in ONE launch: matrix i is x_bf16[i] [rows[i], cols[i]] -> codes[i], scales[i],
+ * all with the same scale rule and scale layout.  For steps made of several small operands (on N GPUs a rank quantises its
+ * 1/N row slices of the activations and its 1/N weight shards), where every separate launch pays its own ramp and tail.
+ * Each matrix needs cols % 32 == 0 and 16-byte aligned x and codes; with DW_SF_TILED also rows % 128 == 0 and
+ * cols % 128 == 0 (whole scale tiles: this entry point writes no padding bytes); anything else is DW_ERR_BAD_ARG and the
+ * caller uses dw_mxfp8_quantize per matrix.  Empty matrices are skipped.  `flags` as for dw_mxfp8_quantize_ex.  Results are
+ * byte-identical to dw_mxfp8_quantize on each matrix.  The pointer arrays are host arrays read during the call.
+ * No counterpart in the reference (quantize_to_mxfp8_bf16, csrc/mxfp8_quantization.cu:232-240, takes one tensor). */
+#define DW_QUANT_BATCH_MAX 8
+int dw_mxfp8_quantize_rows_batch(int count, const void *const *x_bf16, void *const *codes, void *const *scales,
+                                 const int64_t *rows, const int64_t *cols, int scale_rule, int scale_layout, int flags,
+                                 void *stream);
+
 /* Tuning switch of the column-wise (transposed-payload) kernel, process-wide.  Bits [0,2): 0 or 2 = the transposed payload is
  * written through a shared-memory staging buffer, whole 128-byte row segments per store (the default); 1 = straight from
  * registers, 32 bytes per thread and output row (as fast or slightly faster on some GPUs while the output rows are less than

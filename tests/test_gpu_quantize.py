@@ -269,3 +269,50 @@ def test_amax_history_and_transpose_requantise(nv, native_lib):
     ec, es = o.quantize_colwise(deq)
     assert ct.shape == (160, 256) and np.array_equal(ct.view(torch.uint8).cpu().numpy(), ec)
     assert np.array_equal(st.cpu().numpy().reshape(es.shape), es)
+
+
+@pytest.mark.parametrize("rule", [0, 1])
+@pytest.mark.parametrize("layout_name", ["flat", "tiled"])
+def test_rows_batch_is_the_single_quantisations_in_one_launch(nv, rule, layout_name):
+    """dw_mxfp8_quantize_rows_batch: several matrices (here eleven, so two launches; sizes from one slab to several
+    hundred, one empty) give byte for byte what dw_mxfp8_quantize gives for each, and one of them is checked against
+    the C restatement."""
+    layout = nv.SF_FLAT if layout_name == "flat" else nv.SF_TILED
+    g = torch.Generator(device="cuda").manual_seed(99 + rule)
+    shapes = [(128, 128), (4096, 4096), (1536, 4096), (1024, 14336), (256, 384), (0, 128), (2048, 1024), (128, 8192),
+              (768, 4096), (512, 256), (3072, 768)]
+    if layout == nv.SF_FLAT:
+        shapes += [(100, 96), (33, 32)]                  # flat scales have no tile padding: any rows, cols % 32 == 0
+    xs = []
+    for r, k in shapes:
+        x = torch.randn(r, k, device="cuda", generator=g) * 0.5
+        if x.numel():
+            x.view(-1)[:: 97] *= 40.0
+        xs.append(x.bfloat16())
+    codes = [torch.full((r, k), 0xEE, dtype=torch.uint8, device="cuda") for r, k in shapes]
+    scales = [torch.full((nv.scale_bytes(r, k, layout),), 0xEE, dtype=torch.uint8, device="cuda") for r, k in shapes]
+    launches = nv.quantize_rows_batch_into(xs, codes, scales, rule, layout)
+    assert launches == -(-len(shapes) // nv.QUANT_BATCH_MAX)
+    for x, gc, gs in zip(xs, codes, scales):
+        if x.numel() == 0:
+            continue
+        ec, es = nv.quantize(x, nv.DIR_ROW, rule, layout)
+        assert torch.equal(gc, ec.view(torch.uint8)) and torch.equal(gs, es.view(torch.uint8).reshape(-1))
+    er, ers = c.quantize_rowwise(bits_of(xs[2]), rule)
+    exp = ers if layout == nv.SF_FLAT else o.sf_flat_to_tiled(ers)
+    assert np.array_equal(host(codes[2]), er) and np.array_equal(host(scales[2]), exp.reshape(-1))
+
+
+def test_rows_batch_rejects_what_it_cannot_do(nv, native_lib):
+    import ctypes
+    x = torch.zeros(100, 128, dtype=torch.bfloat16, device="cuda")
+    cbuf = torch.zeros(100, 128, dtype=torch.uint8, device="cuda")
+    sbuf = torch.zeros(nv.scale_bytes(100, 128, nv.SF_TILED), dtype=torch.uint8, device="cuda")
+    with pytest.raises(RuntimeError):                    # tiled scales with a ragged last row tile: no padding pass here
+        nv.quantize_rows_batch_into([x], [cbuf], [sbuf], 0, nv.SF_TILED)
+    n = nv.QUANT_BATCH_MAX + 1
+    P, I = ctypes.c_void_p * n, ctypes.c_int64 * n
+    rc = native_lib.dw_mxfp8_quantize_rows_batch(n, P(*[x.data_ptr()] * n), P(*[cbuf.data_ptr()] * n), P(*[sbuf.data_ptr()] * n),
+                                                 I(*[100] * n), I(*[128] * n), 0, nv.SF_FLAT, 0, None)
+    assert rc == -1                                      # DW_ERR_BAD_ARG: more matrices than one launch takes
+    assert native_lib.dw_mxfp8_quantize_rows_batch(0, None, None, None, None, None, 0, nv.SF_FLAT, 0, None) == 0
