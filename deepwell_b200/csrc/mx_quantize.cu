@@ -157,7 +157,8 @@ __global__ void mx_sf_pad_kernel(uint8_t* __restrict__ scales, int64_t rows, int
 // or the four blocks of two consecutive rows, land in 8 different 16-byte bank groups.
 __device__ __forceinline__ uint32_t tile_chunk(uint32_t c, uint32_t r) { return c ^ (r & 7u) ^ ((c >> 3) << 1); }
 
-constexpr int kTileSmemBytes = 2 * 128 * 16 * 16 + 1024 + 2048;   // two 32 KB tiles + two 512-byte scale staging areas + column sums
+// tile buffers of 32 KB (two, or three in the two-group form: see kSplit) + two 512-byte scale staging areas + column sums
+constexpr int tile_smem_bytes(bool split) { return (split ? 3 : 2) * 128 * 16 * 16 + 1024 + 2048; }
 
 // kColSum: also leave the fp32 sum of every column over this tile's 128 rows in colsum_partial[tile row][column]
 // (the bias gradient of a linear layer is the column sum of the output gradient that is being quantised here).
@@ -179,7 +180,10 @@ mx_quant_tile_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes
     // while this tile is quantised, so the SM always has loads outstanding.
     extern __shared__ __align__(16) uint8_t tile_smem[];
     typedef uint4 (*TilePtr)[16];
-    uint8_t* sf_row = tile_smem + 2 * 128 * 16 * 16;
+    // kSplit runs 2 CTAs of 512 threads per SM, which leaves room for a third tile buffer each: two tiles are then in
+    // flight while one is quantised (128 KB of loads outstanding per SM instead of 64 KB)
+    constexpr int kBufs = kSplit ? 3 : 2;
+    uint8_t* sf_row = tile_smem + kBufs * 128 * 16 * 16;
     uint8_t* sf_col = sf_row + 512;
     float* cs_stage = reinterpret_cast<float*>(sf_col + 512);       // [4 row blocks][128 columns]
 
@@ -230,11 +234,17 @@ mx_quant_tile_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes
 
     int buf = 0;
     if (blockIdx.x < num_tiles) { issue_half(blockIdx.x, 0, 0); issue_half(blockIdx.x, 0, 1); }
-    for (uint32_t id = blockIdx.x; id < num_tiles; id += gridDim.x, buf ^= 1) {
-    const uint32_t next = id + gridDim.x;
-    asm volatile("cp.async.wait_group 0;" ::: "memory");     // this tile (the only group in flight)
+    if (kBufs == 3) {                                        // the second tile of the ring (or an empty group: one group per tile)
+        if (blockIdx.x + gridDim.x < num_tiles) { issue_half(blockIdx.x + gridDim.x, 1, 0); issue_half(blockIdx.x + gridDim.x, 1, 1); }
+        else asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    for (uint32_t id = blockIdx.x; id < num_tiles; id += gridDim.x, buf = (buf + 1 == kBufs) ? 0 : buf + 1) {
+    const uint32_t next = id + (kBufs - 1) * gridDim.x;      // the tile fetched during this iteration
+    const int nbuf = (buf + kBufs - 1) % kBufs;              // into the buffer the previous iteration has finished with
+    if (kBufs == 3) asm volatile("cp.async.wait_group 1;" ::: "memory");     // this tile; the following one may still be in flight
+    else asm volatile("cp.async.wait_group 0;" ::: "memory");                // this tile (the only group in flight)
     __syncthreads();
-    if (next < num_tiles) issue_half(next, buf ^ 1, 0);
+    if (next < num_tiles) issue_half(next, nbuf, 0);
     TilePtr tile = reinterpret_cast<TilePtr>(tile_smem + buf * (128 * 16 * 16));
     const uint32_t tr = id / tiles_c, tc = id - tr * tiles_c;
     const int64_t r0 = static_cast<int64_t>(tr) * 128, c0 = static_cast<int64_t>(tc) * 128;
@@ -275,7 +285,8 @@ mx_quant_tile_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes
     // the warps enter the column pass together; on short runs (a few tiles per CTA) the extra barrier costs ~10 %.
     if (!kSplit && kDoRow && kDoCol && num_tiles > 8u * gridDim.x) __syncthreads();
 
-    if (next < num_tiles) issue_half(next, buf ^ 1, 1);
+    if (next < num_tiles) issue_half(next, nbuf, 1);
+    else if (kBufs == 3) asm volatile("cp.async.commit_group;" ::: "memory");
     uint32_t qa[8], qb[8];                                // the column pass's codes: 32 rows of two columns
     const uint32_t p = t & 63u, rb = t >> 6;              // column pass: thread = (column pair p, row block rb)
     if (col_role) {
@@ -574,7 +585,7 @@ static int launch_tile_kernel_impl(const uint16_t* x, uint8_t* cr, uint8_t* sr, 
         std::lock_guard<std::mutex> lock(mu);
         if (!done[di.device]) {
             if (cudaFuncSetAttribute(mx_quant_tile_kernel<kDoRow, kDoCol, kColSum, kStaged, kSplit>,
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, kTileSmemBytes) != cudaSuccess) {
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, tile_smem_bytes(kSplit)) != cudaSuccess) {
                 cudaGetLastError();
                 return DW_ERR_LAUNCH;
             }
@@ -583,7 +594,7 @@ static int launch_tile_kernel_impl(const uint16_t* x, uint8_t* cr, uint8_t* sr, 
     }
     // 3 CTAs of 256 threads and 67 KB per SM, or 2 CTAs of 512 threads (kSplit)
     const uint32_t grid = std::min<uint32_t>(tiles, static_cast<uint32_t>(di.sms) * (kSplit ? 2u : 3u));
-    mx_quant_tile_kernel<kDoRow, kDoCol, kColSum, kStaged, kSplit><<<grid, kSplit ? 512 : 256, kTileSmemBytes, st>>>(
+    mx_quant_tile_kernel<kDoRow, kDoCol, kColSum, kStaged, kSplit><<<grid, kSplit ? 512 : 256, tile_smem_bytes(kSplit), st>>>(
         x, cr, sr, ct, sc, rows, cols, tiles_c, tiles, rule, layout, colsum_partial);
     return launch_status();
 }
@@ -600,9 +611,9 @@ static int launch_tile_kernel(const uint16_t* x, uint8_t* cr, uint8_t* sr, uint8
     const int mode = word & 3;                                                     // 0 automatic (staged), 1 direct, 2 staged
     const bool staged = kDoCol && mode != 1;
     constexpr bool kFused = kDoRow && kDoCol;
-    // two groups of threads side by side once a CTA has several tiles to work through (measured: 16384 x 4096 and larger
-    // gain 3-5 %, 16384 x 1024 loses 10 %); bit 2 of the tuning word: always one group
-    const bool split = kFused && ((word >> 2) & 1) == 0 && (tiles >= 2048u || ((word >> 3) & 1) != 0);   // bit 3: always two groups
+    // two groups of threads side by side (and three tile buffers) once a CTA has several tiles to work through (measured:
+    // 16384 x 4096 and larger gain 7-15 %, 8192 x 3072 5 %, 16384 x 1024 loses 9 %); bit 2 of the tuning word: always one group
+    const bool split = kFused && ((word >> 2) & 1) == 0 && (tiles >= 1536u || ((word >> 3) & 1) != 0);   // bit 3: always two groups
     if (kFused && split) {
         if (staged)
             return launch_tile_kernel_impl<kDoRow, kDoCol, kColSum, true, kFused>(x, cr, sr, ct, sc, rows, cols, tiles_c, tiles, rule,
