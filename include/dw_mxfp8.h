@@ -103,7 +103,8 @@ int dw_mxfp8_quantize_rows_batch(int count, const void *const *x_bf16, void *con
  * written through a shared-memory staging buffer, whole 128-byte row segments per store (the default); 1 = straight from
  * registers, 32 bytes per thread and output row (as fast or slightly faster on some GPUs while the output rows are less than
  * 1 MiB apart, half the rate beyond).  Bit 2 set: the fused both-forms kernel always runs its row and column pass one after
- * the other in 256 threads instead of side by side in two groups of 256 on large inputs; bit 3 set: always side by side.
+ * the other in 256 threads instead of side by side in two groups of 256 on large inputs; bit 3 set: always side by side;
+ * bit 4 set: the column-wise kernel always with two tile buffers per thread block (three are used up to 2^28 elements).
  * Same bytes in every setting.  For
  * measurements; the reference has no column-wise kernel (csrc/mxfp8_quantization.cu:216-226 is empty). */
 int dw_mxfp8_quantize_set_tuning(int word);

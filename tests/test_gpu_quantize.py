@@ -99,8 +99,29 @@ def test_staged_transposed_write_out_gives_the_same_bytes(nv, shape, one_group):
                 assert torch.equal(u.view(torch.uint8) if u.element_size() == 1 else u, v.view(torch.uint8) if v.element_size() == 1 else v)
     finally:
         assert L.dw_mxfp8_quantize_set_tuning(0) == 0
-    assert L.dw_mxfp8_quantize_set_tuning(3) == -1 and L.dw_mxfp8_quantize_set_tuning(16) == -1 and L.dw_mxfp8_quantize_set_tuning(12) == -1
+    assert L.dw_mxfp8_quantize_set_tuning(3) == -1 and L.dw_mxfp8_quantize_set_tuning(32) == -1 and L.dw_mxfp8_quantize_set_tuning(12) == -1
     assert L.dw_mxfp8_quantize_set_tuning(4) == 0 and L.dw_mxfp8_quantize_set_tuning(0) == 0
+
+
+@pytest.mark.parametrize("shape", [(128, 128), (4096, 1024), (96, 160), (8192, 3072), (2048, 14336 + 32)])
+def test_column_kernel_with_two_and_three_tile_buffers_gives_the_same_bytes(nv, shape):
+    """The column-wise kernel keeps two tiles in flight (three tile buffers, the default up to 2^28 elements) or one (two
+    buffers, tuning bit 4): the same bytes, equal to the C restatement; with more tiles than thread blocks, so that the
+    ring of buffers wraps several times, and with a ragged last tile."""
+    g = torch.Generator("cpu").manual_seed(shape[0] + shape[1])
+    x = torch.randn(shape, generator=g)
+    x[torch.rand(shape, generator=g) < 0.01] *= 50
+    x = x.bfloat16().cuda()
+    L = nv.load()
+    et, ets = c.quantize_colwise(bits_of(x), 0, True)
+    exp_ts = o.sf_flat_to_tiled(ets)
+    try:
+        for word in (0, 16):
+            assert L.dw_mxfp8_quantize_set_tuning(word) == 0
+            gc, gs = nv.quantize(x, nv.DIR_COL_T, 0, nv.SF_TILED)
+            assert np.array_equal(host(gc), et) and np.array_equal(host(gs).reshape(exp_ts.shape), exp_ts)
+    finally:
+        assert L.dw_mxfp8_quantize_set_tuning(0) == 0
 
 
 def test_every_bf16_pattern(nv):
