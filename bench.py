@@ -1341,11 +1341,58 @@ def main():
                                "gather_bytes_per_rank_per_step": int(sum(M_TOKENS * l["n"] * 2 * (world - 1) for l in layers)),
                                "note": "each GEMM's output shard all-gathered (NCCL all_gather_into_tensor on its own stream, "
                                        "overlapping the next layer's GEMM); without the gather: `value`"}
-            for l in layers:
-                del l["gathered"]
             nv.check_status(dev)
         except Exception as e:
             with_gather = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
+        # ---- the same gather by the copy engines (deepwell_b200.exchange.ColumnGather): every rank copies its shard into its
+        #      block of the rank-major [world, M, n_local] result on every rank (plain copies, which run while the next GEMM
+        #      holds the SMs), or into columns [n0, n1) of the row-major [M, N] result (pitched copies)
+        if with_gather is not None and "error" not in with_gather:
+            from deepwell_b200.exchange import ColumnGather
+            own_y = [l["y"] for l in layers]
+            for key, layout in (("copy_engines", "blocked"), ("copy_engines_row_major", "row_major")):
+                try:
+                    cg = ColumnGather([(M_TOKENS, l["n"] * world) for l in layers], device=dev, layout=layout)
+                    for i, l in enumerate(layers):
+                        l["y"] = cg.shard(i)               # the GEMMs write straight into the buffers the copies read
+                        l["cg_index"] = i
+                        l.pop("gather_done", None)
+
+                    def push_after(l):
+                        l["gather_done"] = cg.push(l["cg_index"])
+
+                    for _ in range(2):
+                        step(False, push_after)
+                    cg.fence()
+                    c_ms, _ = timed_steps(args.steps, False, push_after, finish=cg.fence)
+                    c_step = c_ms / args.steps
+                    # parity: what arrived against the NCCL all-gather of the same shards
+                    same = True
+                    for i, l in enumerate(layers):
+                        dist.all_gather_into_tensor(l["gathered"].view(world * M_TOKENS, l["n"]), l["y"])
+                        full = cg.full(i)
+                        for r in range(world):
+                            got = full[r] if layout == "blocked" else full[:, r * l["n"]:(r + 1) * l["n"]]
+                            same = same and bool(torch.equal(got, l["gathered"][r]))
+                    flag = torch.tensor([1 if same else 0], device=dev, dtype=torch.int32)
+                    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+                    with_gather[key] = {
+                        "value": total_flops() / (c_step * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": c_step,
+                        "layout": "[world, M, n_local]" if layout == "blocked" else "[M, N]", "how": cg.how,
+                        "parity_vs_nccl_all_gather": "ok" if int(flag.item()) == 1 else "MISMATCH"}
+                    del cg
+                except Exception as e:
+                    with_gather[key] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
+                for l, y in zip(layers, own_y):
+                    l["y"] = y
+                    l.pop("gather_done", None)
+            with_gather["copy_engines_note"] = (
+                "each rank copies its shard into every rank's result with device-to-device copies on the copy engines over NVLink "
+                "(plain copies for the rank-major layout, replayed as one CUDA graph per layer; pitched copies for the row-major "
+                "one) behind each GEMM; one 4-byte all-reduce at the end of the timed region as fence")
+        for l in layers:
+            l.pop("gathered", None)
+            l.pop("gather_done", None)
 
     # ---- end to end through the public API with host buffers ----
     e2e = None

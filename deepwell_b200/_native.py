@@ -42,6 +42,7 @@ ABI_SYMBOLS = (
     "dw_mxfp8_update_amax_history", "dw_mxfp8_gemm_planned", "dw_mxfp8_gemm_workspace_planned",
     "dw_mxfp8_selftest_bounded_wait", "dw_mxfp8_debug_fake_device", "dw_mxfp8_debug_counter",
     "dw_mxfp8_quantize_set_tuning", "dw_mxfp8_quantize_ex", "dw_mxfp8_quantize_rows_batch",
+    "dw_mxfp8_copy_2d_async",
 )
 
 _lib = None
@@ -77,6 +78,7 @@ def load() -> ctypes.CDLL:
     L.dw_mxfp8_quantize_ex.argtypes = [p, p, p, i64, i64, i32, i32, i32, i32, p]
     L.dw_mxfp8_quantize_rows_batch.argtypes = [i32, ctypes.POINTER(p), ctypes.POINTER(p), ctypes.POINTER(p),
                                                ctypes.POINTER(i64), ctypes.POINTER(i64), i32, i32, i32, p]
+    L.dw_mxfp8_copy_2d_async.argtypes = [p, sz, p, sz, sz, sz, p]
     L.dw_mxfp8_quantize_both.argtypes = [p, p, p, p, p, i64, i64, i32, i32, p]
     L.dw_mxfp8_dequantize.argtypes = [p, p, p, i64, i64, i32, p]
     L.dw_mxfp8_update_amax_history.argtypes = [p, p, i32, i64, p]
@@ -160,6 +162,14 @@ def quantize_into(x: torch.Tensor, codes: torch.Tensor, scales: torch.Tensor, di
     with torch.cuda.device(x.device):
         check(load().dw_mxfp8_quantize(x.data_ptr(), codes.data_ptr(), scales.data_ptr(), rows, cols, direction, rule, layout,
                                        _stream(x.device)), "dw_mxfp8_quantize")
+
+
+def copy_2d_async(dst_ptr: int, dst_pitch: int, src_ptr: int, src_pitch: int, width_bytes: int, height: int, device) -> None:
+    """dw_mxfp8_copy_2d_async on the current stream of `device`: `height` rows of `width_bytes` bytes between two device
+    addresses with their own pitches (either may be a peer GPU's mapped memory); executed by a copy engine."""
+    with torch.cuda.device(device):
+        check(load().dw_mxfp8_copy_2d_async(dst_ptr, dst_pitch, src_ptr, src_pitch, width_bytes, height, _stream(device)),
+              "dw_mxfp8_copy_2d_async")
 
 
 QUANT_BATCH_MAX = 8

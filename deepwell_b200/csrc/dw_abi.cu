@@ -54,6 +54,18 @@ extern "C" DW_API int dw_mxfp8_device_supported(int device) {
     return major == 10 ? 1 : 0;
 }
 
+extern "C" DW_API int dw_mxfp8_copy_2d_async(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes,
+                                       size_t height, void* stream) {
+    if (width_bytes == 0 || height == 0) return DW_OK;
+    if (!dst || !src || dst_pitch < width_bytes || src_pitch < width_bytes) return DW_ERR_BAD_ARG;
+    if (cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, height, cudaMemcpyDeviceToDevice,
+                          static_cast<cudaStream_t>(stream)) != cudaSuccess) {
+        cudaGetLastError();
+        return DW_ERR_LAUNCH;
+    }
+    return DW_OK;
+}
+
 extern "C" DW_API int dw_mxfp8_debug_fake_device(int cc_major, int sms) {
     dw::g_fake_sms.store(sms, std::memory_order_relaxed);
     dw::g_fake_cc.store(cc_major, std::memory_order_relaxed);

@@ -236,3 +236,113 @@ class QuantizedRowExchange:
         finished the work it issued before its own fence (so the other slot may be refilled)."""
         torch.cuda.current_stream(self.device).wait_event(self._pushed[slot])
         dist.all_reduce(self._token, group=self.group)
+
+class ColumnGather:
+    """The column shards Y_r = Y[:, n0_r:n1_r] that the ranks of an N-sharded layer compute, brought to every rank by the
+    copy engines instead of an NCCL all-gather, whose kernels wait for the GEMM's thread blocks like any other kernel.
+
+    layout "blocked" (default): rank-major blocks [world, M, n_local], the layout an all-gather delivers.  A shard is one
+    contiguous piece, so each destination takes one plain device-to-device copy: copy-engine traffic over NVLink at
+    ~750 GB/s that runs while the next layer's GEMM holds the SMs.  The GEMM writes its shard straight into block `rank`
+    of this rank's buffer; the copies of one output are recorded once as a CUDA graph and replayed.
+    layout "row_major": the full row-major [M, N]; every destination takes one pitched copy (dw_mxfp8_copy_2d_async).
+    Measured on B200, pitched copies with rows of 4-28 KB do not overlap the GEMMs and are no faster than the NCCL
+    gather followed by a strided pass, so this form only saves that pass.
+
+        cg = ColumnGather([(M, N0), (M, N1), ...], group)          # once
+        y_shard = cg.shard(i)                                       # [M, n_local] bf16: the GEMM's output buffer
+        ... GEMM of layer i writes y_shard ...
+        done = cg.push(i)                                           # asynchronous: copy stream; shard(i) is free after `done`
+        cg.fence()                                                  # all shards of everything pushed so far have landed
+        y_all = cg.full(i)                                          # [world, M, n_local] (blocked) or [M, N] (row_major)
+    """
+
+    def __init__(self, shapes: Sequence[Tuple[int, int]], group=None, device: Optional[torch.device] = None,
+                 layout: str = "blocked"):
+        if not dist.is_initialized():
+            raise RuntimeError("torch.distributed is not initialised")
+        if layout not in ("blocked", "row_major"):
+            raise ValueError("layout must be 'blocked' or 'row_major'")
+        self.group, self.layout = group, layout
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.shapes = [(int(m), int(n)) for m, n in shapes]
+        for m, n in self.shapes:
+            if n % (8 * self.world):
+                raise ValueError(f"output {m} x {n}: N must be a multiple of 8 x world so that every shard's rows are 16-byte pieces")
+        # this rank's buffer: the gathered outputs one after the other; row_major keeps the shards (what the GEMMs
+        # write) behind them, blocked has them inside (block `rank` of each output)
+        self._full_off, self._shard_off, off = [], [], 0
+        for m, n in self.shapes:
+            self._full_off.append(off)
+            off += -(-m * n * 2 // 256) * 256
+        for i, (m, n) in enumerate(self.shapes):
+            if layout == "blocked":
+                self._shard_off.append(self._full_off[i] + self.rank * m * (n // self.world) * 2)
+            else:
+                self._shard_off.append(off)
+                off += -(-m * (n // self.world) * 2 // 256) * 256
+        self.views, self.how = _map_on_all_ranks(off, self.device, group)
+        self.copy_stream = torch.cuda.Stream(self.device)
+        self._ready = [torch.cuda.Event() for _ in self.shapes]
+        self._done = [torch.cuda.Event() for _ in self.shapes]      # the pushes of output i have been executed
+        self._pushed = torch.cuda.Event()
+        self._token = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.bytes_pushed = [m * (n // self.world) * 2 * (self.world - 1) for m, n in self.shapes]
+        self._graphs = None
+        if layout == "blocked" and self.world > 1:
+            torch.cuda.synchronize(self.device)
+            self._graphs = []
+            for i in range(len(self.shapes)):
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=self.copy_stream, capture_error_mode="thread_local"):
+                    self._issue(i)
+                self._graphs.append(graph)
+
+    def _bytes(self, i: int) -> int:
+        m, n = self.shapes[i]
+        return m * (n // self.world) * 2
+
+    def shard(self, i: int) -> torch.Tensor:
+        m, n = self.shapes[i]
+        return self.views[self.rank][self._shard_off[i]: self._shard_off[i] + self._bytes(i)].view(torch.bfloat16).view(m, n // self.world)
+
+    def full(self, i: int) -> torch.Tensor:
+        m, n = self.shapes[i]
+        flat = self.views[self.rank][self._full_off[i]: self._full_off[i] + m * n * 2].view(torch.bfloat16)
+        return flat.view(self.world, m, n // self.world) if self.layout == "blocked" else flat.view(m, n)
+
+    def _issue(self, i: int) -> None:
+        m, n = self.shapes[i]
+        nl, nbytes = n // self.world, self._bytes(i)
+        src = self.views[self.rank][self._shard_off[i]: self._shard_off[i] + nbytes]
+        first = 1 if self.layout == "blocked" else 0             # blocked: the shard already sits in this rank's own block
+        for step in range(first, self.world):                    # every rank starts with a different destination
+            peer = (self.rank + step) % self.world
+            if self.layout == "blocked":
+                at = self._full_off[i] + self.rank * nbytes
+                self.views[peer][at: at + nbytes].copy_(src, non_blocking=True)
+            else:
+                dst = self.views[peer].data_ptr() + self._full_off[i] + self.rank * nl * 2
+                nv.copy_2d_async(dst, n * 2, src.data_ptr(), nl * 2, nl * 2, m, self.device)
+
+    def push(self, i: int) -> "torch.cuda.Event":
+        """Behind the work issued so far on the current stream (the GEMM that writes shard(i)): this rank's shard into its
+        place in output i on every rank.  Returns the event that follows the copies: shard(i) may be overwritten once it
+        has happened."""
+        self._ready[i].record()
+        self.copy_stream.wait_event(self._ready[i])
+        with torch.cuda.stream(self.copy_stream):
+            if self._graphs is not None:
+                self._graphs[i].replay()
+            else:
+                self._issue(i)
+            self._done[i].record()
+            self._pushed.record()
+        return self._done[i]
+
+    def fence(self) -> None:
+        """Stream-wise: after this, every rank's shards of all outputs pushed so far are in this rank's buffers (and this
+        rank's in every other's).  One 4-byte all-reduce."""
+        torch.cuda.current_stream(self.device).wait_event(self._pushed)
+        dist.all_reduce(self._token, group=self.group)

@@ -59,6 +59,14 @@ int         dw_mxfp8_abi_version(void);
 int         dw_mxfp8_device_supported(int device);      /* 1 if compute capability 10.x */
 const char *dw_mxfp8_error_string(int code);
 
+/* Pitched device-to-device copy on `stream`: row r (r < height) of width_bytes bytes from src + r * src_pitch to
+ * dst + r * dst_pitch.  Either side may be another GPU's memory mapped into this process (symmetric memory): the copy is
+ * executed by a copy engine, so it proceeds while kernels occupy every SM.  Used to place a rank's column shard
+ * Y[:, n0:n1] (contiguous [M, n_local] as the GEMM writes it) into columns [n0, n1) of the row-major [M, N] result on every
+ * rank.  The reference has no multi-GPU code (src/deepwell/__init__.py:45-83 is a placeholder). */
+int dw_mxfp8_copy_2d_async(void *dst, size_t dst_pitch, const void *src, size_t src_pitch, size_t width_bytes, size_t height,
+                     void *stream);
+
 /* Bytes of the scale buffer for an operand with `rows` rows and `k` elements along its
  * scaled dimension.  Replaces get_mxfp8_scale_layout_info, csrc/mxfp8_quantization.cu:287-298. */
 size_t dw_mxfp8_scale_bytes(int64_t rows, int64_t k, int scale_layout);
