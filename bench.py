@@ -1107,8 +1107,10 @@ def main():
         step_no[0] += 1
         return n_launch
 
+    exchange_on = [True]       # the legs that gather every output keep NVLink for Y: there every rank quantises all of X itself
+
     def step(record: bool, after_gemm=None, force_separate=False):
-        if exchange is not None and not force_separate:
+        if exchange is not None and exchange_on[0] and not force_separate:
             return exchange_step(record, after_gemm)
         if overlap and not force_separate:
             return overlapped_step(record, after_gemm)
@@ -1331,6 +1333,9 @@ def main():
                     l["gather_done"].record(cstream)
 
             even = all(n % (32 * world) == 0 for _, _, n in LAYERS)
+            exchange_on[0] = False
+            if overlap:
+                quantise_operands(layers[0], 0)       # the pipeline's first operands (the exchange step does not leave them)
             if even:
                 for _ in range(2):
                     step(False, gather_after)
@@ -1340,7 +1345,8 @@ def main():
                 with_gather = {"value": total_flops() / (g_step * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": g_step,
                                "gather_bytes_per_rank_per_step": int(sum(M_TOKENS * l["n"] * 2 * (world - 1) for l in layers)),
                                "note": "each GEMM's output shard all-gathered (NCCL all_gather_into_tensor on its own stream, "
-                                       "overlapping the next layer's GEMM); without the gather: `value`"}
+                                       "overlapping the next layer's GEMM); every rank quantises all of X itself in this leg "
+                                       "(NVLink carries Y only); without the gather: `value`"}
             nv.check_status(dev)
         except Exception as e:
             with_gather = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
@@ -1352,14 +1358,21 @@ def main():
             own_y = [l["y"] for l in layers]
             for key, layout in (("copy_engines", "blocked"), ("copy_engines_row_major", "row_major")):
                 try:
-                    cg = ColumnGather([(M_TOKENS, l["n"] * world) for l in layers], device=dev, layout=layout)
+                    # two slots: a layer's GEMM of step s + 1 fills one while the copies of step s still read the other
+                    cg = ColumnGather([(M_TOKENS, l["n"] * world) for l in layers], device=dev, layout=layout, slots=2)
+                    cg_done = {}
                     for i, l in enumerate(layers):
-                        l["y"] = cg.shard(i)               # the GEMMs write straight into the buffers the copies read
-                        l["cg_index"] = i
+                        l["cg_index"], l["cg_slot"] = i, 0
+                        l["y"] = cg.shard(i, 0)            # the GEMMs write straight into the buffers the copies read
                         l.pop("gather_done", None)
 
                     def push_after(l):
-                        l["gather_done"] = cg.push(l["cg_index"])
+                        i, slot = l["cg_index"], l["cg_slot"]
+                        cg_done[(i, slot)] = cg.push(i, slot)
+                        l["cg_slot"] = slot ^ 1
+                        l["y"] = cg.shard(i, slot ^ 1)      # the next step's GEMM of this layer writes the other slot ...
+                        if (i, slot ^ 1) in cg_done:
+                            l["gather_done"] = cg_done[(i, slot ^ 1)]       # ... once that slot's copies have been made
 
                     for _ in range(2):
                         step(False, push_after)
@@ -1369,8 +1382,8 @@ def main():
                     # parity: what arrived against the NCCL all-gather of the same shards
                     same = True
                     for i, l in enumerate(layers):
-                        dist.all_gather_into_tensor(l["gathered"].view(world * M_TOKENS, l["n"]), l["y"])
-                        full = cg.full(i)
+                        dist.all_gather_into_tensor(l["gathered"].view(world * M_TOKENS, l["n"]), cg.shard(i, l["cg_slot"] ^ 1))
+                        full = cg.full(i, l["cg_slot"] ^ 1)     # the slot the last step filled
                         for r in range(world):
                             got = full[r] if layout == "blocked" else full[:, r * l["n"]:(r + 1) * l["n"]]
                             same = same and bool(torch.equal(got, l["gathered"][r]))
@@ -1393,6 +1406,9 @@ def main():
         for l in layers:
             l.pop("gathered", None)
             l.pop("gather_done", None)
+        exchange_on[0] = True
+        if exchange is not None:
+            prime_exchange()
 
     # ---- end to end through the public API with host buffers ----
     e2e = None
