@@ -6,10 +6,14 @@
 Workload: the four Llama-3-8B linear shapes at M = 16384 tokens (QKV 4096->6144, O 4096->4096,
 fused gate+up 4096->28672, down 14336->4096), bf16 activations N(0,1), weights N(0,0.02),
 synthetic and seeded.  One step = for each of the four layers: quantise X row-wise, quantise the
-weight (shard) row-wise, run the block-scaled GEMM.  The layers are independent problems, so the
-quantisation of layer i+1 runs on a second stream under the GEMM of layer i (--serial: one stream).
-With N GPUs every weight is sharded along its output dimension across the ranks (X is replicated;
-no collective on the data path), so the total work is fixed: strong scaling.
+weight (shard) row-wise, run the block-scaled GEMM.  The layers are independent problems: each GEMM is
+issued before the next layer's quantisers, which may start while it runs (DW_QUANT_OVERLAP_PREVIOUS;
+--serial: every launch after the previous one has finished).
+With N GPUs every weight is sharded along its output dimension across the ranks and X is replicated, so
+the total work is fixed: strong scaling.  The ranks share the quantisation of X (each quantises 1/N of
+the rows and copies its slice into every peer's operand buffer over NVLink with the copy engines, under the
+GEMMs: deepwell_b200/exchange.py; --no-exchange: every rank quantises all of X itself, no data-path
+collective); a rank's slices and weight shards are quantised by one launch (dw_mxfp8_quantize_rows_batch).
 
 Prints ONE JSON line (rank 0).  Keys beyond the basic contract:
   value              whole-job TFLOP/s with inputs resident in HBM (CUDA events, max over ranks)
@@ -26,7 +30,10 @@ Prints ONE JSON line (rank 0).  Keys beyond the basic contract:
   gpt2_mlp, swiglu_mlp, decoder_step   secondary workloads (GPT-2-small MLP forward+backward; the Llama-3-8B gated MLP
                      with and without the SwiGLU epilogue; the end-to-end optimize() training step of a 12-layer
                      decoder), each beside the same layers in bf16 (N = 1 only)
-  with_gather, sharded     N > 1: the step with every layer's output all-gathered over NVLink, and a parity check of
+  exchange           N > 1: how the quantisation of X was shared (rows per layer, bytes pushed per step, the budgets
+                     tried) and `parity`: the assembled operands against the rank's own quantisation of all of X
+  with_gather, sharded     N > 1: the step with every layer's output all-gathered over NVLink (by NCCL, and by the copy
+                     engines: `copy_engines`, checked against the NCCL result), and a parity check of
                      ColumnParallelDWLinear / RowParallelDWLinear under NCCL against the unsharded layer
   cpu_baseline       the CPU restatement of the same path on the host cores (rank 0, N = 1)
 
@@ -902,10 +909,10 @@ def main():
     ap.add_argument("--two-streams", action="store_true", help="the next layer's quantisers on a second, lower-priority stream")
     ap.add_argument("--exchange-push", choices=["graph", "stream"], default="graph",
                     help="N > 1: the peer copies of the shared quantisation as one replayed CUDA graph per step (default) or issued one by one")
-    ap.add_argument("--exchange-budget", default="0.8,1.1,1.4,all",
+    ap.add_argument("--exchange-budget", default="0,0.4,0.8,1.1,all",
                     help="N > 1: share as many rows of X as a rank can receive (at 700 GB/s) in this multiple of the step's GEMM "
-                         "time ('all' = every row); several values, comma-separated: each is tried for a few steps before the "
-                         "timed region and the fastest kept")
+                         "time ('all' = every row, 0 = none: every rank quantises all of X itself, in one launch); several "
+                         "values, comma-separated: each is tried for a few steps before the timed region and the fastest kept")
     ap.add_argument("--quant-batch-pairs", action="store_true",
                     help="the activation and the weight shard of a layer quantised by one launch (dw_mxfp8_quantize_rows_batch)")
     ap.add_argument("--no-quant-batch", action="store_true",
@@ -1108,6 +1115,7 @@ def main():
         return n_launch
 
     exchange_on = [True]       # the legs that gather every output keep NVLink for Y: there every rank quantises all of X itself
+    exchange_used = [True]     # False: the candidates were measured and the plain step (nothing shared, separate launches) won
 
     def step(record: bool, after_gemm=None, force_separate=False):
         if exchange is not None and exchange_on[0] and not force_separate:
@@ -1190,9 +1198,25 @@ def main():
             best = min(tried, key=lambda t: t[0])
             exchange.set_shared_rows(best[2])
             exchange_info["tried_ms_per_step"] = {("all" if f > 1e6 else f"{f:g} x GEMM time"): round(t, 4) for t, f, _ in tried}
-        exchange_info["shared_rows"] = list(exchange.shared_rows)
-        exchange_info["bytes_pushed_per_rank_per_step"] = int(exchange.bytes_pushed_per_call)
-        prime_exchange()
+            # and the step without the exchange object: every rank quantises all of X itself, one launch per operand,
+            # each behind the previous layer's GEMM
+            exchange_on[0] = False
+            quantise_operands(layers[0], 0)
+            for _ in range(2):
+                step(False)
+            t_ms, _ = timed_steps(6, False)
+            exchange_info["tried_ms_per_step"]["no exchange, separate launches"] = round(t_ms / 6, 4)
+            exchange_used[0] = best[0] <= t_ms / 6
+            exchange_on[0] = exchange_used[0]
+        exchange_info["used"] = exchange_used[0]
+        if exchange_used[0]:
+            exchange_info["shared_rows"] = list(exchange.shared_rows)
+            exchange_info["bytes_pushed_per_rank_per_step"] = int(exchange.bytes_pushed_per_call)
+            prime_exchange()
+        else:
+            exchange_info["shared_rows"] = [0] * len(layers)
+            exchange_info["bytes_pushed_per_rank_per_step"] = 0
+            quantise_operands(layers[0], 0)
     for _ in range(warmup):
         step(False)
     nv.check_status(dev)
@@ -1204,7 +1228,7 @@ def main():
     nv.check_status(dev)
     ms_per_step = elapsed_ms / args.steps
     value = total_flops() / (ms_per_step * 1e-3) / 1e12
-    if exchange is not None:
+    if exchange is not None and exchange_used[0]:
         # the operands the exchange assembled (this rank's slice + the peers') against this rank's own quantisation of the whole X
         same = True
         for i, j in ex_index.items():
@@ -1406,9 +1430,11 @@ def main():
         for l in layers:
             l.pop("gathered", None)
             l.pop("gather_done", None)
-        exchange_on[0] = True
-        if exchange is not None:
+        exchange_on[0] = exchange_used[0]
+        if exchange is not None and exchange_used[0]:
             prime_exchange()
+        elif overlap:
+            quantise_operands(layers[0], 0)
 
     # ---- end to end through the public API with host buffers ----
     e2e = None
@@ -1514,7 +1540,7 @@ def main():
                 "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "mxfp8(e4m3+e8m0), fp32 accumulate, bf16 out", "data": "synthetic",
                 "config": {"workload": WORKLOAD, "M": M_TOKENS, "layers": {n: [k, nn] for n, k, nn in LAYERS},
-                           "parallelism": f"N-sharded x{world}, X replicated, no data-path collective" if exchange is None else
+                           "parallelism": f"N-sharded x{world}, X replicated, no data-path collective" if (exchange is None or not exchange_used[0]) else
                                           f"N-sharded x{world}, X replicated; the quantisation of X is shared (rows {exchange_info['shared_rows']} of "
                                           f"{exchange_info['layers']}): each rank quantises 1/N of those rows and copies its slice into every peer's "
                                           "operand buffer over NVLink (copy engines, under the GEMMs), the other rows every rank quantises itself; "

@@ -225,6 +225,8 @@ class QuantizedRowExchange:
             for x, codes, scales in jobs:
                 nv.quantize_into(x, codes, scales, nv.DIR_ROW, self.rule, nv.SF_TILED)
             launches = len(jobs)
+        if self.bytes_pushed_per_call == 0:
+            return launches
         self._quantised[slot].record()
         self.copy_stream.wait_event(self._quantised[slot])
         with torch.cuda.stream(self.copy_stream):
@@ -238,6 +240,8 @@ class QuantizedRowExchange:
     def fence(self, slot: int) -> None:
         """After this returns (stream-wise), every rank's slices of `slot` are in this rank's buffer, and every rank has
         finished the work it issued before its own fence (so the other slot may be refilled)."""
+        if self.bytes_pushed_per_call == 0:          # nothing is shared: every rank filled its own buffer, no rank waits for another
+            return
         torch.cuda.current_stream(self.device).wait_event(self._pushed[slot])
         dist.all_reduce(self._token, group=self.group)
 
