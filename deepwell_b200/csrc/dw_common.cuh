@@ -16,6 +16,36 @@ constexpr int kBlock = 32;  // elements per scaling block
 // host side: the current device
 // ------------------------------------------------------------------------------------------
 constexpr int kMaxDevices = 64;
+// Programmatic dependent launch (griddepcontrol).  A kernel launched with cudaLaunchAttributeProgrammaticStreamSerialization
+// may be made resident while the kernel before it on the stream is still running; pdl_wait() then blocks until that
+// kernel has completed and its writes are visible, so everything before it in the kernel (parameter reads, barrier and
+// tensor-memory set-up) overlaps the predecessor's tail, and nothing after it can see the predecessor half done.
+// pdl_launch_dependents() lets the NEXT kernel of the stream become resident early in the same way.  Both are no-ops in
+// a kernel that was launched without the attribute.  A kernel that calls pdl_launch_dependents() must call pdl_wait()
+// first: the successor only waits for THIS kernel, and that covers the kernels before it only if this one waited.
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
+
+// Host side: launch `kernel` allowing it to become resident while its predecessor on `st` still runs (see above).
+#ifdef __CUDACC__
+template <typename... KArgs>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, KArgs... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+#endif
+
 struct DeviceInfo { int device; int sms; int cc_major; };
 // Properties of the CURRENT device (cached per device index, so one process may drive several GPUs).
 // DW_OK; DW_ERR_ARCH if it is not compute capability 10.x (*out is still filled); DW_ERR_LAUNCH if no device answers.

@@ -183,6 +183,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     // DW_QUANT_OVERLAP_PREVIOUS) may start now and take the SMs this grid does not occupy.  Without such a launch
     // behind it the instruction does nothing.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // This kernel itself is launched the same way: everything above (barriers, tensor memory, tensor-map prefetch) may have
+    // run while the kernel before it on the stream (usually the quantiser of its operands) was finishing; from here on
+    // that kernel has completed and its writes are visible.
+    pdl_wait();
 
     const uint32_t num_workers = gridDim.x / kCtas, worker = blockIdx.x / kCtas;
     const uint32_t num_units = p.num_tiles * p.splits;
@@ -878,11 +882,13 @@ static int launch_gemm(const void* a, const void* a_sf, const void* b, const voi
     cfg.blockDim = dim3(kGemmThreads);
     cfg.dynamicSmemBytes = Cfg::kSmemBytes;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = kCtas; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;      // see pdl_wait() in the kernel
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     if (cudaLaunchKernelEx(&cfg, mx_gemm_kernel<BN, kCtas, kGroup>, tm_a, tm_b, tm_sfa, tm_sfb, tm_d, p) != cudaSuccess) {
         cudaGetLastError();
         return DW_ERR_LAUNCH;

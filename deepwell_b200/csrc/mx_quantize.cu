@@ -33,7 +33,10 @@ namespace dw {
 template <bool kWide>  // kWide: 32-byte aligned input -> one 256-bit load per chunk
 __global__ void __launch_bounds__(256)
 mx_quant_row_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes, uint8_t* __restrict__ scales,
-                    uint32_t total_chunks, FastDiv cpr, int rule, int layout, int packed_sf) {
+                    uint32_t total_chunks, FastDiv cpr, int rule, int layout, int packed_sf, int pdl) {
+    // pdl: wait for the kernel before this one on the stream, then let the next one become resident (dw_common.cuh);
+    // 0: DW_QUANT_OVERLAP_PREVIOUS, this kernel runs beside its predecessor and must not release its successor early
+    if (pdl) { pdl_wait(); pdl_launch_dependents(); }
     const uint32_t chunks_per_row = cpr.div;
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t T = gridDim.x * blockDim.x;
@@ -111,7 +114,8 @@ mx_quant_row_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes,
 // runs at the copy bandwidth (16384 x 14336: 107 us against 130 us for the kernel above, 6.6 against 5.4 TB/s).
 template <int kDeep>
 __global__ void __maxnreg__(88)      // 128 threads x 88 registers
-mx_quant_row_bg_kernel(const RowQuantJob job) {
+mx_quant_row_bg_kernel(const RowQuantJob job, int pdl) {
+    if (pdl) { pdl_wait(); pdl_launch_dependents(); }
     quant_row_slabs<kDeep>(job, blockIdx.x, gridDim.x, threadIdx.x);
 }
 
@@ -123,10 +127,12 @@ struct RowQuantBatch {
     RowQuantJob job[kMaxRowQuantJobs];
     uint32_t first_slab[kMaxRowQuantJobs + 1];
     int count;
+    int pdl;
 };
 template <int kDeep>
 __global__ void __maxnreg__(88)
 mx_quant_row_batch_kernel(const __grid_constant__ RowQuantBatch b) {
+    if (b.pdl) { pdl_wait(); pdl_launch_dependents(); }
     int j = 0;
     while (j + 1 < b.count && blockIdx.x >= b.first_slab[j + 1]) ++j;
     const RowQuantJob job = b.job[j];
@@ -176,6 +182,8 @@ mx_quant_tile_kernel(const uint16_t* __restrict__ x, uint8_t* __restrict__ codes
                      uint8_t* __restrict__ codes_col_t, uint8_t* __restrict__ scales_col, int64_t rows, int64_t cols,
                      uint32_t tiles_c, uint32_t num_tiles, int rule, int layout, float* __restrict__ colsum_partial = nullptr) {
     static_assert(!kSplit || (kDoRow && kDoCol), "the split form is for the fused both-forms kernel");
+    pdl_wait();                      // the kernel before this one on the stream has completed (its output is this one's input)
+    pdl_launch_dependents();         // the next one may become resident as SMs free up; it waits for this one in turn
     // Persistent CTA, two tile buffers: the 16-byte cp.async copies of the next tile are in flight
     // while this tile is quantised, so the SM always has loads outstanding.
     extern __shared__ __align__(16) uint8_t tile_smem[];
@@ -545,32 +553,28 @@ static int quantize_row_fast(const uint16_t* x, uint8_t* codes, uint8_t* scales,
         RowQuantJob job;
         if (!make_row_quant_job(&job, x, codes, scales, rows, cols, rule, layout)) return DW_ERR_BAD_ARG;
         const int64_t slabs = (total_chunks + 128 * kDeep - 1) / (128 * kDeep);
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(static_cast<unsigned>(std::min<int64_t>(slabs, 1ll << 30)));
-        cfg.blockDim = dim3(kRowSlabThreads);
-        cfg.stream = st;
-        cudaLaunchAttribute attr[1];
-        if (flags & DW_QUANT_OVERLAP_PREVIOUS) {
-            // may start once the preceding kernel of this stream has released its dependents (the GEMM does so as soon
-            // as its CTAs are resident) instead of when it has finished; this kernel reads nothing that kernel writes
-            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-            attr[0].val.programmaticStreamSerializationAllowed = 1;
-            cfg.attrs = attr;
-            cfg.numAttrs = 1;
-        }
-        if (cudaLaunchKernelEx(&cfg, mx_quant_row_bg_kernel<kDeep>, job) != cudaSuccess) {
+        // DW_QUANT_OVERLAP_PREVIOUS: the kernel does not wait for its predecessor (it may start once that kernel has
+        // released its dependents, which the GEMM does as soon as its CTAs are resident; it reads nothing that kernel
+        // writes).  Otherwise it becomes resident early, waits for the predecessor to complete and only then touches memory.
+        const int pdl = (flags & DW_QUANT_OVERLAP_PREVIOUS) ? 0 : 1;
+        if (launch_pdl(mx_quant_row_bg_kernel<kDeep>, dim3(static_cast<unsigned>(std::min<int64_t>(slabs, 1ll << 30))),
+                       dim3(kRowSlabThreads), 0, st, job, pdl) != cudaSuccess) {
             cudaGetLastError();
             return DW_ERR_LAUNCH;
         }
         return DW_OK;
     }
-    if (aligned(x, 32))
-        mx_quant_row_kernel<true><<<grid, 256, 0, st>>>(x, codes, scales, static_cast<uint32_t>(total_chunks), cpr, rule,
-                                                        layout, packed);
-    else
-        mx_quant_row_kernel<false><<<grid, 256, 0, st>>>(x, codes, scales, static_cast<uint32_t>(total_chunks), cpr, rule,
-                                                         layout, packed);
-    return launch_status();
+    const int pdl = (flags & DW_QUANT_OVERLAP_PREVIOUS) ? 0 : 1;
+    const cudaError_t rc =
+        aligned(x, 32) ? launch_pdl(mx_quant_row_kernel<true>, dim3(grid), dim3(256), 0, st, x, codes, scales,
+                                    static_cast<uint32_t>(total_chunks), cpr, rule, layout, packed, pdl)
+                       : launch_pdl(mx_quant_row_kernel<false>, dim3(grid), dim3(256), 0, st, x, codes, scales,
+                                    static_cast<uint32_t>(total_chunks), cpr, rule, layout, packed, pdl);
+    if (rc != cudaSuccess) {
+        cudaGetLastError();
+        return DW_ERR_LAUNCH;
+    }
+    return DW_OK;
 }
 
 static std::atomic<int> g_quant_tuning{0};     // dw_mxfp8_quantize_set_tuning
@@ -594,9 +598,13 @@ static int launch_tile_kernel_impl(const uint16_t* x, uint8_t* cr, uint8_t* sr, 
     }
     // 3 CTAs of 256 threads and 67 KB per SM, or 2 CTAs of 512 threads (kSplit)
     const uint32_t grid = std::min<uint32_t>(tiles, static_cast<uint32_t>(di.sms) * ((kSplit || kThree) ? 2u : 3u));
-    mx_quant_tile_kernel<kDoRow, kDoCol, kColSum, kStaged, kSplit, kThree><<<grid, kSplit ? 512 : 256, tile_smem_bytes(kSplit || kThree), st>>>(
-        x, cr, sr, ct, sc, rows, cols, tiles_c, tiles, rule, layout, colsum_partial);
-    return launch_status();
+    if (launch_pdl(mx_quant_tile_kernel<kDoRow, kDoCol, kColSum, kStaged, kSplit, kThree>, dim3(grid), dim3(kSplit ? 512 : 256),
+                   static_cast<size_t>(tile_smem_bytes(kSplit || kThree)), st, x, cr, sr, ct, sc, rows, cols, tiles_c, tiles, rule,
+                   layout, colsum_partial) != cudaSuccess) {
+        cudaGetLastError();
+        return DW_ERR_LAUNCH;
+    }
+    return DW_OK;
 }
 
 // The transposed payload is written out staged (see mx_quant_tile_kernel) unless the tuning word asks for the direct form:
@@ -747,18 +755,9 @@ extern "C" DW_API int dw_mxfp8_quantize_rows_batch(int count, const void* const*
     DeviceInfo di;
     const int drc = current_device(&di);
     if (drc != DW_OK) return drc;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(static_cast<unsigned>(slabs));
-    cfg.blockDim = dim3(kRowSlabThreads);
-    cfg.stream = static_cast<cudaStream_t>(stream);
-    cudaLaunchAttribute attr[1];
-    if (flags & DW_QUANT_OVERLAP_PREVIOUS) {
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-    }
-    if (cudaLaunchKernelEx(&cfg, mx_quant_row_batch_kernel<kDeep>, b) != cudaSuccess) {
+    b.pdl = (flags & DW_QUANT_OVERLAP_PREVIOUS) ? 0 : 1;
+    if (launch_pdl(mx_quant_row_batch_kernel<kDeep>, dim3(static_cast<unsigned>(slabs)), dim3(kRowSlabThreads), 0,
+                   static_cast<cudaStream_t>(stream), b) != cudaSuccess) {
         cudaGetLastError();
         return DW_ERR_LAUNCH;
     }
