@@ -681,6 +681,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 __global__ void __launch_bounds__(256)
 mx_splitk_reduce_kernel(const float* __restrict__ partial, uint16_t* __restrict__ d, const uint16_t* __restrict__ bias,
                         int64_t M, int64_t N, uint32_t splits, float alpha, float beta) {
+    pdl_wait();                      // the GEMM that wrote the partial sums has completed
+    pdl_launch_dependents();
     const int64_t total = M * N, plane = M * N;
     const bool vec = (N % 4) == 0;
     const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x * 4;
@@ -896,8 +898,11 @@ static int launch_gemm(const void* a, const void* a_sf, const void* b, const voi
     if (p.splits > 1) {
         const int64_t quads = (p.M * p.N + 3) / 4;
         const int grid = static_cast<int>(std::min<int64_t>((quads + 255) / 256, static_cast<int64_t>(di.sms) * 8));
-        mx_splitk_reduce_kernel<<<grid, 256, 0, st>>>(p.partial, p.d, p.bias, p.M, p.N, p.splits, p.alpha, p.beta);
-        if (cudaGetLastError() != cudaSuccess) return DW_ERR_LAUNCH;
+        if (launch_pdl(mx_splitk_reduce_kernel, dim3(grid), dim3(256), 0, st, static_cast<const float*>(p.partial), p.d, p.bias,
+                       p.M, p.N, p.splits, p.alpha, p.beta) != cudaSuccess) {
+            cudaGetLastError();
+            return DW_ERR_LAUNCH;
+        }
     }
     return DW_OK;
 }

@@ -804,6 +804,8 @@ extern "C" DW_API int dw_mxfp8_quantize_both(const void* x_bf16, void* codes_row
 __global__ void __launch_bounds__(256)
 mx_colsum_reduce_kernel(const float* __restrict__ partial, int64_t tiles_r, int64_t cols, void* __restrict__ out, int out_bf16) {
     __shared__ float part[8][32];
+    pdl_wait();                      // the quantiser that wrote `partial` has completed
+    pdl_launch_dependents();
     const uint32_t tx = threadIdx.x & 31u, ty = threadIdx.x >> 5;
     const int64_t c = blockIdx.x * 32ll + tx;
     float acc = 0.0f;
@@ -861,9 +863,12 @@ extern "C" DW_API int dw_mxfp8_quantize_both_colsum(const void* x_bf16, void* co
                                                         static_cast<uint32_t>(tiles_r) * tiles_c, scale_rule, scale_layout, di, st,
                                                         static_cast<float*>(workspace));
     if (rc != DW_OK) return rc;
-    mx_colsum_reduce_kernel<<<static_cast<unsigned>((cols + 31) / 32), 256, 0, st>>>(static_cast<const float*>(workspace), tiles_r,
-                                                                                      cols, colsum_out, colsum_is_bf16);
-    return launch_status();
+    if (launch_pdl(mx_colsum_reduce_kernel, dim3(static_cast<unsigned>((cols + 31) / 32)), dim3(256), 0, st,
+                   static_cast<const float*>(workspace), tiles_r, cols, colsum_out, colsum_is_bf16) != cudaSuccess) {
+        cudaGetLastError();
+        return DW_ERR_LAUNCH;
+    }
+    return DW_OK;
 }
 
 extern "C" DW_API int dw_mxfp8_update_amax_history(const void* x_bf16, float* amax_history, int history_len, int64_t num_elements,
