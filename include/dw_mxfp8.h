@@ -11,6 +11,11 @@
  * device that is not compute capability 10.x.  Return value: DW_OK or a negative DW_ERR_* code (the convention of the
  * reference's only C ABI, dw_fmha_bf16_forward, csrc/fmha_bridge_min/fmha_bridge_min.cu:39-46).
  *
+ * Stream order is kept: every kernel launched here behaves as if it started after the work before it on `stream`
+ * had finished.  (The GEMM and the quantisers are launched with programmatic stream serialisation: their thread blocks
+ * may become resident while the preceding kernel is finishing, but they wait for that kernel to complete before they
+ * read or write any memory.  The one exception is asked for explicitly: DW_QUANT_OVERLAP_PREVIOUS.)
+ *
  * Each entry point names the reference interface it replaces (path:line inside the
  * reference project).
  */
