@@ -23,6 +23,9 @@ everywhere and the slot just used may be overwritten.
 What a rank receives per step crosses its NVLink ports at ~750 GB/s; where the GEMMs of a step are shorter than that transfer
 (eight ranks on the Llama-3-8B shapes) only the first `shared_rows[i]` rows of an activation are shared and every rank
 quantises the remaining rows itself, so that the transfer still ends before the step does.
+
+ColumnGather (below) moves the OUTPUT of an N-sharded layer the same way: every rank's column shard into every rank's
+gathered result, by copy engines, while the next layer's GEMM runs.
 """
 from __future__ import annotations
 
