@@ -259,6 +259,20 @@ def run_profile_case(args):
         run = lambda: L.dw_mxfp8_gemm(xc.data_ptr(), xs.data_ptr(), wc.data_ptr(), ws.data_ptr(), y.data_ptr(), None,
                                       M, N, K, 1.0, 0.0, None, 0, sw.data_ptr(), st)
         units = f"gemm M={M} N={N} K={K}: {2.0 * M * N * K / 1e9:.1f} GFLOP per launch"
+    elif args.profile_case == "quant_batch":
+        # what one rank of a 4-GPU job quantises per step in one launch: its quarter of the rows of the four activations
+        # and its quarter of the four weights (dw_mxfp8_quantize_rows_batch)
+        import ctypes
+        shapes = [(M_TOKENS // 4, k) for _, k, _ in LAYERS] + [(n // 4, k) for _, k, n in LAYERS]
+        xs_ = [torch.randn(r, c, device=dev, generator=g).bfloat16() for r, c in shapes]
+        cs_ = [u8(r, c) for r, c in shapes]
+        ss_ = [u8(nv.scale_bytes(r, c, 1)) for r, c in shapes]
+        n = len(shapes)
+        P, I = ctypes.c_void_p * n, ctypes.c_int64 * n
+        a = (P(*[t.data_ptr() for t in xs_]), P(*[t.data_ptr() for t in cs_]), P(*[t.data_ptr() for t in ss_]),
+             I(*[r for r, _ in shapes]), I(*[c for _, c in shapes]))
+        run = lambda: L.dw_mxfp8_quantize_rows_batch(n, a[0], a[1], a[2], a[3], a[4], 0, 1, 0, st)
+        units = f"quant_batch {n} matrices: {sum(r * c for r, c in shapes) * 3.03125 / 1e6:.1f} MB algorithmic per launch"
     else:
         # quant_col_long: 2^21 rows, the transposed payload's rows 2 MiB apart (staged write-out)
         R, C = ((1 << 21), 128) if args.profile_case == "quant_col_long" else (16384, 8192)
@@ -919,7 +933,7 @@ def main():
                     help="N > 1: one quantiser launch per slice and weight shard instead of dw_mxfp8_quantize_rows_batch")
     ap.add_argument("--no-exchange", action="store_true",
                     help="N > 1: every rank quantises the whole of every X itself (no sharing of the quantisation over NVLink)")
-    ap.add_argument("--profile-case", default=None, choices=["gemm", "quant_row", "quant_both", "quant_col", "quant_col_long"],
+    ap.add_argument("--profile-case", default=None, choices=["gemm", "quant_row", "quant_both", "quant_col", "quant_col_long", "quant_batch"],
                     help="run a few launches of one kernel on a small case (for an ncu capture) and exit")
     ap.add_argument("--workload", default="linears", choices=["linears", "decoder_step"],
                     help="linears: the headline Llama-3-8B linear shapes; decoder_step: end-to-end optimize() training step (1 GPU)")
