@@ -923,7 +923,7 @@ def main():
     ap.add_argument("--two-streams", action="store_true", help="the next layer's quantisers on a second, lower-priority stream")
     ap.add_argument("--exchange-push", choices=["graph", "stream"], default="graph",
                     help="N > 1: the peer copies of the shared quantisation as one replayed CUDA graph per step (default) or issued one by one")
-    ap.add_argument("--exchange-budget", default="0,0.4,0.8,1.1,all",
+    ap.add_argument("--exchange-budget", default="0,0.2,0.4,0.6,0.8,1.1,all",
                     help="N > 1: share as many rows of X as a rank can receive (at 700 GB/s) in this multiple of the step's GEMM "
                          "time ('all' = every row, 0 = none: every rank quantises all of X itself, in one launch); several "
                          "values, comma-separated: each is tried for a few steps before the timed region and the fastest kept")
