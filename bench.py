@@ -929,6 +929,9 @@ def main():
                          "values, comma-separated: each is tried for a few steps before the timed region and the fastest kept")
     ap.add_argument("--quant-batch-pairs", action="store_true",
                     help="the activation and the weight shard of a layer quantised by one launch (dw_mxfp8_quantize_rows_batch)")
+    ap.add_argument("--exchange-own-work", choices=["auto", "start", "spread"], default="auto",
+                    help="N > 1 with shared quantisation: the rank's own quantisations in one launch at the start of the step, or spread "
+                         "behind the GEMMs; auto = measured before the timed region")
     ap.add_argument("--no-quant-batch", action="store_true",
                     help="N > 1: one quantiser launch per slice and weight shard instead of dw_mxfp8_quantize_rows_batch")
     ap.add_argument("--no-exchange", action="store_true",
@@ -1088,7 +1091,7 @@ def main():
             from deepwell_b200.exchange import QuantizedRowExchange
             exchange = QuantizedRowExchange([(M_TOKENS, layers[i]["k"]) for i in order], device=dev, push=args.exchange_push)
             exchange.set_shared_rows(ex_plans[0][1])
-            exchange_info = {"layers": [layers[i]["name"] for i in order], "how": exchange.how, "push": exchange.push}
+            exchange_info = {"layers": [layers[i]["name"] for i in order], "how": exchange.how, "push": exchange.push_mode}
         except Exception as e:          # no peer mapping on this box: every rank quantises everything itself
             exchange, ex_index = None, {}
             exchange_info = {"error": f"{type(e).__name__}: {str(e)[:300]}"}
@@ -1128,12 +1131,45 @@ def main():
         step_no[0] += 1
         return n_launch
 
+    exchange_spread = [args.exchange_own_work == "spread"]   # True: exchange_step_spread instead of exchange_step
+
+    def exchange_step_spread(record: bool, after_gemm=None):
+        """The same exchange with the rank's own work spread over the step: only its slices of the shared rows are quantised
+        at the start (they have to travel); the rows every rank quantises itself and the weight shards follow the GEMMs one by
+        one with DW_QUANT_OVERLAP_PREVIOUS, as in the step without exchange.  Layer i's GEMM is followed by the local rows of
+        activation i for the NEXT step (the other slot) and by the weight shard of layer i + 1."""
+        now, nxt = step_no[0] % 2, (step_no[0] + 1) % 2
+        order = sorted(ex_index, key=lambda j: ex_index[j])
+        shared, local = exchange.pieces([layers[i]["x"] for i in order], nxt)
+        n_launch = exchange.quantise(shared)
+        exchange.push(nxt)
+        for i, l in enumerate(layers):
+            a_codes, a_sf = exchange.operand(now, ex_index[i])
+            if after_gemm is not None and "gather_done" in l:
+                stream.wait_event(l["gather_done"])
+            nv.check(L.dw_mxfp8_gemm(a_codes.data_ptr(), a_sf.data_ptr(), l["wc"].data_ptr(), l["ws"].data_ptr(), l["y"].data_ptr(),
+                                     None, M_TOKENS, l["n"], l["k"], 1.0, 0.0, None, 0, status.data_ptr(), st), "gemm")
+            n_launch += 1
+            for x_rows, codes, scales in local[ex_index[i]]:
+                nv.check(L.dw_mxfp8_quantize_ex(x_rows.data_ptr(), codes.data_ptr(), scales.data_ptr(), x_rows.shape[0], x_rows.shape[1],
+                                                nv.DIR_ROW, nv.RULE_OCP_FLOOR, nv.SF_TILED, nv.QUANT_OVERLAP_PREVIOUS, st), "quantize X")
+                n_launch += 1
+            w = layers[(i + 1) % len(layers)]
+            nv.check(L.dw_mxfp8_quantize_ex(w["w"].data_ptr(), w["wc"].data_ptr(), w["ws"].data_ptr(), w["n"], w["k"],
+                                            nv.DIR_ROW, nv.RULE_OCP_FLOOR, nv.SF_TILED, nv.QUANT_OVERLAP_PREVIOUS, st), "quantize W")
+            n_launch += 1
+            if after_gemm is not None:
+                after_gemm(l)
+        exchange.fence(nxt)
+        step_no[0] += 1
+        return n_launch
+
     exchange_on = [True]       # the legs that gather every output keep NVLink for Y: there every rank quantises all of X itself
     exchange_used = [True]     # False: the candidates were measured and the plain step (nothing shared, separate launches) won
 
     def step(record: bool, after_gemm=None, force_separate=False):
         if exchange is not None and exchange_on[0] and not force_separate:
-            return exchange_step(record, after_gemm)
+            return exchange_step_spread(record, after_gemm) if exchange_spread[0] else exchange_step(record, after_gemm)
         if overlap and not force_separate:
             return overlapped_step(record, after_gemm)
         launches = 0
@@ -1198,6 +1234,7 @@ def main():
         step_no[0] = 0
         exchange.quantise_and_push([layers[i]["x"] for i in sorted(ex_index, key=lambda j: ex_index[j])], 0)
         exchange.fence(0)
+        quantise_operands(layers[0], 0)               # W of the first layer, which the spread form expects to be there
 
     if exchange is not None:
         if len(ex_plans) > 1:                         # measure the candidates, keep the fastest (the same on every rank)
@@ -1212,6 +1249,18 @@ def main():
             best = min(tried, key=lambda t: t[0])
             exchange.set_shared_rows(best[2])
             exchange_info["tried_ms_per_step"] = {("all" if f > 1e6 else f"{f:g} x GEMM time"): round(t, 4) for t, f, _ in tried}
+            # the best plan again with the rank's own quantisations spread over the step instead of one launch at its start
+            if args.exchange_own_work == "auto":
+                prime_exchange()
+                exchange_spread[0] = True
+                for _ in range(2):
+                    step(False)
+                t_ms, _ = timed_steps(6, False)
+                exchange_info["tried_ms_per_step"]["best plan, own work behind the GEMMs"] = round(t_ms / 6, 4)
+                if t_ms / 6 < best[0]:
+                    best = (t_ms / 6, best[1], best[2])
+                else:
+                    exchange_spread[0] = False
             # and the step without the exchange object: every rank quantises all of X itself, one launch per operand,
             # each behind the previous layer's GEMM
             exchange_on[0] = False
@@ -1223,6 +1272,7 @@ def main():
             exchange_used[0] = best[0] <= t_ms / 6
             exchange_on[0] = exchange_used[0]
         exchange_info["used"] = exchange_used[0]
+        exchange_info["own_work"] = "behind the GEMMs" if exchange_spread[0] else "one launch at the start of the step"
         if exchange_used[0]:
             exchange_info["shared_rows"] = list(exchange.shared_rows)
             exchange_info["bytes_pushed_per_rank_per_step"] = int(exchange.bytes_pushed_per_call)

@@ -131,7 +131,7 @@ class QuantizedRowExchange:
         # recorded once as a CUDA graph of memcpy nodes and replayed with a single launch.
         if push not in ("graph", "stream"):
             raise ValueError("push must be 'graph' or 'stream'")
-        self.push = push
+        self.push_mode = push
         self._graphs = None
         self.shared_rows: List[int] = []
         self.set_shared_rows(None)
@@ -147,7 +147,7 @@ class QuantizedRowExchange:
         self.shared_rows = wanted
         self.bytes_pushed_per_call = sum(self._slice_bytes(i) for i in range(len(self.shapes))) * (self.world - 1)
         self._graphs = None
-        if self.push == "graph" and self.world > 1 and self.bytes_pushed_per_call > 0:
+        if self.push_mode == "graph" and self.world > 1 and self.bytes_pushed_per_call > 0:
             self._graphs = [self._capture_copies(slot) for slot in range(self.slots)]
         dist.barrier(group=self.group)
 
@@ -197,39 +197,50 @@ class QuantizedRowExchange:
             self._issue_copies(slot)
         return graph
 
-    def quantise_and_push(self, xs: Sequence[torch.Tensor], slot: int,
-                          extra: Sequence[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = ()) -> int:
-        """Quantises this rank's row slice of every activation (and the rows that are not shared) into `slot` on the current
-        stream and copies the slices into every peer's buffer (copy stream: copy engines over NVLink, asynchronous to the
-        current stream).  `extra`: further (input, codes, tiled scales) triples quantised row-wise in the same launches,
-        e.g. the rank's weight shards: the pieces of a sharded step are small, and one launch for all of them saves each
-        its own ramp and tail.  Returns the number of quantiser launches."""
+    def pieces(self, xs: Sequence[torch.Tensor], slot: int):
+        """(shared, local): the (input rows, codes, scales) triples that fill `slot` on this rank — `shared`: this rank's part
+        of the shared rows of every activation (what push() sends to the peers); `local`: per activation the rows every rank
+        quantises itself (a list of lists, in the order of the activations).  A caller that wants the local rows quantised
+        elsewhere in its step (behind a GEMM, say) quantises `shared`, calls push(slot), and issues `local` when it likes,
+        before fence(slot)."""
         if len(xs) != len(self.shapes):
             raise ValueError("one tensor per registered activation")
-        jobs = []
+        shared, local = [], []
         for i, x in enumerate(xs):
             rows, cols = self.shapes[i]
             if tuple(x.shape) != (rows, cols) or x.dtype != torch.bfloat16 or not x.is_contiguous():
                 raise ValueError(f"activation {i} must be a contiguous bfloat16 [{rows}, {cols}] tensor")
             codes, scales = self._region(self.views[self.rank], slot, i)
-            r0, r1 = self._rows_of(i, self.rank)
-            pieces = [(r0, r1)] if r1 > r0 else []                 # this rank's part of the shared rows
-            if self.shared_rows[i] < rows:
-                pieces.append((self.shared_rows[i], rows))         # the rows every rank quantises itself
-            for p0, p1 in pieces:
+
+            def triple(p0, p1):
                 c_lo, c_hi, s_lo, s_hi = self._byte_ranges(i, p0, p1)
-                jobs.append((x[p0:p1], codes[c_lo:c_hi], scales[s_lo:s_hi]))
-        jobs.extend(extra)
+                return (x[p0:p1], codes[c_lo:c_hi], scales[s_lo:s_hi])
+
+            r0, r1 = self._rows_of(i, self.rank)
+            if r1 > r0:
+                shared.append(triple(r0, r1))
+            local.append([triple(self.shared_rows[i], rows)] if self.shared_rows[i] < rows else [])
+        return shared, local
+
+    def quantise(self, jobs) -> int:
+        """Row-wise quantisation of (input, codes, tiled scales) triples on the current stream, in one launch per eight where
+        the shapes allow.  Returns the number of launches."""
+        jobs = list(jobs)
+        if not jobs:
+            return 0
         if all(j[0].shape[0] % 128 == 0 and j[0].shape[1] % 128 == 0 and j[0].data_ptr() % 16 == 0 and j[1].data_ptr() % 16 == 0
                for j in jobs):
-            launches = nv.quantize_rows_batch_into([j[0] for j in jobs], [j[1] for j in jobs], [j[2] for j in jobs],
-                                                   self.rule, nv.SF_TILED)
-        else:                                                      # shapes the batched launch does not take
-            for x, codes, scales in jobs:
-                nv.quantize_into(x, codes, scales, nv.DIR_ROW, self.rule, nv.SF_TILED)
-            launches = len(jobs)
+            return nv.quantize_rows_batch_into([j[0] for j in jobs], [j[1] for j in jobs], [j[2] for j in jobs],
+                                               self.rule, nv.SF_TILED)
+        for x, codes, scales in jobs:                              # shapes the batched launch does not take
+            nv.quantize_into(x, codes, scales, nv.DIR_ROW, self.rule, nv.SF_TILED)
+        return len(jobs)
+
+    def push(self, slot: int) -> None:
+        """Behind the work issued so far on the current stream: this rank's shared slices of `slot` into every peer's buffer
+        (copy stream: copy engines over NVLink, asynchronous to the current stream)."""
         if self.bytes_pushed_per_call == 0:
-            return launches
+            return
         self._quantised[slot].record()
         self.copy_stream.wait_event(self._quantised[slot])
         with torch.cuda.stream(self.copy_stream):
@@ -238,6 +249,16 @@ class QuantizedRowExchange:
             else:
                 self._issue_copies(slot)
             self._pushed[slot].record()
+
+    def quantise_and_push(self, xs: Sequence[torch.Tensor], slot: int,
+                          extra: Sequence[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = ()) -> int:
+        """Quantises this rank's row slice of every activation (and the rows that are not shared) into `slot` on the current
+        stream and copies the slices into every peer's buffer.  `extra`: further (input, codes, tiled scales) triples
+        quantised row-wise in the same launches, e.g. the rank's weight shards: the pieces of a sharded step are small, and
+        one launch for all of them saves each its own ramp and tail.  Returns the number of quantiser launches."""
+        shared, local = self.pieces(xs, slot)
+        launches = self.quantise(shared + [j for per in local for j in per] + list(extra))
+        self.push(slot)
         return launches
 
     def fence(self, slot: int) -> None:
